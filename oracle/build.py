@@ -1,0 +1,81 @@
+"""Build recipe for the CPU oracle (test infrastructure, never imported by the product).
+
+    python oracle/build.py          # oracle/libmp_oracle.so  (C restatement, gcc + OpenMP)
+    python oracle/build.py --ref    # additionally oracle/_ref/  (the reference's own C++ CPU
+                                    #  extensions, compiled from its sources where they lie)
+
+The reference sources are only read, never copied; the `--ref` outputs go to `oracle/_ref/`,
+which is git-ignored.  `--ref` needs the reference checkout (path in $MPL_REFERENCE_DIR,
+default the directory mounted next to this repository) and is skipped when it is absent.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, "libmp_oracle.so")
+SRC = os.path.join(HERE, "mp_oracle.c")
+REF_OUT = os.path.join(HERE, "_ref")
+
+
+def reference_dir():
+    return os.environ.get("MPL_REFERENCE_DIR", "/root/reference")
+
+
+def _cpu_has_fma():
+    try:
+        with open("/proc/cpuinfo") as f:
+            return " fma " in f.read()
+    except OSError:
+        return False
+
+
+def build_oracle(force=False):
+    if (not force and os.path.exists(LIB)
+            and os.path.getmtime(LIB) >= os.path.getmtime(SRC)):
+        return LIB
+    cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
+    cmd = [cc, "-O2", "-std=c11", "-fopenmp", "-fPIC", "-shared", "-ffp-contract=off"]
+    if _cpu_has_fma():
+        cmd.append("-mfma")  # fmaf() becomes one instruction; nothing else is contracted
+    cmd += [SRC, "-o", LIB, "-lm"]
+    subprocess.check_call(cmd)
+    return LIB
+
+
+def build_reference_cpu(force=False):
+    """Compile the reference's TRWP / ISGMR C++ CPU extensions (forward only) into oracle/_ref/.
+
+    Sources used (unmodified, read in place): MPLayers/TRWP/TRWP.cpp, MPLayers/ISGMR/ISGMR.cpp,
+    MPLayers/common.cpp, tools/cpp/utils.cpp.  USE_CUDA is left undefined, so only the CPU path
+    (ForwardCPU) is compiled.  Returns the output directory, or None if the reference is absent.
+    """
+    ref = reference_dir()
+    if not os.path.isdir(os.path.join(ref, "MPLayers")):
+        return None
+    os.makedirs(REF_OUT, exist_ok=True)
+    os.environ["CXX"] = "/usr/bin/g++"  # the default wrapper compiler cannot link OpenMP here
+    from torch.utils.cpp_extension import load
+    mp = os.path.join(ref, "MPLayers")
+    for name in ("TRWP", "ISGMR"):
+        bdir = os.path.join(REF_OUT, "build_" + name)
+        so = os.path.join(REF_OUT, name + ".so")
+        if os.path.exists(so) and not force:
+            continue
+        os.makedirs(bdir, exist_ok=True)
+        load(name=name,
+             sources=[os.path.join(mp, name, name + ".cpp"), os.path.join(mp, "common.cpp"),
+                      os.path.join(ref, "tools", "cpp", "utils.cpp")],
+             extra_include_paths=[mp, os.path.join(mp, name), os.path.join(ref, "tools", "cpp")],
+             extra_cflags=["-O3", "-fopenmp", "-Wno-deprecated-declarations", "-w",
+                           "-DMAX_DISPARITY=256", "-DTORCH_VERSION_MAJOR=2"],
+             extra_ldflags=["-fopenmp"], build_directory=bdir, verbose=False)
+        built = os.path.join(bdir, name + ".so")
+        os.replace(built, so)
+    return REF_OUT
+
+
+if __name__ == "__main__":
+    print(build_oracle(force="--force" in sys.argv))
+    if "--ref" in sys.argv:
+        print(build_reference_cpu(force="--force" in sys.argv))

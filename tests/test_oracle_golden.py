@@ -1,0 +1,38 @@
+"""Pins the CPU oracle (oracle/mp_oracle.c) to golden vectors produced by the reference's own
+pure-PyTorch autograd implementation (tests/golden/make_golden.py).  CPU only."""
+import os
+
+import numpy as np
+import pytest
+
+import cases
+from helpers import COST_RTOL, GRAD_RTOL, rel_err
+from oracle import oracle
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_oracle_matches_reference_golden(name):
+    inp = cases.make_inputs(name)
+    gold = np.load(os.path.join(GOLD, name + ".npz"))
+    fwd = oracle.forward(inp["mode"], inp["unary"], inp["ctx"], inp["ew"], inp["n_dir"],
+                         inp["n_iter"], training=True)
+    assert rel_err(fwd["cost"], gold["cost"]) < COST_RTOL
+    if "min_idx" in gold.files:
+        # float64 reference vs float32 oracle: identical indices except where two candidates
+        # are closer than fp32 resolution; the seeded small cases have none.
+        assert np.array_equal(fwd["norm_idx"], gold["norm_idx"])
+        assert np.array_equal(fwd["min_idx"], gold["min_idx"])
+    for keep_diag in (False, True):
+        bwd = oracle.backward(inp["mode"], inp["ctx"], inp["ew"], inp["dcost"], fwd["min_idx"],
+                              fwd["norm_idx"], keep_diag=keep_diag)
+        assert rel_err(bwd["dunary"], gold["dunary"]) < GRAD_RTOL
+        assert rel_err(bwd["dew"], gold["dew"]) < GRAD_RTOL
+        want = gold["dctx"].copy()
+        if keep_diag:
+            if want.ndim == 2:
+                want[np.diag_indices_from(want)] = gold["dctx_diag"]
+            else:
+                want[0] = gold["dctx_diag"][0]
+        assert rel_err(bwd["dctx"], want) < GRAD_RTOL
