@@ -1,0 +1,136 @@
+/*
+ * mplayers_b200 -- C ABI of the TRWP / ISGMR min-sum message-passing layers for NVIDIA B200
+ * (sm_100a).  Plain pointers and sizes only; every pointer is DEVICE memory of the current CUDA
+ * device unless stated otherwise, and every call is asynchronous on `stream` (a cudaStream_t
+ * passed as void*; NULL = the legacy default stream).
+ *
+ * Tensor layouts are the reference extension's (all contiguous, fp32 values, u8 indices):
+ *   unary, cost_final, dcost_final, dunary ....... [B, cv, H, W, L]
+ *   msg, msg_update, dmsg, dmsg_update ........... [D, B, cv, H, W, L]
+ *   edge_weights, dedge_weights .................. [D, B, cv, H, W]   (weight of edge front->cur at cur)
+ *   msg_min_index ................................ [I, D, B, cv, H, W, L]   u8
+ *   msg_norm_index ............................... [I, D, B, cv, H, W]      u8
+ *   label_all .................................... [I, B, cv, H, W]         u8
+ *   context ...................................... [L] (rank 1: ctx[|c-f|]) or [L, L] (rank 2: read
+ *                                                  as ctx[min(c,f)][max(c,f)], upper triangle)
+ * The reference selects the context convention by `L == 21`; here it is `context_rank`.
+ *
+ * Every function returns MPL_OK or an error code; mpl_last_error() gives the message of the last
+ * failure on the calling thread.  Nothing is computed on the CPU: without a CUDA device the
+ * compute entry points fail with MPL_ERR_CUDA.
+ */
+#ifndef MPLAYERS_B200_H_
+#define MPLAYERS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MPL_OK 0
+#define MPL_ERR_INVALID 1     /* bad shape, NULL pointer, workspace too small */
+#define MPL_ERR_UNSUPPORTED 2 /* e.g. n_disp > 256, odd n_dir */
+#define MPL_ERR_CUDA 3        /* a CUDA runtime call failed */
+
+/* Problem description.  Replaces the shape reads the reference does from its at::Tensor
+ * arguments (MPLayers/TRWP/TRWP_forward.cu:390-408, MPLayers/TRWP/TRWP_backward.cu:288-294) and
+ * the scalar arguments of Forward()/Backward() (MPLayers/TRWP/TRWP.cpp:245-256,285-295;
+ * MPLayers/ISGMR/ISGMR.cpp:300-313,344-356). */
+typedef struct mpl_problem {
+  int32_t n_iter;           /* I */
+  int32_t n_dir;            /* D: 2..16, even; directions 0..D-1 of MPLayers/common.cpp:28-76 */
+  int32_t batch;            /* B */
+  int32_t n_cv;             /* cv (second batch-like axis) */
+  int32_t height;           /* H */
+  int32_t width;            /* W */
+  int32_t n_disp;           /* L: 1..256 */
+  int32_t context_rank;     /* 1 or 2 */
+  int32_t enable_min_a_dir; /* cost = U + min_d M_d instead of U + sum_d M_d */
+  int32_t enable_sgm;       /* ISGMR only: cost = D*U + sum_d M_d */
+  int32_t keep_diag;        /* backward: 1 = also accumulate dcontext where c == f (what
+                               MPLayers/TRWP_hard_soft does), 0 = skip it (TRWP / ISGMR libs,
+                               MPLayers/TRWP/TRWP_backward.cu:111-112) */
+  float rho;                /* 0.5 for TRWP, 1 for ISGMR (pytorch/MP_module.py:172) */
+} mpl_problem;
+
+/* Bytes of device scratch the forward / backward entry points need for `p` (never 0). */
+size_t mpl_forward_workspace_bytes(const mpl_problem* p);
+size_t mpl_backward_workspace_bytes(const mpl_problem* p);
+
+/* TRWP forward.  Replaces TRWP.forward of the reference extension
+ * (MPLayers/TRWP/TRWP.cpp:245-283,323-326 -> ForwardCUDA, MPLayers/TRWP/TRWP_forward.cu:378-564).
+ *   msg            in/out: must be zero on entry, holds the final messages on exit
+ *   edge_weights   NULL = every weight is 1
+ *   msg_min_index, msg_norm_index   both NULL = inference (nothing saved); both non-NULL = training
+ *   label_all      NULL = do not save per-iteration labels
+ * The reference's `unary_update` scratch argument has no counterpart (the update is fused). */
+int mpl_trwp_forward(const mpl_problem* p, const float* unary, const float* context,
+                     const float* edge_weights, float* msg, float* cost_final,
+                     uint8_t* msg_min_index, uint8_t* msg_norm_index, uint8_t* label_all,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* TRWP backward.  Replaces TRWP.backward (MPLayers/TRWP/TRWP.cpp:285-321 -> BackwardCUDA,
+ * MPLayers/TRWP/TRWP_backward.cu:277-437).
+ *   dunary          out (overwritten)
+ *   dcontext        accumulated into ([L] or [L,L]; zero it for a plain gradient)
+ *   dedge_weights   accumulated into; may be NULL when edge_weights is NULL
+ *   dmsg            scratch [D,B,cv,H,W,L], contents on entry ignored
+ * The reference's `dunary_update` scratch argument has no counterpart. */
+int mpl_trwp_backward(const mpl_problem* p, const float* context, const float* edge_weights,
+                      const float* dcost_final, const uint8_t* msg_min_index,
+                      const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                      float* dedge_weights, float* dmsg, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/* ISGMR (and SGM) forward.  Replaces ISGMR.forward (MPLayers/ISGMR/ISGMR.cpp:300-342,399-404 ->
+ * ForwardCUDA, MPLayers/ISGMR/ISGMR_forward.cu:433-665).  msg and msg_update must both be zero on
+ * entry; the two buffers are used alternately (no per-iteration copy) and on exit `msg` holds the
+ * final messages, `msg_update` those of the iteration before. */
+int mpl_isgmr_forward(const mpl_problem* p, const float* unary, const float* context,
+                      const float* edge_weights, float* msg, float* msg_update, float* cost_final,
+                      uint8_t* msg_min_index, uint8_t* msg_norm_index, uint8_t* label_all,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ISGMR backward.  Replaces ISGMR.backward (MPLayers/ISGMR/ISGMR.cpp:344-397 -> BackwardCUDA,
+ * MPLayers/ISGMR/ISGMR_backward.cu:290-497).  dmsg and dmsg_update are scratch [D,B,cv,H,W,L],
+ * contents on entry ignored. */
+int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* edge_weights,
+                       const float* dcost_final, const uint8_t* msg_min_index,
+                       const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                       float* dedge_weights, float* dmsg, float* dmsg_update, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* Message of the last error on the calling thread ("" if none).  Replaces the reference's
+ * printf-and-return error reporting (MPLayers/TRWP/TRWP.cpp:269-273,316). */
+const char* mpl_last_error(void);
+
+/* Number of CUDA kernels this library has launched in this process so far (all threads). */
+int64_t mpl_kernel_launches(void);
+
+/* Library version (major*10000 + minor*100 + patch). */
+int32_t mpl_version(void);
+
+/* Chain enumeration used by every kernel (host-side copy, for tests and callers that want to
+ * inspect the traversal).  Counterpart of the reference's n_trees / tree_id -> start mapping
+ * (MPLayers/common.cpp:78-87, MPLayers/TRWP/TRWP_forward.cu:201-218,310-312), restated as: a
+ * chain starts at every pixel whose predecessor lies outside the image.
+ * mpl_chain_count: chains per image of direction `dir` (-1 on bad arguments).
+ * mpl_chain_geometry: out5 = {h_start, w_start, n_pixels, h_step, w_step} of chain `chain`. */
+int32_t mpl_chain_count(int32_t dir, int32_t height, int32_t width);
+int32_t mpl_chain_geometry(int32_t dir, int32_t height, int32_t width, int32_t chain, int32_t* out5);
+
+/* Per-launch timing for benchmarks (no counterpart in the reference, which times with
+ * time.time() around whole calls, MPLayers/main.py:271-300).  While enabled, every sweep and
+ * elementwise kernel launch is bracketed by CUDA events on its stream.  mpl_profile_read waits
+ * for the recorded events and returns the summed device time and launch count of one kind:
+ * 0 = forward sweep, 1 = backward sweep, 2 = elementwise (aggregation, backward prologue). */
+void mpl_profile_enable(int32_t on);
+int32_t mpl_profile_read(int32_t kind, double* total_ms, int64_t* launches);
+void mpl_profile_reset(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MPLAYERS_B200_H_ */

@@ -1,0 +1,67 @@
+"""Drop-in for the reference's `TRWP` extension module (lib_stereo.TRWP / lib_seg.TRWP, and the hard
+branch of TRWP_hard_soft): `forward` / `backward` with the reference's positional signatures
+(MPLayers/TRWP/TRWP.cpp:245-256,285-295,323-326), writing into caller-allocated tensors.
+
+Differences a caller can see: errors raise RuntimeError instead of printing; the kernels run on
+the current CUDA stream of the tensors' device; the `unary_update` / `dunary_update` scratch
+tensors are accepted and ignored; the context convention follows the tensor rank instead of
+`n_disp == 21`; there is no CPU path.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+
+keep_diag = False  # TRWP_hard_soft accumulates dcontext on the diagonal, the TRWP lib does not
+
+
+def _problem(n_iter, msg_shape, context, rho, enable_min_a_dir=0, enable_sgm=0, keep_diag_=0):
+    n_dir, batch, n_cv, h, w, n_disp = msg_shape
+    return _lib.Problem(int(n_iter), n_dir, batch, n_cv, h, w, n_disp,
+                        _lib.context_rank(context, n_disp), int(enable_min_a_dir), int(enable_sgm),
+                        int(keep_diag_), float(rho))
+
+
+def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, cost_final,
+            msg_min_index, msg_norm_index, unary_update, label_all):
+    dev = unary.device
+    for t, n in ((unary, "unary"), (context, "context"), (edge_weights, "edge_weights"), (msg, "msg"),
+                 (cost_final, "cost_final")):
+        _lib.require(t, n, torch.float32, dev)
+    for t, n in ((msg_min_index, "msg_min_index"), (msg_norm_index, "msg_norm_index"),
+                 (label_all, "label_all")):
+        _lib.require(t, n, torch.uint8, dev)
+    if msg.dim() != 6 or tuple(unary.shape) != tuple(msg.shape[1:]):
+        raise RuntimeError("msg must be [D,B,cv,H,W,L] matching unary [B,cv,H,W,L]")
+    prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir)
+    with torch.cuda.device(dev):
+        nbytes = _lib.lib().mpl_forward_workspace_bytes(ctypes.byref(prob))
+        ws = _lib.workspace(nbytes, dev)
+        _lib.check(_lib.lib().mpl_trwp_forward(
+            ctypes.byref(prob), _lib.ptr(unary), _lib.ptr(context), _lib.ptr(edge_weights),
+            _lib.ptr(msg), _lib.ptr(cost_final), _lib.ptr(msg_min_index), _lib.ptr(msg_norm_index),
+            _lib.ptr(label_all), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+
+
+def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index, dunary,
+             dcontext, dedge_weights, dmsg, dunary_update, keep_diag=None):
+    dev = dcost_final.device
+    for t, n in ((context, "context"), (edge_weights, "edge_weights"), (dcost_final, "dcost_final"),
+                 (dunary, "dunary"), (dcontext, "dcontext"), (dedge_weights, "dedge_weights"),
+                 (dmsg, "dmsg")):
+        _lib.require(t, n, torch.float32, dev)
+    for t, n in ((msg_min_index, "msg_min_index"), (msg_norm_index, "msg_norm_index")):
+        _lib.require(t, n, torch.uint8, dev)
+    if msg_min_index.dim() != 7:
+        raise RuntimeError("msg_min_index must be [I,D,B,cv,H,W,L]")
+    kd = globals()["keep_diag"] if keep_diag is None else keep_diag
+    prob = _problem(msg_min_index.size(0), tuple(msg_min_index.shape[1:]), context, rho,
+                    keep_diag_=kd)
+    with torch.cuda.device(dev):
+        nbytes = _lib.lib().mpl_backward_workspace_bytes(ctypes.byref(prob))
+        ws = _lib.workspace(nbytes, dev)
+        _lib.check(_lib.lib().mpl_trwp_backward(
+            ctypes.byref(prob), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(dcost_final),
+            _lib.ptr(msg_min_index), _lib.ptr(msg_norm_index), _lib.ptr(dunary), _lib.ptr(dcontext),
+            _lib.ptr(dedge_weights), _lib.ptr(dmsg), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))

@@ -1,0 +1,362 @@
+// C ABI of libmplayers_b200 (declared in include/mplayers_b200.h): argument validation and the
+// host loops over iterations and directions.  The loop ORDER is the reference's
+// (MPLayers/TRWP/TRWP_forward.cu:440-548, MPLayers/TRWP/TRWP_backward.cu:337-424,
+// MPLayers/ISGMR/ISGMR_forward.cu:506-654, MPLayers/ISGMR/ISGMR_backward.cu:353-484); what runs
+// inside each step is one fused kernel instead of the reference's kernel + memcpy/memset pairs.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/mplayers_b200.h"
+#include "mp_common.cuh"
+
+namespace mpl {
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+static std::atomic<int> g_prof_on{0};
+static std::mutex g_prof_mu;
+struct ProfPair {
+  int kind;
+  cudaEvent_t a, b;
+};
+static std::vector<ProfPair> g_prof_pending;
+static double g_prof_ms[kProfKinds];
+static long long g_prof_n[kProfKinds];
+
+ProfScope::ProfScope(int kind, cudaStream_t st) : kind_(kind), st_(st), a_(nullptr), b_(nullptr), on_(false) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  if (cudaEventCreate(&a_) != cudaSuccess || cudaEventCreate(&b_) != cudaSuccess) return;
+  on_ = cudaEventRecord(a_, st_) == cudaSuccess;
+}
+ProfScope::~ProfScope() {
+  if (!on_) return;
+  cudaEventRecord(b_, st_);
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof_pending.push_back({kind_, a_, b_});
+}
+}  // namespace mpl
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(MPL_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define MPL_CUDA(expr)                                   \
+  do {                                                   \
+    cudaError_t e__ = (expr);                            \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #expr); \
+  } while (0)
+
+struct Dims {
+  long long nimg, npix, slice;
+  int ctx_elems;
+};
+
+int validate(const mpl_problem* p, Dims* d) {
+  if (!p) return fail(MPL_ERR_INVALID, "problem is NULL");
+  if (p->n_iter < 0 || p->batch < 1 || p->n_cv < 1 || p->height < 1 || p->width < 1)
+    return fail(MPL_ERR_INVALID, "bad shape: n_iter=%d batch=%d n_cv=%d height=%d width=%d", p->n_iter,
+                p->batch, p->n_cv, p->height, p->width);
+  if (p->n_disp < 1 || p->n_disp > 256)
+    return fail(MPL_ERR_UNSUPPORTED, "n_disp=%d outside 1..256 (argmin indices are 8-bit)", p->n_disp);
+  if (p->n_dir < 2 || p->n_dir > 16 || (p->n_dir & 1))
+    return fail(MPL_ERR_UNSUPPORTED, "n_dir=%d: must be even and in 2..16", p->n_dir);
+  if (p->context_rank != 1 && p->context_rank != 2)
+    return fail(MPL_ERR_INVALID, "context_rank=%d: must be 1 or 2", p->context_rank);
+  const long long per_img = (long long)p->height * p->width * p->n_disp;
+  if (per_img >= (1ll << 31))
+    return fail(MPL_ERR_UNSUPPORTED, "height*width*n_disp=%lld must be below 2^31", per_img);
+  d->nimg = (long long)p->batch * p->n_cv;
+  d->npix = d->nimg * p->height * p->width;
+  d->slice = d->npix * p->n_disp;
+  if (d->nimg * 4096ll >= (1ll << 31) || d->npix >= (1ll << 40))
+    return fail(MPL_ERR_UNSUPPORTED, "batch*n_cv=%lld too large", d->nimg);
+  d->ctx_elems = p->context_rank == 2 ? p->n_disp * p->n_disp : p->n_disp;
+  return MPL_OK;
+}
+
+int check_chain_count(const mpl_problem* p, const Dims& d) {
+  for (int k = 0; k < p->n_dir; ++k) {
+    const long long n = (long long)mpl::make_geom(k, p->height, p->width).n_chains * d.nimg;
+    if (n * p->n_dir >= (1ll << 31)) return fail(MPL_ERR_UNSUPPORTED, "too many chains (%lld)", n);
+  }
+  return MPL_OK;
+}
+
+void fill_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, const float* unary,
+                  const float* ctx, const float* ew, void* workspace) {
+  fp.unary = unary;
+  fp.ctx = ctx;
+  fp.ew = ew;
+  fp.info = static_cast<const mpl::CtxInfo*>(workspace);
+  fp.H = p->height;
+  fp.W = p->width;
+  fp.L = p->n_disp;
+  fp.D = p->n_dir;
+  fp.nimg = (int)d.nimg;
+  fp.slice = d.slice;
+  fp.pslice = d.npix;
+  fp.rho = p->rho;
+  fp.ctx_rank = p->context_rank;
+}
+
+void set_dirs(mpl::FwdParams& fp, int dir0, int ndirs) {
+  fp.dir0 = dir0;
+  fp.ndirs = ndirs;
+  fp.chain_off[0] = 0;
+  for (int i = 0; i < ndirs; ++i)
+    fp.chain_off[i + 1] = fp.chain_off[i] + mpl::make_geom(dir0 + i, fp.H, fp.W).n_chains * fp.nimg;
+}
+
+int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const float* context,
+                   const float* edge_weights, float* msg, float* msg_update, float* cost_final,
+                   uint8_t* msg_min_index, uint8_t* msg_norm_index, uint8_t* label_all,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (int rc = check_chain_count(p, d)) return rc;
+  if (!unary || !context || !msg || !cost_final || (isgmr && !msg_update))
+    return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if ((msg_min_index == nullptr) != (msg_norm_index == nullptr))
+    return fail(MPL_ERR_INVALID, "msg_min_index and msg_norm_index must both be given or both be NULL");
+  if (!workspace || workspace_bytes < mpl_forward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_forward_workspace_bytes(p));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool train = msg_min_index != nullptr;
+  const int D = p->n_dir, L = p->n_disp;
+
+  mpl::FwdParams fp{};
+  fill_forward(fp, p, d, unary, context, edge_weights, workspace);
+  MPL_CUDA(mpl::launch_analyze(context, L, p->context_rank, edge_weights, d.npix * D,
+                               static_cast<mpl::CtxInfo*>(workspace), st));
+
+  const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
+  // ISGMR alternates between the two message buffers so that the last iteration writes `msg`.
+  float* rd = msg;
+  float* wr = msg;
+  if (isgmr) {
+    const bool last_writes_msg_when_first_writes_msg = (p->n_iter % 2) == 1;
+    wr = last_writes_msg_when_first_writes_msg ? msg : msg_update;
+    rd = wr == msg ? msg_update : msg;
+  }
+  for (int it = 0; it < p->n_iter; ++it) {
+    fp.min_idx = train ? msg_min_index + (long long)it * D * d.slice : nullptr;
+    fp.norm_idx = train ? msg_norm_index + (long long)it * D * d.npix : nullptr;
+    fp.msg_read = rd;
+    fp.msg_write = wr;
+    if (isgmr) {
+      set_dirs(fp, 0, D);  // every direction reads the previous iteration's messages: one launch
+      MPL_CUDA(mpl::launch_forward_sweep(fp, train, st));
+      float* t = rd;
+      rd = wr;
+      wr = t;
+    } else {
+      for (int dir = 0; dir < D; ++dir) {  // later directions see earlier ones' new messages
+        set_dirs(fp, dir, 1);
+        MPL_CUDA(mpl::launch_forward_sweep(fp, train, st));
+      }
+    }
+    if (label_all) {
+      const float* cur = isgmr ? rd : msg;  // after the swap `rd` holds this iteration's messages
+      MPL_CUDA(mpl::launch_aggregate(unary, cur, cost_final, label_all + (long long)it * d.npix, d.npix,
+                                     L, D, d.slice, factor, p->enable_min_a_dir, st));
+    }
+  }
+  const float* fin = isgmr ? rd : msg;
+  if (isgmr && p->n_iter > 0 && fin != msg)
+    return fail(MPL_ERR_CUDA, "internal: ISGMR buffer parity");
+  MPL_CUDA(mpl::launch_aggregate(unary, msg, cost_final, nullptr, d.npix, L, D, d.slice, factor,
+                                 p->enable_min_a_dir, st));
+  return MPL_OK;
+}
+
+int backward_common(bool isgmr, const mpl_problem* p, const float* context, const float* edge_weights,
+                    const float* dcost_final, const uint8_t* msg_min_index,
+                    const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                    float* dedge_weights, float* dmsg, float* dmsg_update, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (int rc = check_chain_count(p, d)) return rc;
+  if (!context || !dcost_final || !msg_min_index || !msg_norm_index || !dunary || !dcontext || !dmsg ||
+      (isgmr && !dmsg_update))
+    return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if (edge_weights && !dedge_weights)
+    return fail(MPL_ERR_INVALID, "dedge_weights is NULL although edge_weights is given");
+  if (!workspace || workspace_bytes < mpl_backward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_backward_workspace_bytes(p));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int D = p->n_dir, L = p->n_disp;
+  const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg);
+  float* part = static_cast<float*>(workspace);
+  MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
+
+  const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
+  float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced
+  float* Y = isgmr ? dmsg : dmsg;         // gradients of the messages the sweeps read
+  MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, st));
+  if (isgmr) MPL_CUDA(cudaMemsetAsync(Y, 0, (size_t)D * d.slice * sizeof(float), st));
+
+  mpl::BwdParams bp{};
+  bp.ctx = context;
+  bp.ew = edge_weights;
+  bp.dunary = dunary;
+  bp.dctx_part = part;
+  bp.n_slots = n_slots;
+  bp.H = p->height;
+  bp.W = p->width;
+  bp.L = L;
+  bp.D = D;
+  bp.nimg = (int)d.nimg;
+  bp.slice = d.slice;
+  bp.pslice = d.npix;
+  bp.rho = p->rho;
+  bp.ctx_rank = p->context_rank;
+  bp.keep_diag = p->keep_diag;
+  for (int it = p->n_iter - 1; it >= 0; --it) {
+    for (int dir = D - 1; dir >= 0; --dir) {
+      bp.dir = dir;
+      bp.min_idx = msg_min_index + ((long long)it * D + dir) * d.slice;
+      bp.norm_idx = msg_norm_index + ((long long)it * D + dir) * d.npix;
+      bp.dm_read = X;
+      bp.dm_acc = Y;
+      bp.dew = (edge_weights && dedge_weights) ? dedge_weights + (long long)dir * d.npix : nullptr;
+      MPL_CUDA(mpl::launch_backward_sweep(bp, st));
+    }
+    if (isgmr) {  // every slice of X has been zeroed by its sweep: it becomes the next accumulator
+      float* t = X;
+      X = Y;
+      Y = t;
+    }
+  }
+  MPL_CUDA(mpl::launch_dctx_reduce(part, n_slots, L, p->context_rank, p->keep_diag, dcontext, st));
+  return MPL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t mpl_forward_workspace_bytes(const mpl_problem* p) {
+  (void)p;
+  return 256;
+}
+
+size_t mpl_backward_workspace_bytes(const mpl_problem* p) {
+  Dims d;
+  if (validate(p, &d) != MPL_OK) return 256;
+  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
+  const size_t b = (size_t)n_slots * d.ctx_elems * sizeof(float);
+  return b < 256 ? 256 : b;
+}
+
+int mpl_trwp_forward(const mpl_problem* p, const float* unary, const float* context,
+                     const float* edge_weights, float* msg, float* cost_final, uint8_t* msg_min_index,
+                     uint8_t* msg_norm_index, uint8_t* label_all, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  return forward_common(false, p, unary, context, edge_weights, msg, nullptr, cost_final, msg_min_index,
+                        msg_norm_index, label_all, workspace, workspace_bytes, stream);
+}
+
+int mpl_isgmr_forward(const mpl_problem* p, const float* unary, const float* context,
+                      const float* edge_weights, float* msg, float* msg_update, float* cost_final,
+                      uint8_t* msg_min_index, uint8_t* msg_norm_index, uint8_t* label_all,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  return forward_common(true, p, unary, context, edge_weights, msg, msg_update, cost_final,
+                        msg_min_index, msg_norm_index, label_all, workspace, workspace_bytes, stream);
+}
+
+int mpl_trwp_backward(const mpl_problem* p, const float* context, const float* edge_weights,
+                      const float* dcost_final, const uint8_t* msg_min_index,
+                      const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                      float* dedge_weights, float* dmsg, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+  return backward_common(false, p, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,
+                         dunary, dcontext, dedge_weights, dmsg, nullptr, workspace, workspace_bytes,
+                         stream);
+}
+
+int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* edge_weights,
+                       const float* dcost_final, const uint8_t* msg_min_index,
+                       const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                       float* dedge_weights, float* dmsg, float* dmsg_update, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+  return backward_common(true, p, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,
+                         dunary, dcontext, dedge_weights, dmsg, dmsg_update, workspace,
+                         workspace_bytes, stream);
+}
+
+const char* mpl_last_error(void) { return g_err.c_str(); }
+
+int64_t mpl_kernel_launches(void) { return mpl::g_launches.load(std::memory_order_relaxed); }
+
+int32_t mpl_version(void) { return 100; }
+
+int32_t mpl_chain_count(int32_t dir, int32_t height, int32_t width) {
+  if (dir < 0 || dir > 15 || height < 1 || width < 1) return -1;
+  return mpl::make_geom(dir, height, width).n_chains;
+}
+
+int32_t mpl_chain_geometry(int32_t dir, int32_t height, int32_t width, int32_t chain, int32_t* out5) {
+  if (dir < 0 || dir > 15 || height < 1 || width < 1 || !out5) return MPL_ERR_INVALID;
+  const mpl::DirGeom g = mpl::make_geom(dir, height, width);
+  if (chain < 0 || chain >= g.n_chains) return MPL_ERR_INVALID;
+  int h0, w0, len;
+  mpl::chain_start(g, height, width, chain, h0, w0, len);
+  out5[0] = h0;
+  out5[1] = w0;
+  out5[2] = len;
+  out5[3] = g.hs;
+  out5[4] = g.ws;
+  return MPL_OK;
+}
+
+void mpl_profile_enable(int32_t on) { mpl::g_prof_on.store(on ? 1 : 0); }
+
+int32_t mpl_profile_read(int32_t kind, double* total_ms, int64_t* launches) {
+  if (kind < 0 || kind >= mpl::kProfKinds) return MPL_ERR_INVALID;
+  std::lock_guard<std::mutex> lk(mpl::g_prof_mu);
+  for (auto& pr : mpl::g_prof_pending) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(pr.b) == cudaSuccess && cudaEventElapsedTime(&ms, pr.a, pr.b) == cudaSuccess) {
+      mpl::g_prof_ms[pr.kind] += ms;
+      mpl::g_prof_n[pr.kind] += 1;
+    }
+    cudaEventDestroy(pr.a);
+    cudaEventDestroy(pr.b);
+  }
+  mpl::g_prof_pending.clear();
+  if (total_ms) *total_ms = mpl::g_prof_ms[kind];
+  if (launches) *launches = mpl::g_prof_n[kind];
+  return MPL_OK;
+}
+
+void mpl_profile_reset(void) {
+  mpl_profile_read(0, nullptr, nullptr);
+  std::lock_guard<std::mutex> lk(mpl::g_prof_mu);
+  for (int k = 0; k < mpl::kProfKinds; ++k) {
+    mpl::g_prof_ms[k] = 0.0;
+    mpl::g_prof_n[k] = 0;
+  }
+}
+
+}  // extern "C"

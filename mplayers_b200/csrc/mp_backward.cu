@@ -1,0 +1,429 @@
+// Backward kernels of the TRWP / ISGMR layers for sm_100a.
+//
+// One backward sweep replays one direction's chains in reverse from the saved argmin indices.
+// The reference does it as a chain kernel with four global atomicAdds per label per step
+// (MPLayers/TRWP/TRWP_backward.cu:49-275), an elementwise UpdateUnaryKernelBack with D+3 more
+// atomics per element (:26-47) and two memsets (:421-422).  Here the whole sweep is one kernel:
+//   * the scatter "dUU[front, idx[c]] += t[c]" never leaves the chip: it is evaluated as a gather
+//     over the labels of the same pixel (fixed order, so the result is run-to-run identical) and
+//     carried to the predecessor pixel in a register;
+//   * the elementwise update of the predecessor's gradients is applied on the fly with
+//     fire-and-forget reductions (each address is touched once per sweep);
+//   * the label-context gradient is accumulated in a per-chain table in shared memory (row c is
+//     private to thread c) and flushed once per chain into per-slot partial tables, which a final
+//     kernel sums in a fixed order;
+//   * the two per-pixel sums (normalisation backward, edge-weight gradient) share one reduction.
+#include "mp_common.cuh"
+
+namespace mpl {
+
+namespace {
+
+constexpr int kPFB = 8;  // pixels of dM_d staged ahead (power of two)
+
+struct BChain {
+  int img, h0, w0, len, pstep;
+};
+
+__device__ __forceinline__ bool decode_bchain(const BwdParams& p, int g, BChain& c) {
+  const DirGeom geo = make_geom(p.dir, p.H, p.W);
+  if (g >= geo.n_chains * p.nimg) return false;
+  c.img = g / geo.n_chains;
+  chain_start(geo, p.H, p.W, g - c.img * geo.n_chains, c.h0, c.w0, c.len);
+  c.pstep = geo.hs * p.W + geo.ws;
+  return true;
+}
+
+__device__ __forceinline__ void warp_sum2(float& a, float& b) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// L <= 32: one warp per chain, lane = label.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) bwd_warp_kernel(const __grid_constant__ BwdParams p) {
+  extern __shared__ __align__(16) float smem[];
+  const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = blockIdx.x * wpb + warp;
+  BChain ch;
+  if (!decode_bchain(p, g, ch)) return;
+  const int L = p.L, D = p.D, dir = p.dir, inv = dir ^ 1;
+  const int LS = L | 1;                       // odd row stride: bank-conflict-free private rows
+  const int tab = p.ctx_rank == 2 ? L * LS : 32;
+  const int per_warp = kPFB * 32 + 2 * 32 + 2 * 32 + ((tab + 3) & ~3);
+  float* ring = smem + warp * per_warp;       // [kPFB][32]  dM_d of upcoming pixels
+  float* ts = ring + kPFB * 32;               // [2][32]
+  int* is = reinterpret_cast<int*>(ts + 64);  // [2][32]
+  float* acc = ts + 128;                      // context-gradient table
+  const bool act = lane < L;
+  for (int i = lane; i < tab; i += 32) acc[i] = 0.f;
+  is[lane] = -1;
+  is[32 + lane] = -1;
+  __syncwarp();
+
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  float* DMr = p.dm_read + (long long)dir * p.slice + ibase * L;
+  float* DMa = p.dm_acc + ibase * L;
+  float* DU = p.dunary + ibase * L;
+  const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
+  float* DE = p.dew ? p.dew + ibase : nullptr;
+  const uint8_t* MI = p.min_idx + ibase * L;
+  const uint8_t* NI = p.norm_idx + ibase;
+  const int len = ch.len;
+  const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * ch.pstep;  // last pixel of the chain
+  const float rho = p.rho;
+
+  // step s visits chain pixel j = len-1-s, at image pixel pixl - s*pstep
+  auto issue = [&](int s) {
+    if (s < len - 1 && act)  // the chain start (s == len-1) has no incoming message gradient to read
+      cp_async4(ring + (s & (kPFB - 1)) * 32 + lane, DMr + (long long)(pixl - s * ch.pstep) * L + lane);
+    cp_async_commit();
+  };
+  auto load_idx = [&](int s) -> int {
+    return (s < len - 1 && act) ? (int)MI[(long long)(pixl - s * ch.pstep) * L + lane] : -1;
+  };
+  // per-pixel scalars of a block of 32 steps: lane l holds those of step 32*b + l
+  auto load_blk = [&](int b, float& eb, int& nb) {
+    const int s = 32 * b + lane;
+    eb = 1.f;
+    nb = 0;
+    if (s < len - 1) {
+      const int px = pixl - s * ch.pstep;
+      if (E) eb = E[px];
+      nb = NI[px];
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < kPFB; ++s) issue(s);
+  int i0 = load_idx(0), i1 = load_idx(1), i2 = load_idx(2), i3 = load_idx(3);
+  float e_cur, e_nxt;
+  int n_cur, n_nxt;
+  load_blk(0, e_cur, n_cur);
+  load_blk(1, e_nxt, n_nxt);
+
+  float q = 0.f;  // lane f: sum of t[c] of the successor pixel over labels c whose argmin was f
+  for (int s = 0; s < len; ++s) {
+    if ((s & 31) == 0 && s) {
+      e_cur = e_nxt;
+      n_cur = n_nxt;
+      load_blk((s >> 5) + 1, e_nxt, n_nxt);
+    }
+    cp_async_wait<kPFB - 1>();
+    const int px = pixl - s * ch.pstep;
+    const long long o = (long long)px * L + lane;
+    const bool has_front = s < len - 1;
+    const float rq = rho * q;
+    float qn = 0.f;
+    if (has_front) {
+      const float e = __shfl_sync(0xffffffffu, e_cur, s & 31);
+      const int n = __shfl_sync(0xffffffffu, n_cur, s & 31);
+      const int f = i0;
+      const float t0 = act ? ring[(s & (kPFB - 1)) * 32 + lane] + rq : 0.f;
+      const float cv = act ? ctx_value(p.ctx, p.ctx_rank, L, lane, f) : 0.f;
+      float S = t0, P = cv * t0;
+      warp_sum2(S, P);
+      const float cn = __shfl_sync(0xffffffffu, cv, n);
+      const float t = (lane == n) ? t0 - S : t0;  // MPLayers/commonCUDA.cuh:131-145
+      if (DE && lane == 0) atomicAdd(DE + px, P - cn * S);
+      if (act && (lane != f || p.keep_diag)) {
+        if (p.ctx_rank == 2) {
+          acc[lane * LS + f] += e * t;
+        } else {
+          atomicAdd(acc + (lane > f ? lane - f : f - lane), e * t);
+        }
+      }
+      float* tb = ts + (s & 1) * 32;
+      int* ib = is + (s & 1) * 32;
+      tb[lane] = t;
+      if (act) ib[lane] = f;
+      __syncwarp();
+      for (int c = 0; c < L; ++c)
+        if (ib[c] == lane) qn += tb[c];
+    }
+    if (act) {
+      // UpdateUnaryKernelBack (MPLayers/TRWP/TRWP_backward.cu:26-47) applied to this pixel
+      for (int k = 0; k < D; ++k) {
+        if (k == dir) continue;
+        atomicAdd(DMa + k * p.slice + o, k == inv ? fmaf(rho, q, -q) : rq);
+      }
+      atomicAdd(DU + o, rq);
+      DMr[o] = 0.f;
+    }
+    issue(s + kPFB);
+    i0 = i1;
+    i1 = i2;
+    i2 = i3;
+    i3 = load_idx(s + 4);
+    q = qn;
+  }
+  cp_async_wait<0>();
+
+  // flush the context-gradient table of this chain
+  __syncwarp();
+  float* part = p.dctx_part + (long long)(g % p.n_slots) * (p.ctx_rank == 2 ? L * L : L);
+  if (p.ctx_rank == 2) {
+    for (int i = lane; i < L * L; i += 32) {
+      const float v = acc[(i / L) * LS + (i % L)];
+      if (v != 0.f) atomicAdd(part + i, v);
+    }
+  } else if (act) {
+    const float v = acc[lane];
+    if (v != 0.f) atomicAdd(part + lane, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// L > 32: one CTA per chain, thread = label.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) bwd_cta_kernel(const __grid_constant__ BwdParams p) {
+  extern __shared__ __align__(16) float smem[];
+  BChain ch;
+  if (!decode_bchain(p, blockIdx.x, ch)) return;  // uniform
+  const int L = p.L, D = p.D, dir = p.dir, inv = dir ^ 1, NT = blockDim.x, c = threadIdx.x;
+  const int nw = NT >> 5, lane = c & 31, warp = c >> 5;
+  const int LS = L | 1;
+  float* ring = smem;                          // [kPFB][NT]
+  float* ts = ring + kPFB * NT;                // [2][NT]
+  int* is = reinterpret_cast<int*>(ts + 2 * NT);  // [2][NT]
+  float* red = ts + 4 * NT;                    // [2][16] partial sums, [32..33] cv of the norm label
+  float* acc = red + 40;                       // table (rank 2 in smem: L*LS, rank 1: L)
+  const bool act = c < L;
+  const int tab = p.ctx_rank == 2 ? (p.table_in_smem ? L * LS : 0) : L;
+  for (int i = c; i < tab; i += NT) acc[i] = 0.f;
+  is[c] = -1;
+  is[NT + c] = -1;
+  __syncthreads();
+
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  float* DMr = p.dm_read + (long long)dir * p.slice + ibase * L;
+  float* DMa = p.dm_acc + ibase * L;
+  float* DU = p.dunary + ibase * L;
+  const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
+  float* DE = p.dew ? p.dew + ibase : nullptr;
+  const uint8_t* MI = p.min_idx + ibase * L;
+  const uint8_t* NI = p.norm_idx + ibase;
+  const int len = ch.len;
+  const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * ch.pstep;
+  const float rho = p.rho;
+  float* part = p.dctx_part + (long long)(blockIdx.x % p.n_slots) * (p.ctx_rank == 2 ? L * L : L);
+
+  auto issue = [&](int s) {
+    if (s < len - 1 && act)
+      cp_async4(ring + (s & (kPFB - 1)) * NT + c, DMr + (long long)(pixl - s * ch.pstep) * L + c);
+    cp_async_commit();
+  };
+  auto load_idx = [&](int s) -> int {
+    return (s < len - 1 && act) ? (int)MI[(long long)(pixl - s * ch.pstep) * L + c] : -1;
+  };
+  auto load_blk = [&](int b, float& eb, int& nb) {
+    const int s = 32 * b + lane;
+    eb = 1.f;
+    nb = 0;
+    if (s < len - 1) {
+      const int px = pixl - s * ch.pstep;
+      if (E) eb = E[px];
+      nb = NI[px];
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < kPFB; ++s) issue(s);
+  int i0 = load_idx(0), i1 = load_idx(1), i2 = load_idx(2), i3 = load_idx(3);
+  float e_cur, e_nxt;
+  int n_cur, n_nxt;
+  load_blk(0, e_cur, n_cur);
+  load_blk(1, e_nxt, n_nxt);
+
+  float q = 0.f;
+  for (int s = 0; s < len; ++s) {
+    if ((s & 31) == 0 && s) {
+      e_cur = e_nxt;
+      n_cur = n_nxt;
+      load_blk((s >> 5) + 1, e_nxt, n_nxt);
+    }
+    cp_async_wait<kPFB - 1>();
+    const int px = pixl - s * ch.pstep;
+    const long long o = (long long)px * L + c;
+    const bool has_front = s < len - 1;
+    const float rq = rho * q;
+    float qn = 0.f;
+    if (has_front) {
+      const float e = __shfl_sync(0xffffffffu, e_cur, s & 31);
+      const int n = __shfl_sync(0xffffffffu, n_cur, s & 31);
+      const int f = i0;
+      const float t0 = act ? ring[(s & (kPFB - 1)) * NT + c] + rq : 0.f;
+      const float cv = act ? ctx_value(p.ctx, p.ctx_rank, L, c, f) : 0.f;
+      float S = t0, P = cv * t0;
+      warp_sum2(S, P);
+      float* rb = red + (s & 1) * 16;
+      if (lane == 0) {
+        rb[warp] = S;
+        rb[8 + warp] = P;
+      }
+      if (c == n) red[32 + (s & 1)] = cv;
+      __syncthreads();
+      S = 0.f;
+      P = 0.f;
+      for (int w = 0; w < nw; ++w) {
+        S += rb[w];
+        P += rb[8 + w];
+      }
+      const float cn = red[32 + (s & 1)];
+      const float t = (c == n) ? t0 - S : t0;
+      if (DE && c == 0) atomicAdd(DE + px, P - cn * S);
+      if (act && (c != f || p.keep_diag)) {
+        if (p.ctx_rank == 2) {
+          if (p.table_in_smem) {
+            acc[c * LS + f] += e * t;
+          } else {
+            atomicAdd(part + c * L + f, e * t);
+          }
+        } else {
+          atomicAdd(acc + (c > f ? c - f : f - c), e * t);
+        }
+      }
+      float* tb = ts + (s & 1) * NT;
+      int* ib = is + (s & 1) * NT;
+      tb[c] = t;
+      if (act) ib[c] = f;
+      __syncthreads();
+      for (int k = 0; k < L; ++k)
+        if (ib[k] == c) qn += tb[k];
+    }
+    if (act) {
+      for (int k = 0; k < D; ++k) {
+        if (k == dir) continue;
+        atomicAdd(DMa + k * p.slice + o, k == inv ? fmaf(rho, q, -q) : rq);
+      }
+      atomicAdd(DU + o, rq);
+      DMr[o] = 0.f;
+    }
+    issue(s + kPFB);
+    i0 = i1;
+    i1 = i2;
+    i2 = i3;
+    i3 = load_idx(s + 4);
+    q = qn;
+  }
+  cp_async_wait<0>();
+
+  __syncthreads();
+  if (p.ctx_rank == 2) {
+    if (p.table_in_smem)
+      for (int i = c; i < L * L; i += NT) {
+        const float v = acc[(i / L) * LS + (i % L)];
+        if (v != 0.f) atomicAdd(part + i, v);
+      }
+  } else if (act) {
+    const float v = acc[c];
+    if (v != 0.f) atomicAdd(part + c, v);
+  }
+}
+
+// dunary = factor * g, dM_k = g for every k.  MPLayers/TRWP/TRWP_backward.cu:8-24,
+// MPLayers/ISGMR/ISGMR_backward.cu:18-37.
+__global__ void backward_init_kernel(const float* __restrict__ g, float* __restrict__ dunary,
+                                     float* __restrict__ dm, long long n, int D, float factor) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = g[i];
+    dunary[i] = factor * v;
+    for (int k = 0; k < D; ++k) dm[k * n + i] = v;
+  }
+}
+
+// Sums the per-slot partial tables in slot order and folds them into the caller's dcontext with
+// the reference's addressing (MPLayers/TRWP/TRWP_backward.cu:102-112): rank 2 -> cell
+// [min(c,f)][max(c,f)], rank 1 -> cell |c-f|.
+__global__ void dctx_reduce_kernel(const float* __restrict__ part, int n_slots, int L, int rank,
+                                   float* __restrict__ dctx) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int CT = rank == 2 ? L * L : L;
+  if (i >= CT) return;
+  if (rank == 2) {
+    const int a = i / L, b = i % L;
+    if (a > b) return;
+    float s = 0.f;
+    if (a == b) {
+      for (int k = 0; k < n_slots; ++k) s += part[(long long)k * CT + i];
+    } else {
+      const int j = b * L + a;
+      for (int k = 0; k < n_slots; ++k) s += part[(long long)k * CT + i] + part[(long long)k * CT + j];
+    }
+    dctx[i] += s;
+  } else {
+    float s = 0.f;
+    for (int k = 0; k < n_slots; ++k) s += part[(long long)k * CT + i];
+    dctx[i] += s;
+  }
+}
+
+constexpr int kSmemTableMaxL = 128;  // rank-2 table L*(L|1) floats fits next to the staging ring
+
+}  // namespace
+
+int backward_slots(int H, int W, int L, int D, int nimg) {
+  long long mx = 1;
+  for (int d = 0; d < D; ++d) {
+    const long long n = (long long)make_geom(d, H, W).n_chains * nimg;
+    if (n > mx) mx = n;
+  }
+  if (mx > 4096) mx = 4096;
+  return (int)mx;
+}
+
+cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,
+                                 float factor, cudaStream_t st) {
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  ProfScope prof(kProfElementwise, st);
+  backward_init_kernel<<<(int)blocks, 256, 0, st>>>(dcost, dunary, dm, n, D, factor);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
+  BwdParams p = p0;
+  const int total = make_geom(p.dir, p.H, p.W).n_chains * p.nimg;
+  if (total == 0) return cudaSuccess;
+  const int L = p.L, LS = L | 1;
+  ProfScope prof(kProfBwdSweep, st);
+  if (L <= 32) {
+    const int wpb = total >= 148 * 32 ? 4 : 1;
+    const int tab = p.ctx_rank == 2 ? L * LS : 32;
+    const size_t smem = (size_t)wpb * (kPFB * 32 + 128 + ((tab + 3) & ~3)) * sizeof(float);
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(bwd_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    bwd_warp_kernel<<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+  } else {
+    const int NT = ((L + 31) / 32) * 32;
+    p.table_in_smem = (p.ctx_rank == 2 && L <= kSmemTableMaxL) ? 1 : 0;
+    const int tab = p.ctx_rank == 2 ? (p.table_in_smem ? L * LS : 0) : L;
+    const size_t smem = ((size_t)kPFB * NT + 4 * NT + 40 + tab + 4) * sizeof(float);
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(bwd_cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    bwd_cta_kernel<<<total, NT, smem, st>>>(p);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dctx_reduce(const float* part, int n_slots, int L, int rank, int keep_diag,
+                               float* dctx, cudaStream_t st) {
+  (void)keep_diag;  // the diagonal is filtered where the table is accumulated
+  const int CT = rank == 2 ? L * L : L;
+  dctx_reduce_kernel<<<(CT + 127) / 128, 128, 0, st>>>(part, n_slots, L, rank, dctx);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace mpl

@@ -1,0 +1,185 @@
+// Shared device/host helpers of the TRWP / ISGMR kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mpl {
+
+// Direction table, identical to the reference's (MPLayers/common.cpp:28-76): step of direction d;
+// a message in direction d at pixel `cur` comes from `front = cur - step`; dir_inv = d ^ 1.
+namespace detail {
+constexpr int kHs[16] = {0, 0, 1, -1, 1, -1, 1, -1, 1, -1, 2, -2, 2, -2, 1, -1};
+constexpr int kWs[16] = {1, -1, 0, 0, 1, -1, -1, 1, 2, -2, 1, -1, -1, 1, -2, 2};
+constexpr unsigned long long pack16(const int* v) {
+  unsigned long long r = 0;
+  for (int i = 0; i < 16; ++i) r |= (unsigned long long)(v[i] + 2) << (4 * i);
+  return r;
+}
+constexpr unsigned long long kHsPacked = pack16(kHs), kWsPacked = pack16(kWs);
+}  // namespace detail
+
+__host__ __device__ inline void dir_step(int dir, int& hs, int& ws) {
+  hs = (int)((detail::kHsPacked >> (4 * dir)) & 15) - 2;  // nibble table: no local-memory array
+  ws = (int)((detail::kWsPacked >> (4 * dir)) & 15) - 2;
+}
+
+// Chains of one direction inside one image.  A chain starts at every pixel whose `front` lies
+// outside the image and follows +step until it leaves the image, so every pixel belongs to exactly
+// one chain per direction.  (The reference enumerates "trees" and skips out-of-image steps,
+// MPLayers/TRWP/TRWP_forward.cu:201-218,310-312; the visited pixel sequences are the same.)
+struct DirGeom {
+  int hs, ws;     // step
+  int ah, aw;     // min(|hs|, H), min(|ws|, W)
+  int n_first;    // chains starting in the first ah rows (all columns)
+  int n_chains;   // chains per image
+};
+
+__host__ __device__ inline DirGeom make_geom(int dir, int H, int W) {
+  DirGeom g;
+  dir_step(dir, g.hs, g.ws);
+  const int ahs = g.hs < 0 ? -g.hs : g.hs, aws = g.ws < 0 ? -g.ws : g.ws;
+  g.ah = ahs < H ? ahs : H;
+  g.aw = aws < W ? aws : W;
+  g.n_first = g.ah * W;
+  g.n_chains = g.n_first + (H - g.ah) * g.aw;
+  return g;
+}
+
+// Start pixel (h0, w0) and number of pixels `len` of chain t (0 <= t < n_chains).
+__host__ __device__ inline void chain_start(const DirGeom& g, int H, int W, int t, int& h0, int& w0,
+                                            int& len) {
+  if (t < g.n_first) {
+    const int rr = t / W;
+    h0 = g.hs > 0 ? rr : H - 1 - rr;
+    w0 = t - rr * W;
+  } else {
+    const int t2 = t - g.n_first;
+    const int rr = g.ah + t2 / g.aw;
+    const int ci = t2 - (t2 / g.aw) * g.aw;
+    h0 = g.hs < 0 ? H - 1 - rr : rr;
+    w0 = g.ws > 0 ? ci : W - 1 - ci;
+  }
+  int nh = 0x7fffffff, nw = 0x7fffffff;
+  if (g.hs > 0) nh = (H - 1 - h0) / g.hs;
+  if (g.hs < 0) nh = h0 / (-g.hs);
+  if (g.ws > 0) nw = (W - 1 - w0) / g.ws;
+  if (g.ws < 0) nw = w0 / (-g.ws);
+  len = 1 + (nh < nw ? nh : nw);
+}
+
+// What the device learned about a rank-1 context and the edge weights (written by
+// analyze kernels, read by the sweep kernels; lives in the caller's workspace).
+struct CtxInfo {
+  int windowed;   // 1: ctx[k] <= ctx[L-1] for k < R, ctx[k] == ctx[L-1] for k >= R, and 2R-1 < L
+  int R;          // first offset at which ctx has reached its final value
+  float cmax;     // ctx[L-1]
+  int ew_min_bits;  // order-preserving int image of min(edge weight)
+};
+
+struct FwdParams {
+  const float* unary;     // [nimg,H,W,L]
+  const float* msg_read;  // [D,nimg,H,W,L] messages entering UU
+  float* msg_write;       // [D,nimg,H,W,L] slice `dir` receives the new messages
+  const float* ctx;
+  const float* ew;        // [D,nimg,H,W] or nullptr (= 1)
+  uint8_t* min_idx;       // [D,nimg,H,W,L] of this iteration, or nullptr
+  uint8_t* norm_idx;      // [D,nimg,H,W]
+  const CtxInfo* info;
+  int H, W, L, D, nimg;
+  long long slice;        // nimg*H*W*L
+  long long pslice;       // nimg*H*W
+  float rho;
+  int ctx_rank;
+  int dir0, ndirs;        // this launch covers directions dir0 .. dir0+ndirs-1
+  int chain_off[17];      // prefix sums of nimg*n_chains over those directions
+};
+
+struct BwdParams {
+  const float* ctx;
+  const float* ew;        // or nullptr (= 1)
+  const uint8_t* min_idx; // slice [nimg,H,W,L] of (iter, dir)
+  const uint8_t* norm_idx;
+  float* dm_read;         // [D,...]: slice `dir` holds the gradient of this sweep's messages; zeroed here
+  float* dm_acc;          // [D,...]: gradient of the messages the sweep read (TRWP: == dm_read)
+  float* dunary;
+  float* dew;             // slice of `dir`, or nullptr
+  float* dctx_part;       // [n_slots, ctx_table] partial tables
+  int n_slots;
+  int H, W, L, D, nimg;
+  long long slice, pslice;
+  float rho;
+  int ctx_rank, keep_diag;
+  int dir;
+  int table_in_smem;      // CTA kernel: 1 = [L][L|1] table in shared memory
+};
+
+__device__ __forceinline__ float ctx_value(const float* ctx, int rank, int L, int c, int f) {
+  if (rank == 2) {
+    const int a = c < f ? c : f, b = c < f ? f : c;
+    return __ldg(ctx + a * L + b);
+  }
+  const int k = c - f;
+  return __ldg(ctx + (k < 0 ? -k : k));
+}
+
+// Warp-wide float min in one instruction (sm_100a).
+__device__ __forceinline__ float warp_min(float v) {
+  float m;
+  asm volatile("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(m) : "f"(v));
+  return m;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* gmem_src) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ int float_order_bits(float x) {
+  const int b = __float_as_int(x);
+  return b >= 0 ? b : b ^ 0x7fffffff;
+}
+__device__ __forceinline__ float float_from_order_bits(int b) {
+  return __int_as_float(b >= 0 ? b : b ^ 0x7fffffff);
+}
+
+constexpr float kInf = __builtin_huge_valf();
+
+// Host-side launchers (mp_forward.cu / mp_backward.cu).  Return cudaGetLastError() of the launch.
+cudaError_t launch_analyze(const float* ctx, int L, int rank, const float* ew, long long n_ew,
+                           CtxInfo* info, cudaStream_t st);
+cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st);
+cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, uint8_t* label,
+                             long long npix, int L, int D, long long slice, float factor,
+                             int min_a_dir, cudaStream_t st);
+cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,
+                                 float factor, cudaStream_t st);
+cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
+cudaError_t launch_dctx_reduce(const float* part, int n_slots, int L, int rank, int keep_diag,
+                               float* dctx, cudaStream_t st);
+int backward_slots(int H, int W, int L, int D, int nimg);
+void count_launch(int n = 1);
+
+// Optional per-launch timing (mpl_profile_enable): CUDA events recorded on the launching stream
+// directly before and after a kernel launch, summed per kernel kind when read.
+enum ProfKind { kProfFwdSweep = 0, kProfBwdSweep = 1, kProfElementwise = 2, kProfKinds = 3 };
+struct ProfScope {
+  ProfScope(int kind, cudaStream_t st);
+  ~ProfScope();
+  int kind_;
+  cudaStream_t st_;
+  cudaEvent_t a_, b_;
+  bool on_;
+};
+
+}  // namespace mpl
