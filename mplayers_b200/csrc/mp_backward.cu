@@ -43,123 +43,193 @@ __device__ __forceinline__ void warp_sum2(float& a, float& b) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// L <= 32: one warp per chain, lane = label.
+// L <= 32: one warp per chain, lane = label.  DT = compile-time direction count (0: from params).
+//
+// The chain is walked in blocks of 32 steps.  The message gradients of a whole block are staged
+// in shared memory one block ahead (cp.async), which lets lane j compute the per-pixel scalars of
+// step 32*b + j for the whole block at once -- the normalisation sum, the edge weight, the
+// normalisation index, and afterwards the edge-weight gradient -- instead of one warp reduction
+// per step.  The sum the normalisation backward needs is taken over the staged gradient alone:
+// the part carried from the successor pixel sums to zero (it is itself the output of a
+// normalisation backward), so only rounding noise is dropped.
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) bwd_warp_kernel(const __grid_constant__ BwdParams p) {
+constexpr int kRB = 64;  // ring rows: two blocks of 32 steps
+constexpr int kRS = 33;  // padded row stride (conflict-free both along and across rows)
+
+__host__ __device__ inline int bwd_warp_floats(int L, int rank) {
+  const int tab = rank == 2 ? L * (L | 1) : 32;
+  return kRB * kRS + 32 * kRS + 128 + ((tab + 3) & ~3);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = p.L, D = DT ? DT : p.D, dir = p.dir, inv = dir ^ 1;
+  const int LS = L | 1;  // odd row stride: private rows without bank conflicts
+  // full (symmetric / Toeplitz) context table shared by the CTA
+  float* ctab = smem;
+  const int ctab_floats = (L * LS + 3) & ~3;
+  for (int i = threadIdx.x; i < L * L; i += blockDim.x)
+    ctab[(i / L) * LS + (i % L)] = ctx_value(p.ctx, p.ctx_rank, L, i / L, i % L);
+  __syncthreads();
   const int g = blockIdx.x * wpb + warp;
   BChain ch;
   if (!decode_bchain(p, g, ch)) return;
-  const int L = p.L, D = p.D, dir = p.dir, inv = dir ^ 1;
-  const int LS = L | 1;                       // odd row stride: bank-conflict-free private rows
   const int tab = p.ctx_rank == 2 ? L * LS : 32;
-  const int per_warp = kPFB * 32 + 2 * 32 + 2 * 32 + ((tab + 3) & ~3);
-  float* ring = smem + warp * per_warp;       // [kPFB][32]  dM_d of upcoming pixels
-  float* ts = ring + kPFB * 32;               // [2][32]
-  int* is = reinterpret_cast<int*>(ts + 64);  // [2][32]
-  float* acc = ts + 128;                      // context-gradient table
+  float* ring = smem + ctab_floats + warp * bwd_warp_floats(L, p.ctx_rank);  // [kRB][kRS]
+  float* dtile = ring + kRB * kRS;                                          // [32][kRS]
+  float* ts = dtile + 32 * kRS;                                             // [2][32]
+  int* is = reinterpret_cast<int*>(ts + 64);                                // [2][32]
+  float* acc = ts + 128;                                                    // context-gradient table
   const bool act = lane < L;
   for (int i = lane; i < tab; i += 32) acc[i] = 0.f;
   is[lane] = -1;
   is[32 + lane] = -1;
-  __syncwarp();
 
   const long long ibase = (long long)ch.img * p.H * p.W;
-  float* DMr = p.dm_read + (long long)dir * p.slice + ibase * L;
-  float* DMa = p.dm_acc + ibase * L;
-  float* DU = p.dunary + ibase * L;
+  float* DMrl = p.dm_read + (long long)dir * p.slice + ibase * L + lane;
+  float* DMal = p.dm_acc + ibase * L + lane;
+  float* DUl = p.dunary + ibase * L + lane;
   const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
   float* DE = p.dew ? p.dew + ibase : nullptr;
-  const uint8_t* MI = p.min_idx + ibase * L;
+  const uint8_t* MIl = p.min_idx + ibase * L + lane;
   const uint8_t* NI = p.norm_idx + ibase;
   const int len = ch.len;
-  const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * ch.pstep;  // last pixel of the chain
+  const int pstep = ch.pstep, ostep = ch.pstep * L;
+  const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * pstep;  // last pixel of the chain
   const float rho = p.rho;
+  const float rinv = rho - 1.f;  // dM_inv += rho*q - q
+  const int nsteps = len - 1;    // steps with a predecessor pixel (s = 0 .. len-2)
 
-  // step s visits chain pixel j = len-1-s, at image pixel pixl - s*pstep
-  auto issue = [&](int s) {
-    if (s < len - 1 && act)  // the chain start (s == len-1) has no incoming message gradient to read
-      cp_async4(ring + (s & (kPFB - 1)) * 32 + lane, DMr + (long long)(pixl - s * ch.pstep) * L + lane);
+  // step s visits chain pixel len-1-s at image pixel pixl - s*pstep
+  auto stage_block = [&](int b) {  // dM_d of the 32 steps of block b -> ring rows (32*b .. ) & 63
+    if (act) {
+      int s = 32 * b;
+      int o = (pixl - s * pstep) * L;
+      float* dst = ring + (s & (kRB - 1)) * kRS + lane;
+#pragma unroll 8
+      for (int u = 0; u < 32; ++u) {
+        if (s + u < nsteps) cp_async4(dst + u * kRS, DMrl + o);
+        o -= ostep;
+      }
+    }
     cp_async_commit();
   };
-  auto load_idx = [&](int s) -> int {
-    return (s < len - 1 && act) ? (int)MI[(long long)(pixl - s * ch.pstep) * L + lane] : -1;
-  };
-  // per-pixel scalars of a block of 32 steps: lane l holds those of step 32*b + l
-  auto load_blk = [&](int b, float& eb, int& nb) {
+  auto load_blk = [&](int b, float& eb, int& nb) {  // lane l: scalars of step 32*b + l
     const int s = 32 * b + lane;
     eb = 1.f;
     nb = 0;
-    if (s < len - 1) {
-      const int px = pixl - s * ch.pstep;
+    if (s < nsteps) {
+      const int px = pixl - s * pstep;
       if (E) eb = E[px];
       nb = NI[px];
     }
   };
 
-#pragma unroll
-  for (int s = 0; s < kPFB; ++s) issue(s);
-  int i0 = load_idx(0), i1 = load_idx(1), i2 = load_idx(2), i3 = load_idx(3);
+  stage_block(0);
   float e_cur, e_nxt;
   int n_cur, n_nxt;
   load_blk(0, e_cur, n_cur);
-  load_blk(1, e_nxt, n_nxt);
+  int fa[8], fb[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) fa[u] = (u < nsteps && act) ? (int)MIl[(pixl - u * pstep) * L] : -1;
 
   float q = 0.f;  // lane f: sum of t[c] of the successor pixel over labels c whose argmin was f
-  for (int s = 0; s < len; ++s) {
-    if ((s & 31) == 0 && s) {
-      e_cur = e_nxt;
-      n_cur = n_nxt;
-      load_blk((s >> 5) + 1, e_nxt, n_nxt);
+  int of = pixl * L;
+  const int nblocks = (len + 31) >> 5;
+  for (int b = 0; b < nblocks; ++b) {
+    stage_block(b + 1);
+    load_blk(b + 1, e_nxt, n_nxt);
+    cp_async_wait<1>();
+    __syncwarp();
+    // normalisation sums of this block: lane j sums row j of the staged gradients
+    float s_cur = 0.f;
+    {
+      const float* row = ring + ((32 * b + lane) & (kRB - 1)) * kRS;
+      for (int c = 0; c < L; ++c) s_cur += row[c];
     }
-    cp_async_wait<kPFB - 1>();
-    const int px = pixl - s * ch.pstep;
-    const long long o = (long long)px * L + lane;
-    const bool has_front = s < len - 1;
-    const float rq = rho * q;
-    float qn = 0.f;
-    if (has_front) {
-      const float e = __shfl_sync(0xffffffffu, e_cur, s & 31);
-      const int n = __shfl_sync(0xffffffffu, n_cur, s & 31);
-      const int f = i0;
-      const float t0 = act ? ring[(s & (kPFB - 1)) * 32 + lane] + rq : 0.f;
-      const float cv = act ? ctx_value(p.ctx, p.ctx_rank, L, lane, f) : 0.f;
-      float S = t0, P = cv * t0;
-      warp_sum2(S, P);
-      const float cn = __shfl_sync(0xffffffffu, cv, n);
-      const float t = (lane == n) ? t0 - S : t0;  // MPLayers/commonCUDA.cuh:131-145
-      if (DE && lane == 0) atomicAdd(DE + px, P - cn * S);
-      if (act && (lane != f || p.keep_diag)) {
-        if (p.ctx_rank == 2) {
-          acc[lane * LS + f] += e * t;
-        } else {
-          atomicAdd(acc + (lane > f ? lane - f : f - lane), e * t);
+    for (int g8 = 0; g8 < 4; ++g8) {
+      const int s0 = 32 * b + 8 * g8;
+      if (s0 >= len) break;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {  // argmin indices of the next group of 8 steps
+        const int s = s0 + 8 + u;
+        fb[u] = (s < nsteps && act) ? (int)MIl[(pixl - s * pstep) * L] : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int s = s0 + u;
+        if (s < len) {
+          const float rq = rho * q;
+          float qn = 0.f;
+          if (s < nsteps) {
+            const int sl = s & 31;
+            const float e = __shfl_sync(0xffffffffu, e_cur, sl);
+            const int n = __shfl_sync(0xffffffffu, n_cur, sl);
+            const float S = __shfl_sync(0xffffffffu, s_cur, sl);
+            const int f = fa[u];
+            const float x = ring[(s & (kRB - 1)) * kRS + lane];
+            const float t0 = act ? x + rq : 0.f;
+            const float t = (lane == n) ? t0 - S : t0;  // MPLayers/commonCUDA.cuh:131-145
+            float cv = 0.f;
+            if (act) {
+              cv = ctab[lane * LS + f];
+              if (lane != f || p.keep_diag) {
+                if (p.ctx_rank == 2) {
+                  acc[lane * LS + f] += e * t;
+                } else {
+                  atomicAdd(acc + (lane > f ? lane - f : f - lane), e * t);
+                }
+              }
+            }
+            dtile[sl * kRS + lane] = cv * t;
+            float* tb = ts + (s & 1) * 32;
+            int* ib = is + (s & 1) * 32;
+            tb[lane] = t;
+            if (act) ib[lane] = f;
+            __syncwarp();
+            float q0 = 0.f, q1 = 0.f, q2 = 0.f;
+            int c = 0;
+            for (; c + 2 < L; c += 3) {
+              if (ib[c] == lane) q0 += tb[c];
+              if (ib[c + 1] == lane) q1 += tb[c + 1];
+              if (ib[c + 2] == lane) q2 += tb[c + 2];
+            }
+            for (; c < L; ++c)
+              if (ib[c] == lane) q0 += tb[c];
+            qn = (q0 + q1) + q2;
+          }
+          if (act) {
+            // UpdateUnaryKernelBack (MPLayers/TRWP/TRWP_backward.cu:26-47) applied to this pixel
+#pragma unroll
+            for (int k = 0; k < (DT ? DT : 16); ++k) {
+              if (k < D && k != dir) atomicAdd(DMal + k * p.slice + of, k == inv ? rinv * q : rq);
+            }
+            atomicAdd(DUl + of, rq);
+            DMrl[of] = 0.f;
+          }
+          q = qn;
+          of -= ostep;
         }
       }
-      float* tb = ts + (s & 1) * 32;
-      int* ib = is + (s & 1) * 32;
-      tb[lane] = t;
-      if (act) ib[lane] = f;
-      __syncwarp();
-      for (int c = 0; c < L; ++c)
-        if (ib[c] == lane) qn += tb[c];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) fa[u] = fb[u];
     }
-    if (act) {
-      // UpdateUnaryKernelBack (MPLayers/TRWP/TRWP_backward.cu:26-47) applied to this pixel
-      for (int k = 0; k < D; ++k) {
-        if (k == dir) continue;
-        atomicAdd(DMa + k * p.slice + o, k == inv ? fmaf(rho, q, -q) : rq);
+    // edge-weight gradients of this block: lane j sums row j of the product tile
+    __syncwarp();
+    if (DE) {
+      const int s = 32 * b + lane;
+      if (s < nsteps) {
+        const float* row = dtile + lane * kRS;
+        float de = 0.f;
+        for (int c = 0; c < L; ++c) de += row[c];
+        atomicAdd(DE + (pixl - s * pstep), de);
       }
-      atomicAdd(DU + o, rq);
-      DMr[o] = 0.f;
     }
-    issue(s + kPFB);
-    i0 = i1;
-    i1 = i2;
-    i2 = i3;
-    i3 = load_idx(s + 4);
-    q = qn;
+    __syncwarp();
+    e_cur = e_nxt;
+    n_cur = n_nxt;
   }
   cp_async_wait<0>();
 
@@ -395,13 +465,18 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
   ProfScope prof(kProfBwdSweep, st);
   if (L <= 32) {
     const int wpb = total >= 148 * 32 ? 4 : 1;
-    const int tab = p.ctx_rank == 2 ? L * LS : 32;
-    const size_t smem = (size_t)wpb * (kPFB * 32 + 128 + ((tab + 3) & ~3)) * sizeof(float);
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(bwd_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return e;
-    }
-    bwd_warp_kernel<<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+    const size_t smem =
+        ((size_t)((L * LS + 3) & ~3) + (size_t)wpb * bwd_warp_floats(L, p.ctx_rank)) * sizeof(float);
+    auto go = [&](auto kernel) -> cudaError_t {
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+      }
+      kernel<<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+      return cudaSuccess;
+    };
+    cudaError_t e = p.D == 4 ? go(bwd_warp_kernel<4>) : p.D == 8 ? go(bwd_warp_kernel<8>) : go(bwd_warp_kernel<0>);
+    if (e != cudaSuccess) return e;
   } else {
     const int NT = ((L + 31) / 32) * 32;
     p.table_in_smem = (p.ctx_rank == 2 && L <= kSmemTableMaxL) ? 1 : 0;

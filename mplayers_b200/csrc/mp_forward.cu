@@ -50,6 +50,60 @@ __device__ __forceinline__ float uu_from_ring(const float* slot, int rs, int col
   return fmaf(s, rho, -slot[(1 + inv) * rs + col]);
 }
 
+__device__ __forceinline__ float min3f(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));  // 3-input min (sm_100)
+  return d;
+}
+
+// Minimum of N registers with 3-input min instructions: depth ceil(log3 N) instead of the
+// reference's serial scan.
+template <int N>
+__device__ __forceinline__ float min_tree(const float (&v)[N]) {
+  if constexpr (N == 1) {
+    return v[0];
+  } else if constexpr (N == 2) {
+    return fminf(v[0], v[1]);
+  } else if constexpr (N == 3) {
+    return min3f(v[0], v[1], v[2]);
+  } else {
+    constexpr int M = (N + 2) / 3;
+    float t[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) {
+      if (3 * i + 2 < N) {
+        t[i] = min3f(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+      } else if (3 * i + 1 < N) {
+        t[i] = fminf(v[3 * i], v[3 * i + 1]);
+      } else {
+        t[i] = v[3 * i];
+      }
+    }
+    return min_tree<M>(t);
+  }
+}
+
+__device__ __forceinline__ float eq_flag(float a, float b) {
+  float d;
+  asm("set.eq.f32.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));  // 1.0f if a == b else 0.0f
+  return d;
+}
+
+__device__ __forceinline__ constexpr float pow2f(int k) {
+  float r = 1.f;
+  for (int i = 0; i < k; ++i) r *= 2.f;
+  return r;
+}
+
+// Candidates val[f] = e*ctx(c,f) + h[f] for the label c of this thread, their minimum and -- when
+// TRAIN -- the HIGHEST f attaining it (what the reference's high-to-low strict-< scan returns,
+// MPLayers/TRWP/TRWP_forward.cu:126-152).
+//
+// Compare / select / min instructions run at half the rate of fused multiply-adds, so the index is
+// not tracked with a compare-and-select chain.  The exact minimum is taken first (3-input min
+// tree); then every candidate contributes (val[f] == min) * 2^f to a float accumulator with one
+// set + one fma (groups of 24 labels per accumulator, exact in a 24-bit mantissa), and the wanted
+// index is the exponent of the accumulator.
 template <int LMAX, bool TRAIN>
 __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr)[LMAX], float e,
                                                float& best, int& bi) {
@@ -63,95 +117,129 @@ __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr
     hv[4 * q + 2] = t.z;
     hv[4 * q + 3] = t.w;
   }
-  best = fmaf(e, cr[LMAX - 1], hv[LMAX - 1]);
-  bi = LMAX - 1;
+  float val[LMAX];
 #pragma unroll
-  for (int f = LMAX - 2; f >= 0; --f) {
-    const float v = fmaf(e, cr[f], hv[f]);
-    if (TRAIN) {
-      if (v < best) {
-        best = v;
-        bi = f;
+  for (int f = 0; f < LMAX; ++f) val[f] = fmaf(e, cr[f], hv[f]);
+  best = min_tree<LMAX>(val);
+  bi = 0;
+  if (TRAIN) {
+    constexpr int NA = (LMAX + 23) / 24;
+    float acc[NA];
+#pragma unroll
+    for (int a = 0; a < NA; ++a) acc[a] = 0.f;
+#pragma unroll
+    for (int f = 0; f < LMAX; ++f) acc[f / 24] = fmaf(eq_flag(val[f], best), pow2f(f % 24), acc[f / 24]);
+#pragma unroll
+    for (int a = 0; a < NA; ++a) {
+      const int ex = ((__float_as_int(acc[a]) >> 23) & 0xff) - 127 + 24 * a;
+      if (a == 0) {
+        bi = ex;
+      } else {
+        bi = acc[a] != 0.f ? ex : bi;
       }
-    } else {
-      best = fminf(best, v);
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------------
-// L <= 32: one warp per chain.
+// L <= 32: one warp per chain.  DT = compile-time direction count (0: read it from the params).
 // ------------------------------------------------------------------------------------------------
-template <int LMAX, bool TRAIN>
-__global__ void __launch_bounds__(128) fwd_warp_kernel(const __grid_constant__ FwdParams p) {
+// Generic kernel: any direction, any alignment.  Inputs are staged through a ring of 4-byte
+// cp.async copies kPF pixels ahead (a register ring of plain loads was measured slower: waiting on
+// a register load drains every younger load too, whereas cp.async groups retire in order).
+// DT = compile-time direction count (0: read it from the params).
+template <int LMAX, int DT, bool TRAIN>
+__global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   ChainCtx ch;
   if (!decode_chain(p, blockIdx.x * wpb + warp, ch)) return;
-  const int L = p.L, D = p.D, rows = D + 2;
-  float* ring = smem + warp * (kPF * rows * 32 + 64);
-  float* hbuf = ring + kPF * rows * 32;
+  const int L = p.L, D = DT ? DT : p.D, rows = D + 2;
+  const int slot_floats = rows * 32;
+  float* ring = smem + warp * (kPF * slot_floats + 64);
+  float* hbuf = ring + kPF * slot_floats;
+  float* ring_lane = ring + lane;
   const bool act = lane < L;
+  const int lc = act ? lane : L - 1;  // idle lanes shadow the last label: no divergent code below
+  const float rho = p.rho;
 
   float cr[LMAX];
 #pragma unroll
   for (int f = 0; f < LMAX; ++f) cr[f] = (act && f < L) ? ctx_value(p.ctx, p.ctx_rank, L, lane, f) : 0.f;
 
   const long long ibase = (long long)ch.img * p.H * p.W;
-  const float* U = p.unary + ibase * L;
-  const float* Mr = p.msg_read + ibase * L;
-  float* Mw = p.msg_write + (long long)ch.dir * p.slice + ibase * L;
-  const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
-  uint8_t* MI = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L : nullptr;
+  // per-lane base pointers; everything below addresses them with 32-bit element offsets
+  const float* Ul = p.unary + ibase * L + lc;
+  const float* Ml = p.msg_read + ibase * L + lc;
+  float* Mwl = p.msg_write + (long long)ch.dir * p.slice + ibase * L + lc;
+  const bool has_e = p.ew != nullptr;
+  const float* E = has_e ? p.ew + (long long)ch.dir * p.pslice + ibase : p.unary;
+  uint8_t* MIl = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L + lc : nullptr;
   uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
-  const int pix0 = ch.h0 * p.W + ch.w0;
   const int len = ch.len;
+  const int ostep = ch.pstep * L;
+  const int dir_row = (1 + ch.dir) * 32, inv_row = (1 + ch.inv) * 32;
 
+  // Staging of chain pixel j (its unary and D messages, used when it is the predecessor, and its
+  // edge weight, used when it is the current pixel).  Pixels past the chain end are replaced by
+  // the last pixel (the copies land in slots nobody reads), which keeps the loop branch-free.
+  const int px_last = ch.h0 * p.W + ch.w0 + (len - 1) * ch.pstep;
+  int px_pf = ch.h0 * p.W + ch.w0;
   auto issue = [&](int j) {
-    if (j < len) {
-      float* dst = ring + (j & (kPF - 1)) * rows * 32 + lane;
-      const int px = pix0 + j * ch.pstep;
-      if (act && j < len - 1) {
-        cp_async4(dst, U + (long long)px * L + lane);
-        for (int k = 0; k < D; ++k) cp_async4(dst + (1 + k) * 32, Mr + k * p.slice + (long long)px * L + lane);
-      }
-      if (E && j >= 1) cp_async4(dst + (D + 1) * 32, E + px);
-    }
+    float* dst = ring_lane + (j & (kPF - 1)) * slot_floats;
+    const int pxc = j < len ? px_pf : px_last;
+    const int o = pxc * L;
+    cp_async4(dst, Ul + o);
+#pragma unroll
+    for (int k = 0; k < (DT ? DT : 16); ++k)
+      if (k < D) cp_async4(dst + (1 + k) * 32, Ml + k * p.slice + o);
+    cp_async4(dst + (D + 1) * 32, E + pxc);
     cp_async_commit();
+    px_pf += ch.pstep;
+  };
+  auto uu_of = [&](const float* sl) {  // sl: this lane's column of a ring slot
+    float s = sl[0];
+#pragma unroll
+    for (int k = 0; k < (DT ? DT : 16); ++k)
+      if (k < D) s += sl[(1 + k) * 32];
+    s -= sl[dir_row];
+    return fmaf(s, rho, -sl[inv_row]);
   };
 
 #pragma unroll
   for (int j = 0; j < kPF; ++j) issue(j);
   cp_async_wait<kPF - 1>();
-  float uu = act ? uu_from_ring(ring, 32, lane, D, ch.dir, ch.inv, p.rho) : 0.f;
+  float uu = uu_of(ring_lane);
   issue(kPF);
   float r = 0.f;
+  int px = ch.h0 * p.W + ch.w0 + ch.pstep;  // pixel i = 1
+  int of = px * L;
 
   for (int i = 1; i < len; ++i) {
     cp_async_wait<kPF - 1>();  // everything staged for chain pixel i has landed
-    const float* slot = ring + (i & (kPF - 1)) * rows * 32;
-    const float e = E ? slot[(D + 1) * 32 + lane] : 1.f;
+    const float* sl = ring_lane + (i & (kPF - 1)) * slot_floats;
+    const float e = has_e ? sl[(D + 1) * 32] : 1.f;
     // Old values at pixel i are consumed BEFORE the new message of pixel i is stored (TRWP updates
     // the message slice in place).
-    const float uu_next = (act && i < len - 1) ? uu_from_ring(slot, 32, lane, D, ch.dir, ch.inv, p.rho) : 0.f;
+    const float uu_next = uu_of(sl);
     float* hb = hbuf + (i & 1) * 32;
-    hb[lane] = act ? fmaf(p.rho, r, uu) : kInf;
+    hb[lane] = act ? fmaf(rho, r, uu) : kInf;
     __syncwarp();
     float best;
     int bi;
     minplus_regrow<LMAX, TRAIN>(hb, cr, e, best, bi);
-    const float vv = act ? best : kInf;
-    const float m = warp_min(vv);
+    const float m = warp_min(act ? best : kInf);
     r = best - m;
-    const int px = pix0 + i * ch.pstep;
-    if (act) Mw[(long long)px * L + lane] = r;
+    if (act) Mwl[of] = r;
     if (TRAIN) {
       const unsigned bal = __ballot_sync(0xffffffffu, act && best == m);
-      if (act) MI[(long long)px * L + lane] = (uint8_t)bi;
+      if (act) MIl[of] = (uint8_t)bi;
       if (lane == 0) NI[px] = (uint8_t)(31 - __clz(bal));
     }
     issue(i + kPF);
     uu = uu_next;
+    px += ch.pstep;
+    of += ostep;
   }
   cp_async_wait<0>();
 }
@@ -392,17 +480,24 @@ cudaError_t ensure_smem(K kernel, size_t bytes) {
   return cudaSuccess;
 }
 
-template <int LMAX, bool TRAIN>
-cudaError_t launch_warp(const FwdParams& p, cudaStream_t st) {
+template <int LMAX, int DT, bool TRAIN>
+cudaError_t launch_warp_d(const FwdParams& p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int wpb = total >= 148 * 32 ? 4 : 1;
   const size_t smem = (size_t)wpb * (kPF * (p.D + 2) * 32 + 64) * sizeof(float);
-  cudaError_t e = ensure_smem(fwd_warp_kernel<LMAX, TRAIN>, smem);
+  cudaError_t e = ensure_smem(fwd_warp_kernel<LMAX, DT, TRAIN>, smem);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
-  fwd_warp_kernel<LMAX, TRAIN><<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+  fwd_warp_kernel<LMAX, DT, TRAIN><<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
   count_launch();
   return cudaGetLastError();
+}
+
+template <int LMAX, bool TRAIN>
+cudaError_t launch_warp(const FwdParams& p, cudaStream_t st) {
+  if (p.D == 4) return launch_warp_d<LMAX, 4, TRAIN>(p, st);
+  if (p.D == 8) return launch_warp_d<LMAX, 8, TRAIN>(p, st);
+  return launch_warp_d<LMAX, 0, TRAIN>(p, st);
 }
 
 template <int MODE, bool TRAIN>
