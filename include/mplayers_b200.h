@@ -102,6 +102,12 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
                        float* dedge_weights, float* dmsg, float* dmsg_update, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* Reads back (synchronously) the device status word of a forward workspace after the forward
+ * call that used it: 0 = every kernel ran to completion, otherwise the code of a bounded wait
+ * that gave up (101 / 102: staging pipeline of the bulk-copy kernel).  No counterpart in the
+ * reference, whose kernels never wait on anything. */
+int mpl_forward_status(const void* workspace, int32_t* status);
+
 /* Message of the last error on the calling thread ("" if none).  Replaces the reference's
  * printf-and-return error reporting (MPLayers/TRWP/TRWP.cpp:269-273,316). */
 const char* mpl_last_error(void);

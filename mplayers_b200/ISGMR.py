@@ -33,6 +33,7 @@ def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weig
             _lib.ptr(msg), _lib.ptr(msg_update), _lib.ptr(cost_final), _lib.ptr(msg_min_index),
             _lib.ptr(msg_norm_index), _lib.ptr(label_all), _lib.ptr(ws), nbytes,
             _lib.stream_ptr(dev)))
+        _lib.check_status(ws)
 
 
 def backward(enable_sgm, rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,

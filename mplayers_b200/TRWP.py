@@ -42,6 +42,7 @@ def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, co
             ctypes.byref(prob), _lib.ptr(unary), _lib.ptr(context), _lib.ptr(edge_weights),
             _lib.ptr(msg), _lib.ptr(cost_final), _lib.ptr(msg_min_index), _lib.ptr(msg_norm_index),
             _lib.ptr(label_all), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+        _lib.check_status(ws)
 
 
 def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index, dunary,

@@ -47,6 +47,8 @@ def lib():
         L.mpl_isgmr_forward.argtypes = [pp] + [vp] * 10 + [sz, vp]
         L.mpl_isgmr_backward.restype = ctypes.c_int
         L.mpl_isgmr_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
+        L.mpl_forward_status.restype = ctypes.c_int
+        L.mpl_forward_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32)]
         L.mpl_last_error.restype = ctypes.c_char_p
         L.mpl_kernel_launches.restype = ctypes.c_int64
         L.mpl_version.restype = ctypes.c_int32
@@ -61,6 +63,18 @@ def kernel_launches():
 def check(rc):
     if rc != MPL_OK:
         raise RuntimeError("mplayers_b200: " + lib().mpl_last_error().decode())
+
+
+def check_status(ws):
+    """With MPL_CHECK_STATUS=1 in the environment: wait for the forward call that used workspace
+    `ws` and raise if a kernel recorded that one of its bounded waits gave up.  Off by default
+    because it synchronises."""
+    if os.environ.get("MPL_CHECK_STATUS") != "1":
+        return
+    st = ctypes.c_int32(0)
+    check(lib().mpl_forward_status(ctypes.c_void_p(ws.data_ptr()), ctypes.byref(st)))
+    if st.value != 0:
+        raise RuntimeError("mplayers_b200: device status %d (a staging wait timed out)" % st.value)
 
 
 def ptr(t):

@@ -106,6 +106,7 @@ void fill_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, const
   fp.ctx = ctx;
   fp.ew = ew;
   fp.info = static_cast<const mpl::CtxInfo*>(workspace);
+  fp.status = reinterpret_cast<int*>(static_cast<char*>(workspace) + 64);
   fp.H = p->height;
   fp.W = p->width;
   fp.L = p->n_disp;
@@ -145,6 +146,7 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
 
   mpl::FwdParams fp{};
   fill_forward(fp, p, d, unary, context, edge_weights, workspace);
+  MPL_CUDA(cudaMemsetAsync(fp.status, 0, sizeof(int), st));
   MPL_CUDA(mpl::launch_analyze(context, L, p->context_rank, edge_weights, d.npix * D,
                                static_cast<mpl::CtxInfo*>(workspace), st));
 
@@ -303,6 +305,12 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
   return backward_common(true, p, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,
                          dunary, dcontext, dedge_weights, dmsg, dmsg_update, workspace,
                          workspace_bytes, stream);
+}
+
+int mpl_forward_status(const void* workspace, int32_t* status) {
+  if (!workspace || !status) return fail(MPL_ERR_INVALID, "NULL pointer");
+  MPL_CUDA(cudaMemcpy(status, static_cast<const char*>(workspace) + 64, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  return MPL_OK;
 }
 
 const char* mpl_last_error(void) { return g_err.c_str(); }

@@ -85,11 +85,13 @@ struct FwdParams {
   uint8_t* min_idx;       // [D,nimg,H,W,L] of this iteration, or nullptr
   uint8_t* norm_idx;      // [D,nimg,H,W]
   const CtxInfo* info;
+  int* status;            // device word: 0 = ok, else the code of a wait that gave up
   int H, W, L, D, nimg;
   long long slice;        // nimg*H*W*L
   long long pslice;       // nimg*H*W
   float rho;
   int ctx_rank;
+  int tma_stages;         // bulk-copy kernel: ring depth
   int dir0, ndirs;        // this launch covers directions dir0 .. dir0+ndirs-1
   int chain_off[17];      // prefix sums of nimg*n_chains over those directions
 };
@@ -154,6 +156,47 @@ __device__ __forceinline__ float float_from_order_bits(int b) {
 }
 
 constexpr float kInf = __builtin_huge_valf();
+
+// ---- mbarrier / bulk-copy (TMA) primitives; every wait is bounded --------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// Waits for the phase with the given parity; gives up after about a second and returns false.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  const unsigned a = smem_u32(bar);
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(a), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (clock64() - t0 > 2000000000ll) return false;
+  }
+}
+// Global -> shared bulk copy (no multicast), completion counted in bytes on `bar`.
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 
 // Host-side launchers (mp_forward.cu / mp_backward.cu).  Return cudaGetLastError() of the launch.
 cudaError_t launch_analyze(const float* ctx, int L, int rank, const float* ew, long long n_ew,

@@ -123,19 +123,23 @@ __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr
   best = min_tree<LMAX>(val);
   bi = 0;
   if (TRAIN) {
+    // Sums of distinct powers of two are exact in any order, so each group of 24 labels is
+    // accumulated in three interleaved partial sums (short dependency chains).
     constexpr int NA = (LMAX + 23) / 24;
-    float acc[NA];
+    float acc[NA][3];
 #pragma unroll
-    for (int a = 0; a < NA; ++a) acc[a] = 0.f;
+    for (int a = 0; a < NA; ++a) acc[a][0] = acc[a][1] = acc[a][2] = 0.f;
 #pragma unroll
-    for (int f = 0; f < LMAX; ++f) acc[f / 24] = fmaf(eq_flag(val[f], best), pow2f(f % 24), acc[f / 24]);
+    for (int f = 0; f < LMAX; ++f)
+      acc[f / 24][f % 3] = fmaf(eq_flag(val[f], best), pow2f(f % 24), acc[f / 24][f % 3]);
 #pragma unroll
     for (int a = 0; a < NA; ++a) {
-      const int ex = ((__float_as_int(acc[a]) >> 23) & 0xff) - 127 + 24 * a;
+      const float sum = (acc[a][0] + acc[a][1]) + acc[a][2];
+      const int ex = ((__float_as_int(sum) >> 23) & 0xff) - 127 + 24 * a;
       if (a == 0) {
         bi = ex;
       } else {
-        bi = acc[a] != 0.f ? ex : bi;
+        bi = sum != 0.f ? ex : bi;
       }
     }
   }
@@ -242,6 +246,215 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
     of += ostep;
   }
   cp_async_wait<0>();
+}
+
+// ------------------------------------------------------------------------------------------------
+// L <= 32, directions 0..3, 16-byte-aligned rows: bulk-copy (TMA) staged kernel.
+//
+// A CTA walks four neighbouring chains (four image rows for the horizontal directions, four
+// adjacent columns for the vertical ones) with one consumer warp each; a fifth warp is the
+// producer.  Per stage of kTK chain pixels the producer issues plain (non-multicast)
+// cp.async.bulk copies of whole row segments -- kTK*L floats per array and chain horizontally,
+// 4*L floats per array and image row vertically -- into a ring of shared-memory tiles; completion
+// is counted in bytes on one mbarrier per stage, and consumers hand a tile back through a second
+// mbarrier.  The consumers therefore spend no instruction on global loads or their addresses.
+// Every wait is bounded: after about a second it records a code in *status and the warp leaves.
+// ------------------------------------------------------------------------------------------------
+constexpr int kTK = 16;
+
+// LT = compile-time label count (0: runtime, up to LMAX = 32); FWD = the chain walks towards
+// increasing coordinates (directions 0 and 2).
+template <int LMAX, int LT, int DT, bool TRAIN, bool VERT, bool FWD>
+__global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(128) float smem[];
+  constexpr int A = DT + 1;   // staged arrays: unary + D message slices
+  constexpr int AE = A + 1;   // ... + edge weights
+  const int L = LT ? LT : p.L, H = p.H, W = p.W, NS = p.tma_stages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int dir = p.dir0, inv = dir ^ 1;
+  const bool has_e = p.ew != nullptr;
+  const int len = VERT ? H : W;
+  const int nstages = (len + kTK - 1) / kTK;
+  const int tile_floats = A * kTK * 4 * L;
+
+  float* tiles = smem;                                   // [NS][tile_floats]
+  float* etiles = tiles + NS * tile_floats;              // [NS][64]
+  float* hbufs = etiles + NS * 64;                       // [4][64]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(hbufs + 4 * 64);  // [NS]
+  unsigned long long* empty = full + NS;                 // [NS]
+
+  // the four chains of this CTA
+  int nact, img0 = 0, w0 = 0, chain0 = 0;
+  if (VERT) {
+    const int gpi = W >> 2;
+    img0 = blockIdx.x / gpi;
+    w0 = (blockIdx.x - img0 * gpi) << 2;
+    nact = 4;
+  } else {
+    chain0 = blockIdx.x << 2;  // flattened (image, row)
+    const int total = p.nimg * H;
+    nact = total - chain0 < 4 ? total - chain0 : 4;
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], nact);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == 4) {
+    // ---------------------------------- producer ----------------------------------
+    const unsigned row_bytes = VERT ? 16u * L : 0u;
+    for (int s = 0; s < nstages; ++s) {
+      const int slot = s % NS;
+      if (s >= NS && !mbar_wait(&empty[slot], ((s / NS) - 1) & 1)) {
+        if (lane == 0) atomicExch(p.status, 101);
+        break;
+      }
+      const int npix = len - s * kTK < kTK ? len - s * kTK : kTK;
+      float* T = tiles + slot * tile_floats;
+      float* ET = etiles + slot * 64;
+      if (lane == 0) {
+        const unsigned bytes = VERT ? (unsigned)npix * (A * row_bytes + (has_e ? 16u : 0u))
+                                    : (unsigned)nact * (unsigned)npix * (A * 4u * L + (has_e ? 4u : 0u));
+        mbar_arrive_expect_tx(&full[slot], bytes);
+      }
+      __syncwarp();
+      const int ncopy = (VERT ? npix : nact) * AE;
+      for (int c = lane; c < ncopy; c += 32) {
+        const int q = c / AE, a = c - q * AE;
+        long long pix;  // first pixel of the segment, over all images
+        if (VERT) {
+          const int h = FWD ? s * kTK + q : H - 1 - (s * kTK + q);
+          pix = ((long long)img0 * H + h) * W + w0;
+        } else {
+          const int wlo = FWD ? s * kTK : W - s * kTK - npix;
+          pix = (long long)(chain0 + q) * W + wlo;
+        }
+        if (a < A) {
+          const float* src = (a == 0 ? p.unary : p.msg_read + (long long)(a - 1) * p.slice) + pix * L;
+          float* dst = VERT ? T + (a * kTK + q) * 4 * L : T + (q * A + a) * kTK * L;
+          bulk_g2s(dst, src, VERT ? row_bytes : (unsigned)npix * 4u * L, &full[slot]);
+        } else if (has_e) {
+          const float* src = p.ew + (long long)dir * p.pslice + pix;
+          float* dst = VERT ? ET + q * 4 : ET + q * kTK;
+          bulk_g2s(dst, src, VERT ? 16u : (unsigned)npix * 4u, &full[slot]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------- consumers ----------------------------------
+  const int wc = warp;
+  if (wc >= nact) return;
+  const bool act = lane < L;
+  // Idle lanes (lane >= L) mirror the last label: same loads, same arithmetic, same `best`, so the
+  // warp-wide minimum needs no select; only their stores are masked.
+  const int lc = act ? lane : L - 1;
+  const unsigned lmask = L >= 32 ? 0xffffffffu : (1u << L) - 1u;
+  const float rho = p.rho;
+  float cr[LMAX];
+#pragma unroll
+  for (int f = 0; f < LMAX; ++f) cr[f] = f < L ? ctx_value(p.ctx, p.ctx_rank, L, lc, f) : 0.f;
+
+  int img, fix;  // fix = the coordinate that stays constant along the chain
+  if (VERT) {
+    img = img0;
+    fix = w0 + wc;
+  } else {
+    img = (chain0 + wc) / H;
+    fix = (chain0 + wc) - img * H;
+  }
+  const long long ibase = (long long)img * H * W;
+  float* Mwl = p.msg_write + (long long)dir * p.slice + ibase * L + lc;
+  uint8_t* MIl = TRAIN ? p.min_idx + (long long)dir * p.slice + ibase * L + lc : nullptr;
+  uint8_t* NI = TRAIN ? p.norm_idx + (long long)dir * p.pslice + ibase : nullptr;
+  float* hbuf = hbufs + wc * 64;
+  for (int i = lane; i < 64; i += 32) hbuf[i] = kInf;  // labels >= L (LMAX > L) never win
+  if (!has_e)  // no edge weights: the producer copies none, every staged weight reads as 1
+    for (int i = lane; i < NS * 64; i += 32) etiles[i] = 1.f;
+  __syncwarp();
+  const int sa = VERT ? kTK * 4 * L : kTK * L;        // stride between staged arrays
+  const int sk = VERT ? 4 * L : (FWD ? L : -L);        // stride between consecutive chain pixels
+  const int ek = VERT ? 4 : (FWD ? 1 : -1);
+  const int pstep = VERT ? (FWD ? W : -W) : (FWD ? 1 : -1);
+  const int px0 = VERT ? (FWD ? 0 : H - 1) * W + fix : fix * W + (FWD ? 0 : W - 1);  // chain pixel 0
+  const int dir_off = (1 + dir) * sa, inv_off = (1 + inv) * sa;
+
+  float uu = 0.f, r = 0.f;
+  // inputs of one chain pixel -> UU of that pixel (reference order of the additions)
+  auto uu_at = [&](const float* t) {
+    float sum = t[0];
+#pragma unroll
+    for (int a = 1; a <= DT; ++a) sum += t[a * sa];
+    sum -= t[dir_off];
+    return fmaf(sum, rho, -t[inv_off]);
+  };
+  // message of chain pixel `px` from its predecessor's UU (in `uu`) and running message `r`
+  auto step = [&](const float* t, float e, int par, int px) {
+    const float uu_next = uu_at(t);
+    float* hb = hbuf + par * 32;
+    if (LT == 0 || LMAX != LT) {
+      if (act) hb[lane] = fmaf(rho, r, uu);
+    } else {
+      hb[lane] = fmaf(rho, r, uu);  // entries >= L are written but never read
+    }
+    __syncwarp();
+    float best;
+    int bi;
+    minplus_regrow<LMAX, TRAIN>(hb, cr, e, best, bi);
+    const float m = warp_min(best);
+    r = best - m;
+    // Unpredicated stores: idle lanes hold the same values as lane L-1 and write the same
+    // address, and the normalisation index is warp-uniform.
+    const int of = px * L;
+    Mwl[of] = r;
+    if (TRAIN) {
+      const unsigned bal = __ballot_sync(0xffffffffu, best == m) & lmask;
+      MIl[of] = (uint8_t)bi;
+      NI[px] = (uint8_t)(31 - __clz(bal));
+    }
+    uu = uu_next;
+  };
+
+  for (int s = 0; s < nstages; ++s) {
+    const int slot = s % NS;
+    if (!mbar_wait(&full[slot], (s / NS) & 1)) {
+      if (lane == 0) atomicExch(p.status, 102);
+      return;
+    }
+    const int npix = len - s * kTK < kTK ? len - s * kTK : kTK;
+    const float* T = tiles + slot * tile_floats + lc;
+    const float* ET = etiles + slot * 64;
+    const float* t0;
+    const float* e0;
+    if (VERT) {
+      t0 = T + wc * L;
+      e0 = ET + wc;
+    } else {
+      t0 = T + wc * A * kTK * L + (FWD ? 0 : (npix - 1) * L);
+      e0 = ET + wc * kTK + (FWD ? 0 : npix - 1);
+    }
+    const int pxs = px0 + s * kTK * pstep;
+    if (s > 0 && npix == kTK) {
+      // full stage: fully unrolled, every tile offset is an immediate
+#pragma unroll
+      for (int k = 0; k < kTK; ++k) step(t0 + k * sk, e0[k * ek], k & 1, pxs + k * pstep);
+    } else {
+      for (int k = 0; k < npix; ++k) {
+        if (s + k == 0) {
+          uu = uu_at(t0);  // chain pixel 0 only provides the inputs of pixel 1
+        } else {
+          step(t0 + k * sk, e0[k * ek], k & 1, pxs + k * pstep);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[slot]);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -500,6 +713,54 @@ cudaError_t launch_warp(const FwdParams& p, cudaStream_t st) {
   return launch_warp_d<LMAX, 0, TRAIN>(p, st);
 }
 
+size_t tma_smem_bytes(int L, int D, int stages) {
+  return ((size_t)stages * ((size_t)(D + 1) * kTK * 4 * L + 64) + 4 * 64) * sizeof(float) + 2 * stages * 8 + 16;
+}
+
+// Can direction `dir` of this problem use the bulk-copy kernel?  Needs 16-byte aligned row segments.
+bool tma_eligible(const FwdParams& p, int dir, int* stages) {
+  if (dir > 3 || p.L > 32 || (p.D != 4 && p.D != 8)) return false;
+  if ((p.W & 3) || (((long long)p.W * p.L) & 3)) return false;
+  const uintptr_t bits = (uintptr_t)p.unary | (uintptr_t)p.msg_read | (uintptr_t)p.ew;
+  if (bits & 15) return false;
+  int ns = 3;
+  while (ns >= 2 && tma_smem_bytes(p.L, p.D, ns) > (ns == 3 ? 100 : 200) * 1024) --ns;
+  if (ns < 2) return false;
+  *stages = ns;
+  return true;
+}
+
+template <int LMAX, int LT, int DT, bool TRAIN, bool VERT, bool FWD>
+cudaError_t launch_tma_v(FwdParams p, int dir, int stages, cudaStream_t st) {
+  p.dir0 = dir;
+  p.ndirs = 1;
+  p.tma_stages = stages;
+  const int groups = VERT ? p.nimg * (p.W >> 2) : (p.nimg * p.H + 3) >> 2;
+  const size_t smem = tma_smem_bytes(p.L, p.D, stages);
+  cudaError_t e = ensure_smem(fwd_tma_kernel<LMAX, LT, DT, TRAIN, VERT, FWD>, smem);
+  if (e != cudaSuccess) return e;
+  ProfScope prof(kProfFwdSweep, st);
+  fwd_tma_kernel<LMAX, LT, DT, TRAIN, VERT, FWD><<<groups, 160, smem, st>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+template <int LMAX, int LT, int DT, bool TRAIN>
+cudaError_t launch_tma_d(const FwdParams& p, int dir, int stages, cudaStream_t st) {
+  switch (dir) {
+    case 0: return launch_tma_v<LMAX, LT, DT, TRAIN, false, true>(p, dir, stages, st);
+    case 1: return launch_tma_v<LMAX, LT, DT, TRAIN, false, false>(p, dir, stages, st);
+    case 2: return launch_tma_v<LMAX, LT, DT, TRAIN, true, true>(p, dir, stages, st);
+    default: return launch_tma_v<LMAX, LT, DT, TRAIN, true, false>(p, dir, stages, st);
+  }
+}
+
+template <int LMAX, int LT, bool TRAIN>
+cudaError_t launch_tma(const FwdParams& p, int dir, int stages, cudaStream_t st) {
+  if (p.D == 4) return launch_tma_d<LMAX, LT, 4, TRAIN>(p, dir, stages, st);
+  return launch_tma_d<LMAX, LT, 8, TRAIN>(p, dir, stages, st);
+}
+
 template <int MODE, bool TRAIN>
 cudaError_t launch_cta(const FwdParams& p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
@@ -531,8 +792,26 @@ cudaError_t launch_analyze(const float* ctx, int L, int rank, const float* ew, l
 cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st) {
   if (p.chain_off[p.ndirs] == 0) return cudaSuccess;
   if (p.L <= 32) {
-    if (p.L == 21) return train ? launch_warp<21, true>(p, st) : launch_warp<21, false>(p, st);
-    return train ? launch_warp<32, true>(p, st) : launch_warp<32, false>(p, st);
+    // directions with aligned row segments go to the bulk-copy kernel (one launch each), the
+    // remaining contiguous range of directions to the generic kernel
+    FwdParams rest = p;
+    int first_generic = p.dir0;
+    for (int d = p.dir0; d < p.dir0 + p.ndirs; ++d) {
+      int stages = 0;
+      if (d != first_generic || !tma_eligible(p, d, &stages)) break;
+      cudaError_t e = p.L == 21 ? (train ? launch_tma<21, 21, true>(p, d, stages, st) : launch_tma<21, 21, false>(p, d, stages, st))
+                                : (train ? launch_tma<32, 0, true>(p, d, stages, st) : launch_tma<32, 0, false>(p, d, stages, st));
+      if (e != cudaSuccess) return e;
+      first_generic = d + 1;
+    }
+    const int nrest = p.dir0 + p.ndirs - first_generic;
+    if (nrest == 0) return cudaSuccess;
+    const int base = p.chain_off[first_generic - p.dir0];
+    rest.dir0 = first_generic;
+    rest.ndirs = nrest;
+    for (int i = 0; i <= nrest; ++i) rest.chain_off[i] = p.chain_off[first_generic - p.dir0 + i] - base;
+    if (p.L == 21) return train ? launch_warp<21, true>(rest, st) : launch_warp<21, false>(rest, st);
+    return train ? launch_warp<32, true>(rest, st) : launch_warp<32, false>(rest, st);
   }
   if (p.ctx_rank == 1) return train ? launch_cta<1, true>(p, st) : launch_cta<1, false>(p, st);
   if (p.L <= 64) return train ? launch_cta<2, true>(p, st) : launch_cta<2, false>(p, st);

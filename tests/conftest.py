@@ -3,6 +3,8 @@ import sys
 
 import pytest
 
+os.environ.setdefault("MPL_CHECK_STATUS", "1")   # tests verify that no device-side wait gave up
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

@@ -171,3 +171,24 @@ def test_run_to_run_identical():
     gb = g.backward("TRWP", ctx, ew, dcost, a["min_idx"], a["norm_idx"])
     for k in ("dunary", "dctx", "dew"):
         assert np.array_equal(ga[k], gb[k])
+
+
+@pytest.mark.parametrize("mode,D,H,W,L,kind", [
+    ("TRWP", 4, 37, 64, 21, "sym2d"),    # horizontal + vertical bulk-copy kernels, ragged last stage vertically
+    ("TRWP", 4, 16, 20, 21, "potts2d"),  # width with a 4-pixel tail stage
+    ("ISGMR", 8, 19, 32, 21, "sym2d"),   # directions 0-3 bulk-copy, 4-7 generic kernel in one call
+    ("TRWP", 4, 33, 48, 32, "sym2d"),    # full warp of labels
+    ("ISGMR", 4, 18, 36, 7, "tl1d"),     # few labels, rank-1 context
+    ("TRWP", 4, 9, 30, 21, "sym2d"),     # width not a multiple of 4: generic kernel only
+])
+def test_bulk_copy_kernel_shapes(mode, D, H, W, L, kind):
+    """Shapes that do / do not meet the 16-byte alignment rules of the bulk-copy staged kernel."""
+    g = _gpu()
+    for B, ewk in ((3, "pos"), (1, "none")):
+        unary, ctx, ew, dcost = _rand_case(500 + H + W + L, mode, D, B, 1, H, W, L, 3, kind, ewk)
+        got = g.forward(mode, unary, ctx, ew, D, 3, save_labels=True)
+        want = oracle.forward(mode, unary, ctx, ew, D, 3, save_labels=True)
+        for k in ("cost", "msg", "norm_idx", "min_idx", "label_all"):
+            assert np.array_equal(got[k], want[k]), k
+        ev = g.forward(mode, unary, ctx, ew, D, 3, training=False)
+        assert np.array_equal(ev["cost"], want["cost"])
