@@ -213,10 +213,15 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
 
   const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
+  // TRWP with L <= 32 keeps the message gradients as dM_k = C + P_k (C in `dunary`, P in `dmsg`),
+  // see BwdParams::cp_scheme; everything else updates dunary and the D slices directly.
+  const int cp = (!isgmr && L <= 32) ? 1 : 0;
   float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced
   float* Y = isgmr ? dmsg : dmsg;         // gradients of the messages the sweeps read
-  MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, st));
+  MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp, st));
   if (isgmr) MPL_CUDA(cudaMemsetAsync(Y, 0, (size_t)D * d.slice * sizeof(float), st));
+  int* status = reinterpret_cast<int*>(part + (size_t)n_slots * d.ctx_elems);
+  MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
 
   mpl::BwdParams bp{};
   bp.ctx = context;
@@ -234,6 +239,8 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   bp.rho = p->rho;
   bp.ctx_rank = p->context_rank;
   bp.keep_diag = p->keep_diag;
+  bp.cp_scheme = cp;
+  bp.status = status;
   for (int it = p->n_iter - 1; it >= 0; --it) {
     for (int dir = D - 1; dir >= 0; --dir) {
       bp.dir = dir;
@@ -267,7 +274,7 @@ size_t mpl_backward_workspace_bytes(const mpl_problem* p) {
   Dims d;
   if (validate(p, &d) != MPL_OK) return 256;
   const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
-  const size_t b = (size_t)n_slots * d.ctx_elems * sizeof(float);
+  const size_t b = (size_t)n_slots * d.ctx_elems * sizeof(float) + 64;  // tables + status word
   return b < 256 ? 256 : b;
 }
 

@@ -7,19 +7,21 @@
 //   * the scatter "dUU[front, idx[c]] += t[c]" never leaves the chip: it is evaluated as a gather
 //     over the labels of the same pixel (fixed order, so the result is run-to-run identical) and
 //     carried to the predecessor pixel in a register;
-//   * the elementwise update of the predecessor's gradients is applied on the fly with
-//     fire-and-forget reductions (each address is touched once per sweep);
+//   * the elementwise update of the pixel's gradients is applied on the fly (each address is
+//     touched once per sweep);
 //   * the label-context gradient is accumulated in a per-chain table in shared memory (row c is
 //     private to thread c) and flushed once per chain into per-slot partial tables, which a final
 //     kernel sums in a fixed order;
-//   * the two per-pixel sums (normalisation backward, edge-weight gradient) share one reduction.
+//   * per-pixel scalars (normalisation sum, edge weight, normalisation index, edge-weight
+//     gradient) are produced for a whole block of steps at once, one step per lane, instead of
+//     one warp reduction per step.  The normalisation sum is taken over the stored gradient
+//     alone: the part carried from the successor pixel sums to zero (it is itself the output of
+//     a normalisation backward), so only rounding noise is dropped.
 #include "mp_common.cuh"
 
 namespace mpl {
 
 namespace {
-
-constexpr int kPFB = 8;  // pixels of dM_d staged ahead (power of two)
 
 struct BChain {
   int img, h0, w0, len, pstep;
@@ -42,26 +44,57 @@ __device__ __forceinline__ void warp_sum2(float& a, float& b) {
   }
 }
 
+// q[f] = sum over labels c whose saved argmin is f of t[c], for f = `me`; fixed summation order.
+// tb / ib: the t values and argmin indices of all labels of this pixel in shared memory.
+template <int LT>
+__device__ __forceinline__ float gather_q(const float* tb, const int* ib, int L, int me) {
+  float q0 = 0.f, q1 = 0.f, q2 = 0.f;
+  if constexpr (LT > 0) {
+    constexpr int NV = (LT + 3) / 4;
+    float tv[NV * 4];
+    int iv[NV * 4];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const float4 a = reinterpret_cast<const float4*>(tb)[v];
+      const int4 b = reinterpret_cast<const int4*>(ib)[v];
+      tv[4 * v] = a.x, tv[4 * v + 1] = a.y, tv[4 * v + 2] = a.z, tv[4 * v + 3] = a.w;
+      iv[4 * v] = b.x, iv[4 * v + 1] = b.y, iv[4 * v + 2] = b.z, iv[4 * v + 3] = b.w;
+    }
+#pragma unroll
+    for (int c = 0; c < LT; ++c) {
+      const float add = iv[c] == me ? tv[c] : 0.f;
+      if (c % 3 == 0) q0 += add;
+      if (c % 3 == 1) q1 += add;
+      if (c % 3 == 2) q2 += add;
+    }
+  } else {
+    int c = 0;
+    for (; c + 2 < L; c += 3) {
+      q0 += ib[c] == me ? tb[c] : 0.f;
+      q1 += ib[c + 1] == me ? tb[c + 1] : 0.f;
+      q2 += ib[c + 2] == me ? tb[c + 2] : 0.f;
+    }
+    for (; c < L; ++c) q0 += ib[c] == me ? tb[c] : 0.f;
+  }
+  return (q0 + q1) + q2;
+}
+
 // ------------------------------------------------------------------------------------------------
-// L <= 32: one warp per chain, lane = label.  DT = compile-time direction count (0: from params).
+// L <= 32, generic: one warp per chain, lane = label, any direction / alignment.
+// DT = compile-time direction count (0: from params); CP = gradient bookkeeping scheme.
 //
-// The chain is walked in blocks of 32 steps.  The message gradients of a whole block are staged
-// in shared memory one block ahead (cp.async), which lets lane j compute the per-pixel scalars of
-// step 32*b + j for the whole block at once -- the normalisation sum, the edge weight, the
-// normalisation index, and afterwards the edge-weight gradient -- instead of one warp reduction
-// per step.  The sum the normalisation backward needs is taken over the staged gradient alone:
-// the part carried from the successor pixel sums to zero (it is itself the output of a
-// normalisation backward), so only rounding noise is dropped.
+// The chain is walked in blocks of 32 steps; the stored message gradients of a whole block are
+// staged in shared memory one block ahead with cp.async.
 // ------------------------------------------------------------------------------------------------
 constexpr int kRB = 64;  // ring rows: two blocks of 32 steps
 constexpr int kRS = 33;  // padded row stride (conflict-free both along and across rows)
 
-__host__ __device__ inline int bwd_warp_floats(int L, int rank) {
+__host__ __device__ inline int bwd_warp_floats(int L, int rank, int cp) {
   const int tab = rank == 2 ? L * (L | 1) : 32;
-  return kRB * kRS + 32 * kRS + 128 + ((tab + 3) & ~3);
+  return (cp ? 2 : 1) * kRB * kRS + 32 * kRS + 128 + ((tab + 3) & ~3);
 }
 
-template <int DT>
+template <int DT, bool CP>
 __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -77,20 +110,21 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
   BChain ch;
   if (!decode_bchain(p, g, ch)) return;
   const int tab = p.ctx_rank == 2 ? L * LS : 32;
-  float* ring = smem + ctab_floats + warp * bwd_warp_floats(L, p.ctx_rank);  // [kRB][kRS]
-  float* dtile = ring + kRB * kRS;                                          // [32][kRS]
-  float* ts = dtile + 32 * kRS;                                             // [2][32]
-  int* is = reinterpret_cast<int*>(ts + 64);                                // [2][32]
-  float* acc = ts + 128;                                                    // context-gradient table
+  float* ring = smem + ctab_floats + warp * bwd_warp_floats(L, p.ctx_rank, CP);  // [kRB][kRS] (x2 if CP)
+  float* ring2 = ring + kRB * kRS;                                              // CP: P_dir rows
+  float* dtile = ring + (CP ? 2 : 1) * kRB * kRS;                               // [32][kRS]
+  float* ts = dtile + 32 * kRS;                                                 // [2][32]
+  int* is = reinterpret_cast<int*>(ts + 64);                                    // [2][32]
+  float* acc = ts + 128;                                                        // context-gradient table
   const bool act = lane < L;
   for (int i = lane; i < tab; i += 32) acc[i] = 0.f;
   is[lane] = -1;
   is[32 + lane] = -1;
 
   const long long ibase = (long long)ch.img * p.H * p.W;
-  float* DMrl = p.dm_read + (long long)dir * p.slice + ibase * L + lane;
+  float* DMrl = p.dm_read + (long long)dir * p.slice + ibase * L + lane;  // dM_dir, or P_dir
   float* DMal = p.dm_acc + ibase * L + lane;
-  float* DUl = p.dunary + ibase * L + lane;
+  float* DUl = p.dunary + ibase * L + lane;                              // dU, or C
   const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
   float* DE = p.dew ? p.dew + ibase : nullptr;
   const uint8_t* MIl = p.min_idx + ibase * L + lane;
@@ -103,14 +137,18 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
   const int nsteps = len - 1;    // steps with a predecessor pixel (s = 0 .. len-2)
 
   // step s visits chain pixel len-1-s at image pixel pixl - s*pstep
-  auto stage_block = [&](int b) {  // dM_d of the 32 steps of block b -> ring rows (32*b .. ) & 63
+  auto stage_block = [&](int b) {  // stored gradients of the 32 steps of block b -> ring rows
     if (act) {
-      int s = 32 * b;
+      const int s = 32 * b;
       int o = (pixl - s * pstep) * L;
       float* dst = ring + (s & (kRB - 1)) * kRS + lane;
 #pragma unroll 8
       for (int u = 0; u < 32; ++u) {
-        if (s + u < nsteps) cp_async4(dst + u * kRS, DMrl + o);
+        // CP also needs the values of the chain-start pixel (its C is rewritten there)
+        if (s + u < (CP ? len : nsteps)) {
+          cp_async4(dst + u * kRS, CP ? DUl + o : DMrl + o);
+          if (CP) cp_async4(dst + kRB * kRS + u * kRS, DMrl + o);
+        }
         o -= ostep;
       }
     }
@@ -147,7 +185,7 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
     float s_cur = 0.f;
     {
       const float* row = ring + ((32 * b + lane) & (kRB - 1)) * kRS;
-      for (int c = 0; c < L; ++c) s_cur += row[c];
+      for (int c = 0; c < L; ++c) s_cur += CP ? row[c] + row[kRB * kRS + c] : row[c];
     }
     for (int g8 = 0; g8 < 4; ++g8) {
       const int s0 = 32 * b + 8 * g8;
@@ -163,13 +201,14 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
         if (s < len) {
           const float rq = rho * q;
           float qn = 0.f;
+          const float x0 = ring[(s & (kRB - 1)) * kRS + lane];  // dM_dir, or C
           if (s < nsteps) {
             const int sl = s & 31;
             const float e = __shfl_sync(0xffffffffu, e_cur, sl);
             const int n = __shfl_sync(0xffffffffu, n_cur, sl);
             const float S = __shfl_sync(0xffffffffu, s_cur, sl);
             const int f = fa[u];
-            const float x = ring[(s & (kRB - 1)) * kRS + lane];
+            const float x = CP ? x0 + ring2[(s & (kRB - 1)) * kRS + lane] : x0;
             const float t0 = act ? x + rq : 0.f;
             const float t = (lane == n) ? t0 - S : t0;  // MPLayers/commonCUDA.cuh:131-145
             float cv = 0.f;
@@ -189,25 +228,23 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
             tb[lane] = t;
             if (act) ib[lane] = f;
             __syncwarp();
-            float q0 = 0.f, q1 = 0.f, q2 = 0.f;
-            int c = 0;
-            for (; c + 2 < L; c += 3) {
-              if (ib[c] == lane) q0 += tb[c];
-              if (ib[c + 1] == lane) q1 += tb[c + 1];
-              if (ib[c + 2] == lane) q2 += tb[c + 2];
-            }
-            for (; c < L; ++c)
-              if (ib[c] == lane) q0 += tb[c];
-            qn = (q0 + q1) + q2;
+            qn = gather_q<0>(tb, ib, L, lane);
           }
           if (act) {
-            // UpdateUnaryKernelBack (MPLayers/TRWP/TRWP_backward.cu:26-47) applied to this pixel
+            if (CP) {
+              const float cnew = x0 + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
+              DUl[of] = cnew;
+              DMrl[of] = -cnew;            // dM_dir = C + P_dir = 0 after its sweep
+              atomicAdd(DMal + inv * p.slice + of, -q);
+            } else {
+              // UpdateUnaryKernelBack (MPLayers/TRWP/TRWP_backward.cu:26-47) applied to this pixel
 #pragma unroll
-            for (int k = 0; k < (DT ? DT : 16); ++k) {
-              if (k < D && k != dir) atomicAdd(DMal + k * p.slice + of, k == inv ? rinv * q : rq);
+              for (int k = 0; k < (DT ? DT : 16); ++k) {
+                if (k < D && k != dir) atomicAdd(DMal + k * p.slice + of, k == inv ? rinv * q : rq);
+              }
+              atomicAdd(DUl + of, rq);
+              DMrl[of] = 0.f;
             }
-            atomicAdd(DUl + of, rq);
-            DMrl[of] = 0.f;
           }
           q = qn;
           of -= ostep;
@@ -246,6 +283,262 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
     if (v != 0.f) atomicAdd(part + lane, v);
   }
 }
+
+// ------------------------------------------------------------------------------------------------
+// L <= 32, directions 0..3, 16-byte aligned rows, C + P bookkeeping: bulk-copy staged kernel.
+// Same CTA organisation as the forward one: four consumer warps (four neighbouring chains) and a
+// producer warp issuing plain cp.async.bulk copies of C and P_dir row segments, kBK steps per
+// stage, completion counted on mbarriers; every wait is bounded.
+// LT = compile-time label count (0: runtime); VERT = directions 2/3; REV = the backward walk runs
+// towards decreasing coordinates (directions 0 and 2, whose forward walk runs upwards).
+// ------------------------------------------------------------------------------------------------
+constexpr int kBK = 16;
+constexpr int kDS = 33;  // row stride of the per-stage product tile
+
+__host__ __device__ inline int bwd_tma_warp_floats(int L, int rank) {
+  const int tab = rank == 2 ? L * (L | 1) : 32;
+  return kBK * kDS + 128 + ((tab + 3) & ~3);
+}
+
+template <int LT, bool VERT, bool REV>
+__global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__ BwdParams p) {
+  extern __shared__ __align__(128) float smem[];
+  const int L = LT ? LT : p.L, H = p.H, W = p.W, NS = p.tma_stages;
+  const int LS = L | 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int dir = p.dir, inv = dir ^ 1;
+  const int len = VERT ? H : W;
+  const int nstages = (len + kBK - 1) / kBK;
+  const int tile_floats = 2 * kBK * 4 * L;  // C and P_dir, kBK steps, four chains
+
+  float* tiles = smem;                                         // [NS][tile_floats]
+  float* ctab = tiles + NS * tile_floats;                      // [L][LS]
+  float* wbase = ctab + ((L * LS + 3) & ~3);                   // per-warp areas
+  unsigned long long* full =
+      reinterpret_cast<unsigned long long*>(wbase + 4 * bwd_tma_warp_floats(L, p.ctx_rank));
+  unsigned long long* empty = full + NS;
+
+  int nact, img0 = 0, w0 = 0, chain0 = 0;
+  if (VERT) {
+    const int gpi = W >> 2;
+    img0 = blockIdx.x / gpi;
+    w0 = (blockIdx.x - img0 * gpi) << 2;
+    nact = 4;
+  } else {
+    chain0 = blockIdx.x << 2;
+    const int total = p.nimg * H;
+    nact = total - chain0 < 4 ? total - chain0 : 4;
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], nact);
+    }
+    mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < L * L; i += blockDim.x)
+    ctab[(i / L) * LS + (i % L)] = ctx_value(p.ctx, p.ctx_rank, L, i / L, i % L);
+  __syncthreads();
+
+  // step st of the walk visits coordinate (REV ? len-1-st : st) along the chain direction
+  if (warp == 4) {
+    // ---------------------------------- producer ----------------------------------
+    const unsigned row_bytes = 16u * L;
+    for (int s = 0; s < nstages; ++s) {
+      const int slot = s % NS;
+      if (s >= NS && !mbar_wait(&empty[slot], ((s / NS) - 1) & 1)) {
+        if (lane == 0) atomicExch(p.status, 201);
+        break;
+      }
+      const int npix = len - s * kBK < kBK ? len - s * kBK : kBK;
+      float* T = tiles + slot * tile_floats;
+      if (lane == 0) {
+        const unsigned bytes = VERT ? (unsigned)npix * 2u * row_bytes : (unsigned)nact * (unsigned)npix * 8u * L;
+        mbar_arrive_expect_tx(&full[slot], bytes);
+      }
+      __syncwarp();
+      const int ncopy = (VERT ? npix : nact) * 2;
+      for (int c = lane; c < ncopy; c += 32) {
+        const int qd = c >> 1, a = c & 1;
+        long long pix;
+        if (VERT) {
+          const int h = REV ? H - 1 - (s * kBK + qd) : s * kBK + qd;
+          pix = ((long long)img0 * H + h) * W + w0;
+        } else {
+          const int wlo = REV ? W - s * kBK - npix : s * kBK;
+          pix = (long long)(chain0 + qd) * W + wlo;
+        }
+        const float* src = (a == 0 ? p.dunary : p.dm_read + (long long)dir * p.slice) + pix * L;
+        float* dst = VERT ? T + (a * kBK + qd) * 4 * L : T + (qd * 2 + a) * kBK * L;
+        bulk_g2s(dst, src, VERT ? row_bytes : (unsigned)npix * 4u * L, &full[slot]);
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------- consumers ----------------------------------
+  const int wc = warp;
+  if (wc >= nact) return;
+  const bool act = lane < L;
+  const int lc = act ? lane : L - 1;  // idle lanes mirror the last label (stores hit the same address)
+  float* dtile = wbase + wc * bwd_tma_warp_floats(L, p.ctx_rank);  // [kBK][kDS]
+  float* ts = dtile + kBK * kDS;                                   // [2][32]
+  int* is = reinterpret_cast<int*>(ts + 64);                       // [2][32]
+  float* acc = ts + 128;
+  const int tab = p.ctx_rank == 2 ? L * LS : 32;
+  for (int i = lane; i < tab; i += 32) acc[i] = 0.f;
+  is[lane] = -1;
+  is[32 + lane] = -1;
+  __syncwarp();
+
+  int img, fix;
+  if (VERT) {
+    img = img0;
+    fix = w0 + wc;
+  } else {
+    img = (chain0 + wc) / H;
+    fix = (chain0 + wc) - img * H;
+  }
+  const long long ibase = (long long)img * H * W;
+  float* Cl = p.dunary + ibase * L + lc;
+  float* Pdl = p.dm_read + (long long)dir * p.slice + ibase * L + lc;
+  float* Pil = p.dm_read + (long long)inv * p.slice + ibase * L + lc;
+  const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
+  float* DE = p.dew ? p.dew + ibase : nullptr;
+  const uint8_t* MIl = p.min_idx + ibase * L + lc;
+  const uint8_t* NI = p.norm_idx + ibase;
+  const float rho = p.rho;
+  const int sa = VERT ? kBK * 4 * L : kBK * L;        // C -> P_dir inside a tile
+  const int sk = VERT ? 4 * L : (REV ? -L : L);        // consecutive steps inside a tile
+  const int pstep = VERT ? (REV ? -W : W) : (REV ? -1 : 1);
+  const int px0 = VERT ? (REV ? H - 1 : 0) * W + fix : fix * W + (REV ? W - 1 : 0);  // first step
+  const int nsteps = len - 1;  // steps that have a predecessor pixel
+  const bool diag_ok = p.keep_diag != 0;
+  const bool rank2 = p.ctx_rank == 2;
+
+  float q = 0.f;
+  // per-stage scalars, lane j < kBK: step kBK*s + j
+  auto load_scalars = [&](int s, float& es, int& ns) {
+    const int st = s * kBK + lane;
+    es = 1.f;
+    ns = 0;
+    if (lane < kBK && st < nsteps) {
+      const int px = px0 + st * pstep;
+      if (E) es = E[px];
+      ns = NI[px];
+    }
+  };
+  auto load_idx = [&](int s, int (&fi)[kBK]) {
+#pragma unroll
+    for (int u = 0; u < kBK; ++u) {
+      const int st = s * kBK + u;
+      fi[u] = st < nsteps ? (int)MIl[(px0 + st * pstep) * L] : -1;
+    }
+  };
+  float e_st, e_nx;
+  int n_st, n_nx;
+  int fa[kBK], fb[kBK];
+  load_scalars(0, e_st, n_st);
+  load_idx(0, fa);
+
+  // one step: t = tile pointer of this pixel (C at t[0], P_dir at t[sa]), k = step inside the stage
+  auto step = [&](const float* t, int k, int f, float S_st, int px, bool has_front) {
+    const float cval = t[0];
+    const float rq = rho * q;
+    float qn = 0.f;
+    if (has_front) {
+      const float e = __shfl_sync(0xffffffffu, e_st, k);
+      const int n = __shfl_sync(0xffffffffu, n_st, k);
+      const float S = __shfl_sync(0xffffffffu, S_st, k);
+      const float t0 = (cval + t[sa]) + rq;
+      const float tt = (lc == n) ? t0 - S : t0;  // MPLayers/commonCUDA.cuh:131-145
+      const float cv = ctab[lc * LS + f];
+      dtile[k * kDS + lane] = cv * tt;
+      const float et = (lc != f || diag_ok) ? e * tt : 0.f;
+      if (rank2) {
+        acc[lc * LS + f] += et;  // idle lanes repeat lane L-1's read-modify-write in lockstep
+      } else if (act) {
+        atomicAdd(acc + (lc > f ? lc - f : f - lc), et);
+      }
+      float* tb = ts + (k & 1) * 32;
+      int* ib = is + (k & 1) * 32;
+      tb[lane] = tt;
+      ib[lane] = f;
+      __syncwarp();
+      qn = gather_q<LT>(tb, ib, L, lc);
+    }
+    const float cnew = cval + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
+    const int of = px * L;
+    Cl[of] = cnew;
+    Pdl[of] = -cnew;               // dM_dir = C + P_dir = 0 after its sweep
+    if (act) atomicAdd(Pil + of, -q);
+    q = qn;
+  };
+
+  for (int s = 0; s < nstages; ++s) {
+    const int slot = s % NS;
+    load_scalars(s + 1, e_nx, n_nx);
+    load_idx(s + 1, fb);
+    if (!mbar_wait(&full[slot], (s / NS) & 1)) {
+      if (lane == 0) atomicExch(p.status, 202);
+      return;
+    }
+    const int npix = len - s * kBK < kBK ? len - s * kBK : kBK;
+    const float* T = tiles + slot * tile_floats;
+    const float* t0p;
+    if (VERT) {
+      t0p = T + wc * L;
+    } else {
+      t0p = T + wc * 2 * kBK * L + (REV ? (npix - 1) * L : 0);
+    }
+    // normalisation sums of the stage: lane j sums (C + P_dir) over the labels of step j
+    float S_st = 0.f;
+    if (lane < npix) {
+      const float* row = t0p + lane * sk;
+      for (int c = 0; c < L; ++c) S_st += row[c] + row[sa + c];
+    }
+    const float* tl = t0p + lc;
+    const int pxs = px0 + s * kBK * pstep;
+    if (npix == kBK && s != nstages - 1) {
+#pragma unroll
+      for (int k = 0; k < kBK; ++k) step(tl + k * sk, k, fa[k], S_st, pxs + k * pstep, true);
+    } else {
+#pragma unroll
+      for (int k = 0; k < kBK; ++k)
+        if (k < npix) step(tl + k * sk, k, fa[k], S_st, pxs + k * pstep, s * kBK + k < nsteps);
+    }
+    // edge-weight gradients of this stage: lane j sums row j of the product tile
+    __syncwarp();
+    if (DE && lane < kBK && s * kBK + lane < nsteps) {
+      const float* row = dtile + lane * kDS;
+      float de = 0.f;
+      for (int c = 0; c < L; ++c) de += row[c];
+      atomicAdd(DE + (pxs + lane * pstep), de);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[slot]);
+    e_st = e_nx;
+    n_st = n_nx;
+#pragma unroll
+    for (int u = 0; u < kBK; ++u) fa[u] = fb[u];
+  }
+
+  // flush the context-gradient table of this chain
+  __syncwarp();
+  const int gchain = blockIdx.x * 4 + wc;
+  float* part = p.dctx_part + (long long)(gchain % p.n_slots) * (rank2 ? L * L : L);
+  if (rank2) {
+    for (int i = lane; i < L * L; i += 32) {
+      const float v = acc[(i / L) * LS + (i % L)];
+      if (v != 0.f) atomicAdd(part + i, v);
+    }
+  } else if (act) {
+    const float v = acc[lane];
+    if (v != 0.f) atomicAdd(part + lane, v);
+  }
+}
+
+constexpr int kPFB = 8;  // CTA kernel: pixels of dM_d staged ahead (power of two)
 
 // ------------------------------------------------------------------------------------------------
 // L > 32: one CTA per chain, thread = label.
@@ -395,45 +688,89 @@ __global__ void __launch_bounds__(256) bwd_cta_kernel(const __grid_constant__ Bw
   }
 }
 
-// dunary = factor * g, dM_k = g for every k.  MPLayers/TRWP/TRWP_backward.cu:8-24,
-// MPLayers/ISGMR/ISGMR_backward.cu:18-37.
+// Prologue.  cp_scheme 0: dunary = factor * g, dM_k = g for every k (MPLayers/TRWP/TRWP_backward.cu:8-24,
+// MPLayers/ISGMR/ISGMR_backward.cu:18-37).  cp_scheme 1: C = g, P_k = 0.
 __global__ void backward_init_kernel(const float* __restrict__ g, float* __restrict__ dunary,
-                                     float* __restrict__ dm, long long n, int D, float factor) {
+                                     float* __restrict__ dm, long long n, int D, float factor, int cp) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
     const float v = g[i];
-    dunary[i] = factor * v;
-    for (int k = 0; k < D; ++k) dm[k * n + i] = v;
+    dunary[i] = cp ? v : factor * v;
+    for (int k = 0; k < D; ++k) dm[k * n + i] = cp ? 0.f : v;
   }
 }
 
-// Sums the per-slot partial tables in slot order and folds them into the caller's dcontext with
-// the reference's addressing (MPLayers/TRWP/TRWP_backward.cu:102-112): rank 2 -> cell
-// [min(c,f)][max(c,f)], rank 1 -> cell |c-f|.
-__global__ void dctx_reduce_kernel(const float* __restrict__ part, int n_slots, int L, int rank,
-                                   float* __restrict__ dctx) {
+// Sums the per-slot partial tables in slot order (two fixed-order levels) and folds them into the
+// caller's dcontext with the reference's addressing (MPLayers/TRWP/TRWP_backward.cu:102-112):
+// rank 2 -> cell [min(c,f)][max(c,f)], rank 1 -> cell |c-f|.
+constexpr int kRedChunks = 64;
+
+__global__ void dctx_reduce1_kernel(float* __restrict__ part, int n_slots, int CT) {
+  // chunk y sums slots y, y + kRedChunks, ... into slot y (in place; slot y is only read by chunk y)
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int y = blockIdx.y;
+  if (i >= CT || y >= n_slots) return;
+  float s = 0.f;
+  for (int k = y; k < n_slots; k += kRedChunks) s += part[(long long)k * CT + i];
+  part[(long long)y * CT + i] = s;
+}
+
+__global__ void dctx_reduce2_kernel(const float* __restrict__ part, int n_slots, int L, int rank,
+                                    float* __restrict__ dctx) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const int CT = rank == 2 ? L * L : L;
   if (i >= CT) return;
+  const int n = n_slots < kRedChunks ? n_slots : kRedChunks;
   if (rank == 2) {
     const int a = i / L, b = i % L;
     if (a > b) return;
     float s = 0.f;
     if (a == b) {
-      for (int k = 0; k < n_slots; ++k) s += part[(long long)k * CT + i];
+      for (int k = 0; k < n; ++k) s += part[(long long)k * CT + i];
     } else {
       const int j = b * L + a;
-      for (int k = 0; k < n_slots; ++k) s += part[(long long)k * CT + i] + part[(long long)k * CT + j];
+      for (int k = 0; k < n; ++k) s += part[(long long)k * CT + i] + part[(long long)k * CT + j];
     }
     dctx[i] += s;
   } else {
     float s = 0.f;
-    for (int k = 0; k < n_slots; ++k) s += part[(long long)k * CT + i];
+    for (int k = 0; k < n; ++k) s += part[(long long)k * CT + i];
     dctx[i] += s;
   }
 }
 
 constexpr int kSmemTableMaxL = 128;  // rank-2 table L*(L|1) floats fits next to the staging ring
+
+size_t bwd_tma_smem_bytes(int L, int rank, int stages) {
+  return ((size_t)stages * 2 * kBK * 4 * L + ((L * (L | 1) + 3) & ~3) + 4 * (size_t)bwd_tma_warp_floats(L, rank)) *
+             sizeof(float) +
+         2 * stages * 8 + 16;
+}
+
+bool bwd_tma_eligible(const BwdParams& p) {
+  if (!p.cp_scheme || p.dir > 3 || p.L > 32) return false;
+  if ((p.W & 3) || (((long long)p.W * p.L) & 3)) return false;
+  if (((uintptr_t)p.dunary | (uintptr_t)p.dm_read) & 15) return false;
+  return true;
+}
+
+template <int LT>
+cudaError_t launch_bwd_tma(const BwdParams& p, cudaStream_t st) {
+  const bool vert = p.dir >= 2;
+  const bool rev = (p.dir & 1) == 0;  // forward walk upwards -> backward walk downwards
+  const int groups = vert ? p.nimg * (p.W >> 2) : (p.nimg * p.H + 3) >> 2;
+  const size_t smem = bwd_tma_smem_bytes(p.L, p.ctx_rank, p.tma_stages);
+  auto go = [&](auto kernel) -> cudaError_t {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    kernel<<<groups, 160, smem, st>>>(p);
+    return cudaSuccess;
+  };
+  if (vert) return rev ? go(bwd_tma_kernel<LT, true, true>) : go(bwd_tma_kernel<LT, true, false>);
+  return rev ? go(bwd_tma_kernel<LT, false, true>) : go(bwd_tma_kernel<LT, false, false>);
+}
 
 }  // namespace
 
@@ -448,11 +785,11 @@ int backward_slots(int H, int W, int L, int D, int nimg) {
 }
 
 cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,
-                                 float factor, cudaStream_t st) {
+                                 float factor, int cp_scheme, cudaStream_t st) {
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   ProfScope prof(kProfElementwise, st);
-  backward_init_kernel<<<(int)blocks, 256, 0, st>>>(dcost, dunary, dm, n, D, factor);
+  backward_init_kernel<<<(int)blocks, 256, 0, st>>>(dcost, dunary, dm, n, D, factor, cp_scheme);
   count_launch();
   return cudaGetLastError();
 }
@@ -463,10 +800,14 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
   if (total == 0) return cudaSuccess;
   const int L = p.L, LS = L | 1;
   ProfScope prof(kProfBwdSweep, st);
-  if (L <= 32) {
+  if (L <= 32 && bwd_tma_eligible(p)) {
+    p.tma_stages = 3;
+    cudaError_t e = L == 21 ? launch_bwd_tma<21>(p, st) : launch_bwd_tma<0>(p, st);
+    if (e != cudaSuccess) return e;
+  } else if (L <= 32) {
     const int wpb = total >= 148 * 32 ? 4 : 1;
-    const size_t smem =
-        ((size_t)((L * LS + 3) & ~3) + (size_t)wpb * bwd_warp_floats(L, p.ctx_rank)) * sizeof(float);
+    const size_t smem = ((size_t)((L * LS + 3) & ~3) + (size_t)wpb * bwd_warp_floats(L, p.ctx_rank, p.cp_scheme)) *
+                        sizeof(float);
     auto go = [&](auto kernel) -> cudaError_t {
       if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -475,7 +816,13 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
       kernel<<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
       return cudaSuccess;
     };
-    cudaError_t e = p.D == 4 ? go(bwd_warp_kernel<4>) : p.D == 8 ? go(bwd_warp_kernel<8>) : go(bwd_warp_kernel<0>);
+    cudaError_t e;
+    if (p.cp_scheme) {
+      e = go(bwd_warp_kernel<0, true>);
+    } else {
+      e = p.D == 4 ? go(bwd_warp_kernel<4, false>) : p.D == 8 ? go(bwd_warp_kernel<8, false>)
+                                                              : go(bwd_warp_kernel<0, false>);
+    }
     if (e != cudaSuccess) return e;
   } else {
     const int NT = ((L + 31) / 32) * 32;
@@ -492,11 +839,15 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_dctx_reduce(const float* part, int n_slots, int L, int rank, int keep_diag,
-                               float* dctx, cudaStream_t st) {
+cudaError_t launch_dctx_reduce(float* part, int n_slots, int L, int rank, int keep_diag, float* dctx,
+                               cudaStream_t st) {
   (void)keep_diag;  // the diagonal is filtered where the table is accumulated
   const int CT = rank == 2 ? L * L : L;
-  dctx_reduce_kernel<<<(CT + 127) / 128, 128, 0, st>>>(part, n_slots, L, rank, dctx);
+  if (n_slots > kRedChunks) {
+    dctx_reduce1_kernel<<<dim3((CT + 127) / 128, kRedChunks), 128, 0, st>>>(part, n_slots, CT);
+    count_launch();
+  }
+  dctx_reduce2_kernel<<<(CT + 127) / 128, 128, 0, st>>>(part, n_slots, L, rank, dctx);
   count_launch();
   return cudaGetLastError();
 }

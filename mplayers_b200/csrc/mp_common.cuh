@@ -113,6 +113,14 @@ struct BwdParams {
   int ctx_rank, keep_diag;
   int dir;
   int table_in_smem;      // CTA kernel: 1 = [L][L|1] table in shared memory
+  // Gradient bookkeeping.  cp_scheme == 0: `dunary` and the D slices of `dm_acc` are updated with
+  // one reduction each per pixel (the reference's UpdateUnaryKernelBack).  cp_scheme == 1 (TRWP,
+  // L <= 32): the message gradients are kept as dM_k = C + P_k with the common part C stored in
+  // `dunary` (dU and every dM_k receive the same increment rho*q) and P_k in `dm_read`; a sweep
+  // then rewrites C and P_dir and corrects P_inv only.
+  int cp_scheme;
+  int tma_stages;
+  int* status;            // device word: 0 = ok, else the code of a wait that gave up
 };
 
 __device__ __forceinline__ float ctx_value(const float* ctx, int rank, int L, int c, int f) {
@@ -206,9 +214,9 @@ cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, 
                              long long npix, int L, int D, long long slice, float factor,
                              int min_a_dir, cudaStream_t st);
 cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,
-                                 float factor, cudaStream_t st);
+                                 float factor, int cp_scheme, cudaStream_t st);
 cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
-cudaError_t launch_dctx_reduce(const float* part, int n_slots, int L, int rank, int keep_diag,
+cudaError_t launch_dctx_reduce(float* part, int n_slots, int L, int rank, int keep_diag,
                                float* dctx, cudaStream_t st);
 int backward_slots(int H, int W, int L, int D, int nimg);
 void count_launch(int n = 1);
