@@ -44,39 +44,59 @@ __device__ __forceinline__ void warp_sum2(float& a, float& b) {
   }
 }
 
-// q[f] = sum over labels c whose saved argmin is f of t[c], for f = `me`; fixed summation order.
-// tb / ib: the t values and argmin indices of all labels of this pixel in shared memory.
+__device__ __forceinline__ float eq_flag(float a, float b) {
+  float d;
+  asm("set.eq.f32.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));  // 1.0f if a == b else 0.0f
+  return d;
+}
+
+// q[f] = sum over labels c whose saved argmin is f of t[c], for f = `me`; fixed summation order
+// (three interleaved partial sums).  tb / ib: the t values and argmin indices (stored as floats)
+// of all labels of this pixel in shared memory.  One compare-to-flag plus one fused multiply-add
+// per label: compare/select instructions issue at half the rate of multiply-adds.
 template <int LT>
-__device__ __forceinline__ float gather_q(const float* tb, const int* ib, int L, int me) {
+__device__ __forceinline__ float gather_q(const float* tb, const float* ib, int L, float me) {
   float q0 = 0.f, q1 = 0.f, q2 = 0.f;
   if constexpr (LT > 0) {
     constexpr int NV = (LT + 3) / 4;
-    float tv[NV * 4];
-    int iv[NV * 4];
+    float tv[NV * 4], iv[NV * 4];
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       const float4 a = reinterpret_cast<const float4*>(tb)[v];
-      const int4 b = reinterpret_cast<const int4*>(ib)[v];
+      const float4 b = reinterpret_cast<const float4*>(ib)[v];
       tv[4 * v] = a.x, tv[4 * v + 1] = a.y, tv[4 * v + 2] = a.z, tv[4 * v + 3] = a.w;
       iv[4 * v] = b.x, iv[4 * v + 1] = b.y, iv[4 * v + 2] = b.z, iv[4 * v + 3] = b.w;
     }
 #pragma unroll
     for (int c = 0; c < LT; ++c) {
-      const float add = iv[c] == me ? tv[c] : 0.f;
-      if (c % 3 == 0) q0 += add;
-      if (c % 3 == 1) q1 += add;
-      if (c % 3 == 2) q2 += add;
+      const float fl = eq_flag(iv[c], me);
+      if (c % 3 == 0) q0 = fmaf(fl, tv[c], q0);
+      if (c % 3 == 1) q1 = fmaf(fl, tv[c], q1);
+      if (c % 3 == 2) q2 = fmaf(fl, tv[c], q2);
     }
   } else {
     int c = 0;
     for (; c + 2 < L; c += 3) {
-      q0 += ib[c] == me ? tb[c] : 0.f;
-      q1 += ib[c + 1] == me ? tb[c + 1] : 0.f;
-      q2 += ib[c + 2] == me ? tb[c + 2] : 0.f;
+      q0 = fmaf(eq_flag(ib[c], me), tb[c], q0);
+      q1 = fmaf(eq_flag(ib[c + 1], me), tb[c + 1], q1);
+      q2 = fmaf(eq_flag(ib[c + 2], me), tb[c + 2], q2);
     }
-    for (; c < L; ++c) q0 += ib[c] == me ? tb[c] : 0.f;
+    for (; c < L; ++c) q0 = fmaf(eq_flag(ib[c], me), tb[c], q0);
   }
   return (q0 + q1) + q2;
+}
+
+// Sum of n consecutive floats (n = LT when known at compile time).
+template <int LT>
+__device__ __forceinline__ float row_sum(const float* row, int L) {
+  float s = 0.f;
+  if constexpr (LT > 0) {
+#pragma unroll
+    for (int c = 0; c < LT; ++c) s += row[c];
+  } else {
+    for (int c = 0; c < L; ++c) s += row[c];
+  }
+  return s;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -114,12 +134,12 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
   float* ring2 = ring + kRB * kRS;                                              // CP: P_dir rows
   float* dtile = ring + (CP ? 2 : 1) * kRB * kRS;                               // [32][kRS]
   float* ts = dtile + 32 * kRS;                                                 // [2][32]
-  int* is = reinterpret_cast<int*>(ts + 64);                                    // [2][32]
+  float* is = ts + 64;                                                          // [2][32] argmin as float
   float* acc = ts + 128;                                                        // context-gradient table
   const bool act = lane < L;
   for (int i = lane; i < tab; i += 32) acc[i] = 0.f;
-  is[lane] = -1;
-  is[32 + lane] = -1;
+  is[lane] = -1.f;
+  is[32 + lane] = -1.f;
 
   const long long ibase = (long long)ch.img * p.H * p.W;
   float* DMrl = p.dm_read + (long long)dir * p.slice + ibase * L + lane;  // dM_dir, or P_dir
@@ -224,11 +244,11 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
             }
             dtile[sl * kRS + lane] = cv * t;
             float* tb = ts + (s & 1) * 32;
-            int* ib = is + (s & 1) * 32;
+            float* ib = is + (s & 1) * 32;
             tb[lane] = t;
-            if (act) ib[lane] = f;
+            if (act) ib[lane] = (float)f;
             __syncwarp();
-            qn = gather_q<0>(tb, ib, L, lane);
+            qn = gather_q<0>(tb, ib, L, (float)lane);
           }
           if (act) {
             if (CP) {
@@ -296,8 +316,8 @@ constexpr int kBK = 16;
 constexpr int kDS = 33;  // row stride of the per-stage product tile
 
 __host__ __device__ inline int bwd_tma_warp_floats(int L, int rank) {
-  const int tab = rank == 2 ? L * (L | 1) : 32;
-  return kBK * kDS + 128 + ((tab + 3) & ~3);
+  (void)rank;  // the per-chain table is kept per (c, f) pair for both context conventions
+  return kBK * kDS + 128 + ((L * (L | 1) + 3) & ~3);
 }
 
 template <int LT, bool VERT, bool REV>
@@ -383,12 +403,9 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
   const int lc = act ? lane : L - 1;  // idle lanes mirror the last label (stores hit the same address)
   float* dtile = wbase + wc * bwd_tma_warp_floats(L, p.ctx_rank);  // [kBK][kDS]
   float* ts = dtile + kBK * kDS;                                   // [2][32]
-  int* is = reinterpret_cast<int*>(ts + 64);                       // [2][32]
-  float* acc = ts + 128;
-  const int tab = p.ctx_rank == 2 ? L * LS : 32;
-  for (int i = lane; i < tab; i += 32) acc[i] = 0.f;
-  is[lane] = -1;
-  is[32 + lane] = -1;
+  float* is = ts + 64;                                             // [2][32] argmin as float
+  float* acc = ts + 128;                                           // [L][LS], row c private to lane c
+  for (int i = lane; i < L * LS; i += 32) acc[i] = 0.f;
   __syncwarp();
 
   int img, fix;
@@ -415,6 +432,7 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
   const int nsteps = len - 1;  // steps that have a predecessor pixel
   const bool diag_ok = p.keep_diag != 0;
   const bool rank2 = p.ctx_rank == 2;
+  const float mef = (float)lc;
 
   float q = 0.f;
   // per-stage scalars, lane j < kBK: step kBK*s + j
@@ -429,10 +447,16 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
     }
   };
   auto load_idx = [&](int s, int (&fi)[kBK]) {
+    if ((s + 1) * kBK <= nsteps) {  // every step of the stage has a predecessor: no per-load checks
+      const uint8_t* b = MIl + (px0 + s * kBK * pstep) * L;
 #pragma unroll
-    for (int u = 0; u < kBK; ++u) {
-      const int st = s * kBK + u;
-      fi[u] = st < nsteps ? (int)MIl[(px0 + st * pstep) * L] : -1;
+      for (int u = 0; u < kBK; ++u) fi[u] = (int)b[u * pstep * L];
+    } else {
+#pragma unroll
+      for (int u = 0; u < kBK; ++u) {
+        const int st = s * kBK + u;
+        fi[u] = st < nsteps ? (int)MIl[(px0 + st * pstep) * L] : 0;
+      }
     }
   };
   float e_st, e_nx;
@@ -455,17 +479,13 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
       const float cv = ctab[lc * LS + f];
       dtile[k * kDS + lane] = cv * tt;
       const float et = (lc != f || diag_ok) ? e * tt : 0.f;
-      if (rank2) {
-        acc[lc * LS + f] += et;  // idle lanes repeat lane L-1's read-modify-write in lockstep
-      } else if (act) {
-        atomicAdd(acc + (lc > f ? lc - f : f - lc), et);
-      }
+      acc[lc * LS + f] += et;  // idle lanes repeat lane L-1's read-modify-write in lockstep
       float* tb = ts + (k & 1) * 32;
-      int* ib = is + (k & 1) * 32;
+      float* ib = is + (k & 1) * 32;
       tb[lane] = tt;
-      ib[lane] = f;
+      ib[lane] = (float)f;
       __syncwarp();
-      qn = gather_q<LT>(tb, ib, L, lc);
+      qn = gather_q<LT>(tb, ib, L, mef);
     }
     const float cnew = cval + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
     const int of = px * L;
@@ -495,7 +515,12 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
     float S_st = 0.f;
     if (lane < npix) {
       const float* row = t0p + lane * sk;
-      for (int c = 0; c < L; ++c) S_st += row[c] + row[sa + c];
+      if constexpr (LT > 0) {
+#pragma unroll
+        for (int c = 0; c < LT; ++c) S_st += row[c] + row[sa + c];
+      } else {
+        for (int c = 0; c < L; ++c) S_st += row[c] + row[sa + c];
+      }
     }
     const float* tl = t0p + lc;
     const int pxs = px0 + s * kBK * pstep;
@@ -509,12 +534,8 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
     }
     // edge-weight gradients of this stage: lane j sums row j of the product tile
     __syncwarp();
-    if (DE && lane < kBK && s * kBK + lane < nsteps) {
-      const float* row = dtile + lane * kDS;
-      float de = 0.f;
-      for (int c = 0; c < L; ++c) de += row[c];
-      atomicAdd(DE + (pxs + lane * pstep), de);
-    }
+    if (DE && lane < kBK && s * kBK + lane < nsteps)
+      atomicAdd(DE + (pxs + lane * pstep), row_sum<LT>(dtile + lane * kDS, L));
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[slot]);
     e_st = e_nx;
@@ -529,11 +550,16 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
   float* part = p.dctx_part + (long long)(gchain % p.n_slots) * (rank2 ? L * L : L);
   if (rank2) {
     for (int i = lane; i < L * L; i += 32) {
-      const float v = acc[(i / L) * LS + (i % L)];
+      const int c = i / L, f = i - c * L;
+      const float v = acc[c * LS + f];
       if (v != 0.f) atomicAdd(part + i, v);
     }
-  } else if (act) {
-    const float v = acc[lane];
+  } else if (act) {  // rank 1: lane k folds every (c, f) with |c - f| == k, in a fixed order
+    float v = 0.f;
+    for (int c = 0; c < L; ++c) {
+      if (c - lane >= 0) v += acc[c * LS + c - lane];
+      if (lane > 0 && c + lane < L) v += acc[c * LS + c + lane];
+    }
     if (v != 0.f) atomicAdd(part + lane, v);
   }
 }
