@@ -6,6 +6,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -14,6 +15,65 @@
 #include "mp_common.cuh"
 
 namespace mpl {
+int tma_stage_override() {
+  static const int v = [] {
+    const char* e = getenv("MPL_TMA_STAGES");
+    const int n = e ? atoi(e) : 0;
+    return (n >= 2 && n <= 8) ? n : 0;
+  }();
+  return v;
+}
+bool encode_tmap_2d(CUtensorMap* m, const void* base, unsigned long long inner, unsigned long long rows,
+                    unsigned box_inner, unsigned box_rows) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeFn>(f);
+  }();
+  if (!fn) return false;
+  // A descriptor depends only on (address, shape, box); encoding costs tens of microseconds on the
+  // host, so the last few are kept (training loops present the same buffers again and again).
+  struct Entry {
+    const void* base;
+    unsigned long long inner, rows;
+    unsigned bi, br;
+    CUtensorMap map;
+  };
+  static std::mutex mu;
+  static Entry cache[32];
+  static int n_cached = 0, next_slot = 0;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    for (int i = 0; i < n_cached; ++i) {
+      const Entry& e = cache[i];
+      if (e.base == base && e.inner == inner && e.rows == rows && e.bi == box_inner && e.br == box_rows) {
+        *m = e.map;
+        return true;
+      }
+    }
+  }
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {inner * sizeof(float)};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  if (fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  std::lock_guard<std::mutex> lk(mu);
+  Entry& e = cache[next_slot];
+  e.base = base, e.inner = inner, e.rows = rows, e.bi = box_inner, e.br = box_rows, e.map = *m;
+  next_slot = (next_slot + 1) % 32;
+  if (n_cached < 32) ++n_cached;
+  return true;
+}
+
 static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 

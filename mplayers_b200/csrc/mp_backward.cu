@@ -321,7 +321,12 @@ __host__ __device__ inline int bwd_tma_warp_floats(int L, int rank) {
 }
 
 template <int LT, bool VERT, bool REV>
-__global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__ BwdParams p,
+                                                         const __grid_constant__ TmaMaps maps) {
+  // No static shared memory in this kernel: the dynamic region starts at the CTA's shared window
+  // base, which satisfies the 128-byte alignment the tiled TMA destination needs.  (Rounding the
+  // pointer up by hand would hide its address space from the compiler and turn every shared
+  // access into a slower generic one.)
   extern __shared__ __align__(128) float smem[];
   const int L = LT ? LT : p.L, H = p.H, W = p.W, NS = p.tma_stages;
   const int LS = L | 1;
@@ -372,25 +377,25 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
       }
       const int npix = len - s * kBK < kBK ? len - s * kBK : kBK;
       float* T = tiles + slot * tile_floats;
-      if (lane == 0) {
-        const unsigned bytes = VERT ? (unsigned)npix * 2u * row_bytes : (unsigned)nact * (unsigned)npix * 8u * L;
-        mbar_arrive_expect_tx(&full[slot], bytes);
-      }
-      __syncwarp();
-      const int ncopy = (VERT ? npix : nact) * 2;
-      for (int c = lane; c < ncopy; c += 32) {
-        const int qd = c >> 1, a = c & 1;
-        long long pix;
-        if (VERT) {
-          const int h = REV ? H - 1 - (s * kBK + qd) : s * kBK + qd;
-          pix = ((long long)img0 * H + h) * W + w0;
-        } else {
-          const int wlo = REV ? W - s * kBK - npix : s * kBK;
-          pix = (long long)(chain0 + qd) * W + wlo;
+      if (VERT) {
+        // 2-D tiled TMA: one copy per array brings kBK image rows of the 4-pixel column group
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full[slot], 2u * kBK * row_bytes);
+          const int y0 = img0 * H + (REV ? H - (s + 1) * kBK : s * kBK);
+          tma_load_2d(T, &maps.a, w0 * L, y0, &full[slot]);
+          tma_load_2d(T + kBK * 4 * L, &maps.b, w0 * L, dir * p.nimg * H + y0, &full[slot]);
         }
-        const float* src = (a == 0 ? p.dunary : p.dm_read + (long long)dir * p.slice) + pix * L;
-        float* dst = VERT ? T + (a * kBK + qd) * 4 * L : T + (qd * 2 + a) * kBK * L;
-        bulk_g2s(dst, src, VERT ? row_bytes : (unsigned)npix * 4u * L, &full[slot]);
+      } else {
+        if (lane == 0) mbar_arrive_expect_tx(&full[slot], (unsigned)nact * (unsigned)npix * 8u * L);
+        __syncwarp();
+        const int ncopy = nact * 2;
+        for (int c = lane; c < ncopy; c += 32) {
+          const int qd = c >> 1, a = c & 1;
+          const int wlo = REV ? W - s * kBK - npix : s * kBK;
+          const long long pix = (long long)(chain0 + qd) * W + wlo;
+          const float* src = (a == 0 ? p.dunary : p.dm_read + (long long)dir * p.slice) + pix * L;
+          bulk_g2s(T + (qd * 2 + a) * kBK * L, src, (unsigned)npix * 4u * L, &full[slot]);
+        }
       }
     }
     return;
@@ -426,7 +431,7 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
   const uint8_t* NI = p.norm_idx + ibase;
   const float rho = p.rho;
   const int sa = VERT ? kBK * 4 * L : kBK * L;        // C -> P_dir inside a tile
-  const int sk = VERT ? 4 * L : (REV ? -L : L);        // consecutive steps inside a tile
+  const int sk = (VERT ? 4 * L : L) * (REV ? -1 : 1);  // consecutive steps inside a tile
   const int pstep = VERT ? (REV ? -W : W) : (REV ? -1 : 1);
   const int px0 = VERT ? (REV ? H - 1 : 0) * W + fix : fix * W + (REV ? W - 1 : 0);  // first step
   const int nsteps = len - 1;  // steps that have a predecessor pixel
@@ -506,8 +511,8 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
     const int npix = len - s * kBK < kBK ? len - s * kBK : kBK;
     const float* T = tiles + slot * tile_floats;
     const float* t0p;
-    if (VERT) {
-      t0p = T + wc * L;
+    if (VERT) {  // box rows ascend in memory; a downward walk starts at the last row of the box
+      t0p = T + wc * L + (REV ? (kBK - 1) * 4 * L : 0);
     } else {
       t0p = T + wc * 2 * kBK * L + (REV ? (npix - 1) * L : 0);
     }
@@ -770,7 +775,7 @@ constexpr int kSmemTableMaxL = 128;  // rank-2 table L*(L|1) floats fits next to
 size_t bwd_tma_smem_bytes(int L, int rank, int stages) {
   return ((size_t)stages * 2 * kBK * 4 * L + ((L * (L | 1) + 3) & ~3) + 4 * (size_t)bwd_tma_warp_floats(L, rank)) *
              sizeof(float) +
-         2 * stages * 8 + 16;
+         2 * stages * 8 + 16 + 128;
 }
 
 bool bwd_tma_eligible(const BwdParams& p) {
@@ -786,12 +791,19 @@ cudaError_t launch_bwd_tma(const BwdParams& p, cudaStream_t st) {
   const bool rev = (p.dir & 1) == 0;  // forward walk upwards -> backward walk downwards
   const int groups = vert ? p.nimg * (p.W >> 2) : (p.nimg * p.H + 3) >> 2;
   const size_t smem = bwd_tma_smem_bytes(p.L, p.ctx_rank, p.tma_stages);
+  TmaMaps maps{};
+  if (vert) {
+    const unsigned long long inner = (unsigned long long)p.W * p.L, rows = (unsigned long long)p.nimg * p.H;
+    if (!encode_tmap_2d(&maps.a, p.dunary, inner, rows, 4 * p.L, kBK) ||
+        !encode_tmap_2d(&maps.b, p.dm_read, inner, rows * p.D, 4 * p.L, kBK))
+      return cudaErrorNotSupported;
+  }
   auto go = [&](auto kernel) -> cudaError_t {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return e;
     }
-    kernel<<<groups, 160, smem, st>>>(p);
+    kernel<<<groups, 160, smem, st>>>(p, maps);
     return cudaSuccess;
   };
   if (vert) return rev ? go(bwd_tma_kernel<LT, true, true>) : go(bwd_tma_kernel<LT, true, false>);
@@ -827,7 +839,7 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
   const int L = p.L, LS = L | 1;
   ProfScope prof(kProfBwdSweep, st);
   if (L <= 32 && bwd_tma_eligible(p)) {
-    p.tma_stages = 3;
+    p.tma_stages = tma_stage_override() ? tma_stage_override() : 4;
     cudaError_t e = L == 21 ? launch_bwd_tma<21>(p, st) : launch_bwd_tma<0>(p, st);
     if (e != cudaSuccess) return e;
   } else if (L <= 32) {

@@ -1,5 +1,6 @@
 // Shared device/host helpers of the TRWP / ISGMR kernels (sm_100a).
 #pragma once
+#include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through the runtime)
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -197,6 +198,29 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     if (clock64() - t0 > 2000000000ll) return false;
   }
 }
+// Tensor maps of the vertical-direction kernels (2-D tiled TMA: one copy brings kTK image rows of
+// a four-pixel-wide column group).  Passed as a __grid_constant__ kernel parameter.
+struct alignas(64) TmaMaps {
+  CUtensorMap a;  // forward: unary            backward: C (dunary)
+  CUtensorMap b;  // forward: message slices   backward: P (message-gradient slices)
+  CUtensorMap c;  // forward: edge weights
+};
+// Encodes a 2-D fp32 map: `inner` contiguous floats per row, `rows` rows, box = box_inner x box_rows.
+// Returns false if the driver entry point is unavailable or the encode fails.
+bool encode_tmap_2d(CUtensorMap* m, const void* base, unsigned long long inner, unsigned long long rows,
+                    unsigned box_inner, unsigned box_rows);
+
+// 2-D tiled TMA load (no multicast): box at (x, y) -> shared memory, completion in bytes on `bar`.
+// dst 128-byte aligned; x * 4 bytes a multiple of 16.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // Global -> shared bulk copy (no multicast), completion counted in bytes on `bar`.
 // dst, src 16-byte aligned; bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
@@ -219,6 +243,7 @@ cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
 cudaError_t launch_dctx_reduce(float* part, int n_slots, int L, int rank, int keep_diag,
                                float* dctx, cudaStream_t st);
 int backward_slots(int H, int W, int L, int D, int nimg);
+int tma_stage_override();  // MPL_TMA_STAGES environment variable (tuning knob), 0 = not set
 void count_launch(int n = 1);
 
 // Optional per-launch timing (mpl_profile_enable): CUDA events recorded on the launching stream

@@ -265,7 +265,12 @@ constexpr int kTK = 16;
 // LT = compile-time label count (0: runtime, up to LMAX = 32); FWD = the chain walks towards
 // increasing coordinates (directions 0 and 2).
 template <int LMAX, int LT, int DT, bool TRAIN, bool VERT, bool FWD>
-__global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__ FwdParams p,
+                                                         const __grid_constant__ TmaMaps maps) {
+  // No static shared memory in this kernel: the dynamic region starts at the CTA's shared window
+  // base, which satisfies the 128-byte alignment the tiled TMA destination needs.  (Rounding the
+  // pointer up by hand would hide its address space from the compiler and turn every shared
+  // access into a slower generic one.)
   extern __shared__ __align__(128) float smem[];
   constexpr int A = DT + 1;   // staged arrays: unary + D message slices
   constexpr int AE = A + 1;   // ... + edge weights
@@ -316,31 +321,34 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
       const int npix = len - s * kTK < kTK ? len - s * kTK : kTK;
       float* T = tiles + slot * tile_floats;
       float* ET = etiles + slot * 64;
-      if (lane == 0) {
-        const unsigned bytes = VERT ? (unsigned)npix * (A * row_bytes + (has_e ? 16u : 0u))
-                                    : (unsigned)nact * (unsigned)npix * (A * 4u * L + (has_e ? 4u : 0u));
-        mbar_arrive_expect_tx(&full[slot], bytes);
-      }
-      __syncwarp();
-      const int ncopy = (VERT ? npix : nact) * AE;
-      for (int c = lane; c < ncopy; c += 32) {
-        const int q = c / AE, a = c - q * AE;
-        long long pix;  // first pixel of the segment, over all images
-        if (VERT) {
-          const int h = FWD ? s * kTK + q : H - 1 - (s * kTK + q);
-          pix = ((long long)img0 * H + h) * W + w0;
-        } else {
-          const int wlo = FWD ? s * kTK : W - s * kTK - npix;
-          pix = (long long)(chain0 + q) * W + wlo;
+      if (VERT) {
+        // 2-D tiled TMA: one copy per staged array brings kTK image rows of the 4-pixel column
+        // group (box 4L x kTK).  Rows outside the tensor read as zero, rows of a neighbouring image
+        // are never used; the full box is always transferred.
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full[slot], (unsigned)(A * kTK * row_bytes + (has_e ? kTK * 16u : 0u)));
+          const int y0 = img0 * H + (FWD ? s * kTK : H - (s + 1) * kTK);
+          tma_load_2d(T, &maps.a, w0 * L, y0, &full[slot]);
+#pragma unroll
+          for (int a = 1; a < A; ++a)
+            tma_load_2d(T + a * kTK * 4 * L, &maps.b, w0 * L, (a - 1) * p.nimg * H + y0, &full[slot]);
+          if (has_e) tma_load_2d(ET, &maps.c, w0, dir * p.nimg * H + y0, &full[slot]);
         }
-        if (a < A) {
-          const float* src = (a == 0 ? p.unary : p.msg_read + (long long)(a - 1) * p.slice) + pix * L;
-          float* dst = VERT ? T + (a * kTK + q) * 4 * L : T + (q * A + a) * kTK * L;
-          bulk_g2s(dst, src, VERT ? row_bytes : (unsigned)npix * 4u * L, &full[slot]);
-        } else if (has_e) {
-          const float* src = p.ew + (long long)dir * p.pslice + pix;
-          float* dst = VERT ? ET + q * 4 : ET + q * kTK;
-          bulk_g2s(dst, src, VERT ? 16u : (unsigned)npix * 4u, &full[slot]);
+      } else {
+        if (lane == 0)
+          mbar_arrive_expect_tx(&full[slot], (unsigned)nact * (unsigned)npix * (A * 4u * L + (has_e ? 4u : 0u)));
+        __syncwarp();
+        const int ncopy = nact * AE;
+        for (int c = lane; c < ncopy; c += 32) {
+          const int q = c / AE, a = c - q * AE;
+          const int wlo = FWD ? s * kTK : W - s * kTK - npix;
+          const long long pix = (long long)(chain0 + q) * W + wlo;  // first pixel, over all images
+          if (a < A) {
+            const float* src = (a == 0 ? p.unary : p.msg_read + (long long)(a - 1) * p.slice) + pix * L;
+            bulk_g2s(T + (q * A + a) * kTK * L, src, (unsigned)npix * 4u * L, &full[slot]);
+          } else if (has_e) {
+            bulk_g2s(ET + q * kTK, p.ew + (long long)dir * p.pslice + pix, (unsigned)npix * 4u, &full[slot]);
+          }
         }
       }
     }
@@ -378,8 +386,8 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
     for (int i = lane; i < NS * 64; i += 32) etiles[i] = 1.f;
   __syncwarp();
   const int sa = VERT ? kTK * 4 * L : kTK * L;        // stride between staged arrays
-  const int sk = VERT ? 4 * L : (FWD ? L : -L);        // stride between consecutive chain pixels
-  const int ek = VERT ? 4 : (FWD ? 1 : -1);
+  const int sk = (VERT ? 4 * L : L) * (FWD ? 1 : -1);  // stride between consecutive chain pixels
+  const int ek = (VERT ? 4 : 1) * (FWD ? 1 : -1);
   const int pstep = VERT ? (FWD ? W : -W) : (FWD ? 1 : -1);
   const int px0 = VERT ? (FWD ? 0 : H - 1) * W + fix : fix * W + (FWD ? 0 : W - 1);  // chain pixel 0
   const int dir_off = (1 + dir) * sa, inv_off = (1 + inv) * sa;
@@ -431,9 +439,9 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
     const float* ET = etiles + slot * 64;
     const float* t0;
     const float* e0;
-    if (VERT) {
-      t0 = T + wc * L;
-      e0 = ET + wc;
+    if (VERT) {  // box rows ascend in memory; a downward walk starts at the last row of the box
+      t0 = T + wc * L + (FWD ? 0 : (kTK - 1) * 4 * L);
+      e0 = ET + wc + (FWD ? 0 : (kTK - 1) * 4);
     } else {
       t0 = T + wc * A * kTK * L + (FWD ? 0 : (npix - 1) * L);
       e0 = ET + wc * kTK + (FWD ? 0 : npix - 1);
@@ -714,7 +722,7 @@ cudaError_t launch_warp(const FwdParams& p, cudaStream_t st) {
 }
 
 size_t tma_smem_bytes(int L, int D, int stages) {
-  return ((size_t)stages * ((size_t)(D + 1) * kTK * 4 * L + 64) + 4 * 64) * sizeof(float) + 2 * stages * 8 + 16;
+  return ((size_t)stages * ((size_t)(D + 1) * kTK * 4 * L + 64) + 4 * 64) * sizeof(float) + 2 * stages * 8 + 16 + 128;
 }
 
 // Can direction `dir` of this problem use the bulk-copy kernel?  Needs 16-byte aligned row segments.
@@ -723,8 +731,8 @@ bool tma_eligible(const FwdParams& p, int dir, int* stages) {
   if ((p.W & 3) || (((long long)p.W * p.L) & 3)) return false;
   const uintptr_t bits = (uintptr_t)p.unary | (uintptr_t)p.msg_read | (uintptr_t)p.ew;
   if (bits & 15) return false;
-  int ns = 3;
-  while (ns >= 2 && tma_smem_bytes(p.L, p.D, ns) > (ns == 3 ? 100 : 200) * 1024) --ns;
+  int ns = tma_stage_override() ? tma_stage_override() : 4;
+  while (ns >= 2 && tma_smem_bytes(p.L, p.D, ns) > (ns >= 3 ? 110 : 200) * 1024) --ns;
   if (ns < 2) return false;
   *stages = ns;
   return true;
@@ -739,8 +747,16 @@ cudaError_t launch_tma_v(FwdParams p, int dir, int stages, cudaStream_t st) {
   const size_t smem = tma_smem_bytes(p.L, p.D, stages);
   cudaError_t e = ensure_smem(fwd_tma_kernel<LMAX, LT, DT, TRAIN, VERT, FWD>, smem);
   if (e != cudaSuccess) return e;
+  TmaMaps maps{};
+  if (VERT) {
+    const unsigned long long inner = (unsigned long long)p.W * p.L, rows = (unsigned long long)p.nimg * p.H;
+    bool ok = encode_tmap_2d(&maps.a, p.unary, inner, rows, 4 * p.L, kTK) &&
+              encode_tmap_2d(&maps.b, p.msg_read, inner, rows * p.D, 4 * p.L, kTK);
+    if (ok && p.ew) ok = encode_tmap_2d(&maps.c, p.ew, (unsigned long long)p.W, rows * p.D, 4, kTK);
+    if (!ok) return cudaErrorNotSupported;
+  }
   ProfScope prof(kProfFwdSweep, st);
-  fwd_tma_kernel<LMAX, LT, DT, TRAIN, VERT, FWD><<<groups, 160, smem, st>>>(p);
+  fwd_tma_kernel<LMAX, LT, DT, TRAIN, VERT, FWD><<<groups, 160, smem, st>>>(p, maps);
   count_launch();
   return cudaGetLastError();
 }
