@@ -102,6 +102,30 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
                        float* dedge_weights, float* dmsg, float* dmsg_update, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* TRWP backward without any device allocation.  It has no counterpart in the reference.
+ *
+ * Same computation and arguments as mpl_trwp_backward, minus the workspace: the scratch (partial
+ * label-context tables, one per chain, and a status word) is a fixed array of
+ * mpl_static_scratch_bytes() = 8 MiB that is part of the library image, so every GPU that loads
+ * the library carries it until the process exits.  Meant for callers that must not allocate on the
+ * device at call time -- code running inside a memory pool that is already fully handed out, a
+ * capture-safe or real-time section where cudaMalloc's implicit synchronisation is unacceptable,
+ * a plugin whose host forbids allocator calls.  The function itself calls no cudaMalloc/cudaFree
+ * and no allocating library routine.
+ *   - Problems whose mpl_backward_workspace_bytes() exceeds the 8 MiB are rejected with
+ *     MPL_ERR_UNSUPPORTED and a message naming both sizes (the segmentation configuration, 2 x
+ *     512 x 512 pixels with 21 labels, needs 1.8 MB).
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) with that device current; make that first call outside any stream
+ *     capture.
+ *   - All calls on a device share the one array; each call clears what it uses first, but two
+ *     calls whose kernels overlap on the GPU (different streams) race on it.  Serialise them. */
+size_t mpl_static_scratch_bytes(void);
+int mpl_trwp_backward_static(const mpl_problem* p, const float* context, const float* edge_weights,
+                             const float* dcost_final, const uint8_t* msg_min_index,
+                             const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                             float* dedge_weights, float* dmsg, void* stream);
+
 /* Reads back (synchronously) the device status word of a forward workspace after the forward
  * call that used it: 0 = every kernel ran to completion, otherwise the code of a bounded wait
  * that gave up (101 / 102: staging pipeline of the bulk-copy kernel).  No counterpart in the

@@ -47,6 +47,9 @@ def lib():
         L.mpl_isgmr_forward.argtypes = [pp] + [vp] * 10 + [sz, vp]
         L.mpl_isgmr_backward.restype = ctypes.c_int
         L.mpl_isgmr_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
+        L.mpl_trwp_backward_static.restype = ctypes.c_int
+        L.mpl_trwp_backward_static.argtypes = [pp] + [vp] * 10
+        L.mpl_static_scratch_bytes.restype = sz
         L.mpl_forward_status.restype = ctypes.c_int
         L.mpl_forward_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32)]
         L.mpl_last_error.restype = ctypes.c_char_p

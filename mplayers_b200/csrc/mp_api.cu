@@ -380,6 +380,48 @@ int mpl_forward_status(const void* workspace, int32_t* status) {
   return MPL_OK;
 }
 
+// ---- TRWP backward for callers that cannot allocate device memory ------------------------------
+// The scratch of mpl_trwp_backward (per-chain label-context partial tables + a status word) lives
+// in this file-scope device array instead of a caller-provided workspace.  The array's name is only
+// a host-side handle; kernels need its device address, fetched once per device below.
+#define MPL_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[MPL_STATIC_SCRATCH_BYTES];
+
+size_t mpl_static_scratch_bytes(void) { return MPL_STATIC_SCRATCH_BYTES; }
+
+int mpl_trwp_backward_static(const mpl_problem* p, const float* context, const float* edge_weights,
+                             const float* dcost_final, const uint8_t* msg_min_index,
+                             const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                             float* dedge_weights, float* dmsg, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  const size_t need = mpl_backward_workspace_bytes(p);
+  if (need > MPL_STATIC_SCRATCH_BYTES)
+    return fail(MPL_ERR_UNSUPPORTED,
+                "problem needs %zu bytes of scratch, the built-in scratch holds %u; use mpl_trwp_backward "
+                "with a caller-provided workspace",
+                need, MPL_STATIC_SCRATCH_BYTES);
+  // one-time set-up per device (with that device current): resolve the array's device address
+  static std::mutex mu;
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  MPL_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MPL_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!addr[dev]) {
+      void* ptr = nullptr;
+      MPL_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+      addr[dev] = ptr;
+    }
+    scratch = addr[dev];
+  }
+  // backward_common clears the part of the scratch it uses (partial tables and status word)
+  return backward_common(false, p, context, edge_weights, dcost_final, msg_min_index, msg_norm_index, dunary,
+                         dcontext, dedge_weights, dmsg, nullptr, scratch, MPL_STATIC_SCRATCH_BYTES, stream);
+}
+
 const char* mpl_last_error(void) { return g_err.c_str(); }
 
 int64_t mpl_kernel_launches(void) { return mpl::g_launches.load(std::memory_order_relaxed); }
