@@ -171,9 +171,11 @@ def run_ours(a):
     fn = TRWPFunction if cfg["mode"] == "TRWP" else ISGMRFunction
     args.training = train
 
+    from mplayers_b200 import parallel
+
     def reduce_context_grad():
         if world > 1:  # the only cross-GPU exchange of the batch-sharded layer
-            dist.all_reduce(ctx_param.grad)
+            parallel.allreduce_label_context_grad(ctx_param.grad)
 
     def step_layer(u_hwl, e_dhw, g_hwl):
         """The layer proper: extension-level layouts ([B,cv,H,W,L], [D,B,cv,H,W]), no permutes."""
