@@ -209,6 +209,16 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
   MPL_CUDA(cudaMemsetAsync(fp.status, 0, sizeof(int), st));
   MPL_CUDA(mpl::launch_analyze(context, L, p->context_rank, edge_weights, d.npix * D,
                                static_cast<mpl::CtxInfo*>(workspace), st));
+  if (p->context_rank == 1 && L > 32 && !train) {
+    // Inference with a rank-1 context: the choice of the wide windowed kernel is made on the host,
+    // which costs one small device-to-host copy (the call synchronises with its stream here).
+    mpl::CtxInfo hi;
+    MPL_CUDA(cudaMemcpyAsync(&hi, workspace, sizeof(hi), cudaMemcpyDeviceToHost, st));
+    MPL_CUDA(cudaStreamSynchronize(st));
+    const float ew_min = hi.ew_min_bits >= 0 ? 1.f : -1.f;  // order bits: negative <=> negative float
+    fp.host_windowed = hi.windowed && (edge_weights == nullptr || ew_min >= 0.f);
+    fp.host_R = hi.R;
+  }
 
   const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
   // ISGMR alternates between the two message buffers so that the last iteration writes `msg`.

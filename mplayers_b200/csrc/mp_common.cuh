@@ -92,7 +92,10 @@ struct FwdParams {
   long long pslice;       // nimg*H*W
   float rho;
   int ctx_rank;
-  int tma_stages;         // bulk-copy kernel: ring depth
+  int tma_stages;         // bulk-copy kernels: ring depth
+  int tma_k;              // bulk-copy CTA kernel: chain pixels per stage
+  int host_windowed;      // host copy of the context analysis (rank-1, L > 32): windowed path is exact
+  int host_R;             //   ... and its window half-width
   int dir0, ndirs;        // this launch covers directions dir0 .. dir0+ndirs-1
   int chain_off[17];      // prefix sums of nimg*n_chains over those directions
 };

@@ -468,9 +468,19 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
 // ------------------------------------------------------------------------------------------------
 // L > 32: one CTA per chain, thread = label.
 // ------------------------------------------------------------------------------------------------
-// Block-wide min with the index of the HIGHEST thread attaining it.  One __syncthreads inside.
+// Barrier over the whole CTA (nthreads == 0) or over its first `nthreads` threads (named barrier
+// 1; used where a producer warp of the same CTA must not take part).
+__device__ __forceinline__ void cta_sync(int nthreads) {
+  if (nthreads == 0) {
+    __syncthreads();
+  } else {
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  }
+}
+
+// Block-wide min with the index of the HIGHEST thread attaining it.  One barrier inside.
 __device__ __forceinline__ void block_min_hi(float v, bool act, int tid, float* red_v, int* red_i,
-                                             int nw, float& m, int& n) {
+                                             int nw, float& m, int& n, int bar_threads = 0) {
   const float x = act ? v : kInf;
   const float wm = warp_min(x);
   const unsigned bal = __ballot_sync(0xffffffffu, act && x == wm);
@@ -478,7 +488,7 @@ __device__ __forceinline__ void block_min_hi(float v, bool act, int tid, float* 
     red_v[tid >> 5] = wm;
     red_i[tid >> 5] = bal ? (tid & ~31) + 31 - __clz(bal) : -1;
   }
-  __syncthreads();
+  cta_sync(bar_threads);
   m = kInf;
   n = 0;
   for (int w = 0; w < nw; ++w) {
@@ -488,6 +498,94 @@ __device__ __forceinline__ void block_min_hi(float v, bool act, int tid, float* 
       m = y;
       n = yi;
     }
+  }
+}
+
+// State of the label-context evaluation of one CTA-per-chain kernel instance.
+template <int MODE>
+struct CtaCtx {
+  bool windowed;
+  int R;
+  float cmax;
+  float cr[MODE == 2 ? 64 : 1];
+};
+
+// One chain step of the CTA-per-chain kernels: publishes h, evaluates best[c] = min_f (h[f] +
+// e*ctx(c,f)) with its argmin, and the block-wide normalisation minimum m with its index n.
+// Two block barriers.
+template <int MODE, bool TRAIN>
+__device__ __forceinline__ void cta_minplus(const FwdParams& p, const CtaCtx<MODE>& cc, float h, float e,
+                                            bool act, int c, int L, int nw, float* hbuf, const float* ctx1,
+                                            float* redA_v, int* redA_i, float* redB_v, int* redB_i,
+                                            float& best, int& bi, float& m, int& n, int bar_threads = 0) {
+  if (act) hbuf[c] = h;
+  best = kInf;
+  bi = 0;
+  if (MODE == 1 && cc.windowed) {
+    const int R = cc.R;
+    float hmin;
+    int fstar;
+    block_min_hi(h, act, c, redA_v, redA_i, nw, hmin, fstar, bar_threads);  // also publishes hbuf
+    const float gv = fmaf(e, cc.cmax, hmin);
+    if (fstar >= c + R) {  // scanned before the window in the reference's high-to-low order
+      best = gv;
+      bi = fstar;
+    }
+    int fhi = c + R - 1;
+    if (fhi > L - 1) fhi = L - 1;
+    int flo = c - R + 1;
+    if (flo < 0) flo = 0;
+    for (int f = fhi; f >= flo; --f) {
+      const int k = f > c ? f - c : c - f;
+      const float v = fmaf(e, ctx1[k], hbuf[f]);
+      if (v < best) {
+        best = v;
+        bi = f;
+      }
+    }
+    if (fstar <= c - R && gv < best) {
+      best = gv;
+      bi = fstar;
+    }
+  } else {
+    cta_sync(bar_threads);
+    if constexpr (MODE == 2) {
+      minplus_regrow<64, TRAIN>(hbuf, cc.cr, e, best, bi);
+    } else {
+      for (int f = L - 1; f >= 0; --f) {
+        float cv;
+        if (MODE == 1) {
+          cv = ctx1[f > c ? f - c : c - f];
+        } else {
+          cv = ctx_value(p.ctx, 2, L, c, f);
+        }
+        const float v = fmaf(e, cv, hbuf[f]);
+        if (f == L - 1 || v < best) {
+          best = v;
+          bi = f;
+        }
+      }
+    }
+  }
+  block_min_hi(best, act, c, redB_v, redB_i, nw, m, n, bar_threads);
+}
+
+template <int MODE>
+__device__ __forceinline__ void cta_ctx_init(const FwdParams& p, CtaCtx<MODE>& cc, bool act, int c, int L,
+                                             float* ctx1) {
+  cc.windowed = false;
+  cc.R = 0;
+  cc.cmax = 0.f;
+  if (MODE == 1) {
+    ctx1[c] = act ? __ldg(p.ctx + c) : 0.f;
+    const CtxInfo inf = *p.info;
+    cc.windowed = inf.windowed && (p.ew == nullptr || float_from_order_bits(inf.ew_min_bits) >= 0.f);
+    cc.R = inf.R;
+    cc.cmax = inf.cmax;
+  }
+  if constexpr (MODE == 2) {
+#pragma unroll
+    for (int f = 0; f < 64; ++f) cc.cr[f] = (act && f < L) ? ctx_value(p.ctx, 2, L, c, f) : 0.f;
   }
 }
 
@@ -505,22 +603,8 @@ __global__ void __launch_bounds__(256) fwd_cta_kernel(const __grid_constant__ Fw
   float* redB_v = redA_v + 16;
   int* redB_i = reinterpret_cast<int*>(redB_v + 8);
   const bool act = c < L;
-
-  bool windowed = false;
-  int R = 0;
-  float cmax = 0.f;
-  if (MODE == 1) {
-    ctx1[c] = act ? __ldg(p.ctx + c) : 0.f;
-    const CtxInfo inf = *p.info;
-    windowed = inf.windowed && (p.ew == nullptr || float_from_order_bits(inf.ew_min_bits) >= 0.f);
-    R = inf.R;
-    cmax = inf.cmax;
-  }
-  float cr[MODE == 2 ? 64 : 1];
-  if constexpr (MODE == 2) {
-#pragma unroll
-    for (int f = 0; f < 64; ++f) cr[f] = (act && f < L) ? ctx_value(p.ctx, 2, L, c, f) : 0.f;
-  }
+  CtaCtx<MODE> cc;
+  cta_ctx_init<MODE>(p, cc, act, c, L, ctx1);
   hbuf[c] = kInf;  // entries >= L stay +inf
   __syncthreads();
 
@@ -560,58 +644,9 @@ __global__ void __launch_bounds__(256) fwd_cta_kernel(const __grid_constant__ Fw
     const float e = E ? slot[(D + 1) * NT + c] : 1.f;
     const float uu_next = (act && i < len - 1) ? uu_from_ring(slot, NT, c, D, ch.dir, ch.inv, p.rho) : 0.f;
     const float h = act ? fmaf(p.rho, r, uu) : kInf;
-    if (act) hbuf[c] = h;
-
-    float best = kInf;
-    int bi = 0;
-    if (MODE == 1 && windowed) {
-      float hmin;
-      int fstar;
-      block_min_hi(h, act, c, redA_v, redA_i, nw, hmin, fstar);  // also publishes hbuf
-      const float gv = fmaf(e, cmax, hmin);
-      if (fstar >= c + R) {  // scanned before the window in the reference's high-to-low order
-        best = gv;
-        bi = fstar;
-      }
-      int fhi = c + R - 1;
-      if (fhi > L - 1) fhi = L - 1;
-      int flo = c - R + 1;
-      if (flo < 0) flo = 0;
-      for (int f = fhi; f >= flo; --f) {
-        const int k = f > c ? f - c : c - f;
-        const float v = fmaf(e, ctx1[k], hbuf[f]);
-        if (v < best) {
-          best = v;
-          bi = f;
-        }
-      }
-      if (fstar <= c - R && gv < best) {
-        best = gv;
-        bi = fstar;
-      }
-    } else {
-      __syncthreads();
-      if constexpr (MODE == 2) {
-        minplus_regrow<64, TRAIN>(hbuf, cr, e, best, bi);
-      } else {
-        for (int f = L - 1; f >= 0; --f) {
-          float cv;
-          if (MODE == 1) {
-            cv = ctx1[f > c ? f - c : c - f];
-          } else {
-            cv = ctx_value(p.ctx, 2, L, c, f);
-          }
-          const float v = fmaf(e, cv, hbuf[f]);
-          if (f == L - 1 || v < best) {
-            best = v;
-            bi = f;
-          }
-        }
-      }
-    }
-    float m;
-    int n;
-    block_min_hi(best, act, c, redB_v, redB_i, nw, m, n);
+    float best, m;
+    int bi, n;
+    cta_minplus<MODE, TRAIN>(p, cc, h, e, act, c, L, nw, hbuf, ctx1, redA_v, redA_i, redB_v, redB_i, best, bi, m, n);
     r = best - m;
     const int px = pix0 + i * ch.pstep;
     if (act) Mw[(long long)px * L + c] = r;
@@ -623,6 +658,350 @@ __global__ void __launch_bounds__(256) fwd_cta_kernel(const __grid_constant__ Fw
     uu = uu_next;
   }
   cp_async_wait<0>();
+}
+
+// CTA-per-chain kernel with bulk-copy staging, for L % 4 == 0 (every pixel's label row is then
+// 16-byte aligned, in any direction).  The last warp of the CTA is the producer: per stage of K
+// chain pixels it issues, for each of the D+1 input arrays, either one cp.async.bulk of K*L floats
+// (horizontal chains are contiguous) or K copies of one label row each (all other directions);
+// completion on an mbarrier per stage, bounded waits.  Edge weights are fetched one stage ahead by
+// the first K consumer threads and published through shared memory.
+template <int MODE, bool TRAIN>
+__global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(128) float smem[];
+  ChainCtx ch;
+  if (!decode_chain(p, blockIdx.x, ch)) return;  // uniform for the CTA
+  const int L = p.L, D = p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
+  const int NT = blockDim.x - 32, c = threadIdx.x, nw = NT >> 5;
+  const bool producer = c >= NT;
+  const int tile_floats = A * K * L;
+  float* tiles = smem;                        // [NS][A][K][L]
+  float* etile = tiles + NS * tile_floats;    // [2][K]
+  float* hbuf = etile + 2 * K;                // [NT]
+  float* ctx1 = hbuf + NT;                    // [NT]
+  float* redA_v = ctx1 + NT;                  // [8] + [8] + [8] + [8]
+  int* redA_i = reinterpret_cast<int*>(redA_v + 8);
+  float* redB_v = redA_v + 16;
+  int* redB_i = reinterpret_cast<int*>(redB_v + 8);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(redA_v + 32);  // [NS]
+  unsigned long long* empty = full + NS;                                          // [NS]
+  const bool act = c < L;
+
+  const int len = ch.len;
+  const int nstages = (len + K - 1) / K;
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  const int pix0 = ch.h0 * p.W + ch.w0;
+  const bool contiguous = (ch.pstep == 1 || ch.pstep == -1);
+
+  if (c == 0) {
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  CtaCtx<MODE> cc;
+  if (!producer) {
+    cta_ctx_init<MODE>(p, cc, act, c, L, ctx1);
+    hbuf[c] = kInf;  // entries >= L stay +inf
+  }
+  __syncthreads();
+
+  if (producer) {
+    const int lane = c - NT;
+    const float* U = p.unary + ibase * L;
+    const float* Mr = p.msg_read + ibase * L;
+    for (int s = 0; s < nstages; ++s) {
+      const int slot = s % NS;
+      if (s >= NS && !mbar_wait(&empty[slot], ((s / NS) - 1) & 1)) {
+        if (lane == 0) atomicExch(p.status, 111);
+        break;
+      }
+      const int np = len - s * K < K ? len - s * K : K;
+      float* T = tiles + slot * tile_floats;
+      if (lane == 0) mbar_arrive_expect_tx(&full[slot], (unsigned)(np * A * L) * 4u);
+      __syncwarp();
+      if (contiguous) {
+        // pixels s*K .. s*K+np-1 are adjacent in memory (ascending for pstep=1, descending for -1)
+        const int first = ch.pstep == 1 ? pix0 + s * K : pix0 - (s * K + np - 1);
+        if (lane < A) {
+          const float* src = (lane == 0 ? U : Mr + (long long)(lane - 1) * p.slice) + (long long)first * L;
+          bulk_g2s(T + lane * K * L, src, (unsigned)(np * L) * 4u, &full[slot]);
+        }
+      } else {
+        for (int q = lane; q < np * A; q += 32) {
+          const int k = q / A, a = q - k * A;
+          const int px = pix0 + (s * K + k) * ch.pstep;
+          const float* src = (a == 0 ? U : Mr + (long long)(a - 1) * p.slice) + (long long)px * L;
+          bulk_g2s(T + (a * K + k) * L, src, (unsigned)L * 4u, &full[slot]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------- consumers ----------------------------------
+  float* Mw = p.msg_write + (long long)ch.dir * p.slice + ibase * L;
+  const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
+  uint8_t* MI = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L : nullptr;
+  uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
+  const int dir_off = (1 + ch.dir) * K * L, inv_off = (1 + ch.inv) * K * L;
+  auto load_e = [&](int s) -> float {  // thread k < K: weight of chain pixel s*K + k
+    const int j = s * K + c;
+    return (E && c < K && j < len && j >= 1) ? E[pix0 + j * ch.pstep] : 1.f;
+  };
+  if (c < K) etile[c] = load_e(0);
+  float e_next = load_e(1);
+  float uu = 0.f, r = 0.f;
+  for (int s = 0; s < nstages; ++s) {
+    const int slot = s % NS;
+    if (!mbar_wait(&full[slot], (s / NS) & 1)) {
+      if (c == 0) atomicExch(p.status, 112);
+      return;
+    }
+    const int np = len - s * K < K ? len - s * K : K;
+    const float* T = tiles + slot * tile_floats;
+    const float* et = etile + (s & 1) * K;
+    // position of chain pixel s*K + k inside the tile
+    const int kbase = (contiguous && ch.pstep == -1) ? np - 1 : 0;
+    const int kstep = (contiguous && ch.pstep == -1) ? -1 : 1;
+    cta_sync(NT);  // the weights of this stage (written at the end of the previous one) are visible
+    for (int k = 0; k < np; ++k) {
+      const float* t = T + (kbase + k * kstep) * L + c;
+      float uu_next = 0.f;
+      if (act) {
+        float sum = t[0];
+        for (int a = 1; a <= D; ++a) sum += t[a * K * L];
+        sum -= t[dir_off];
+        uu_next = fmaf(sum, p.rho, -t[inv_off]);
+      }
+      if (s + k > 0) {
+        const float e = et[k];
+        const float h = act ? fmaf(p.rho, r, uu) : kInf;
+        float best, m;
+        int bi, n;
+        cta_minplus<MODE, TRAIN>(p, cc, h, e, act, c, L, nw, hbuf, ctx1, redA_v, redA_i, redB_v, redB_i, best, bi,
+                                 m, n, NT);
+        r = best - m;
+        const int px = pix0 + (s * K + k) * ch.pstep;
+        if (act) Mw[(long long)px * L + c] = r;
+        if (TRAIN) {
+          if (act) MI[(long long)px * L + c] = (uint8_t)bi;
+          if (c == 0) NI[px] = (uint8_t)n;
+        }
+      }
+      uu = uu_next;
+    }
+    if (c < K) etile[((s + 1) & 1) * K + c] = e_next;
+    e_next = load_e(s + 2);
+    cta_sync(NT);  // every consumer is done with the tile
+    if (c == 0) mbar_arrive(&empty[slot]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Inference, rank-1 context that saturates inside a window (truncated linear / quadratic, Potts),
+// 32 < L <= 256, L % 4 == 0: one WARP per chain, LPT = ceil(L/32) consecutive labels per lane.
+//
+// With several labels per lane the whole label vector of a chain lives in one warp's registers:
+// no block barrier per step (the CTA-per-chain kernel needs two), the window around a lane's
+// labels is fetched with a few 16-byte shared loads, and every candidate costs one fma and a
+// share of a 3-input min.  Inputs are staged by a producer warp with cp.async.bulk copies
+// (one per array for horizontal chains, one label row per pixel otherwise) on an mbarrier ring.
+// RW = compile-time window half-width (candidates |c-f| < RW; RW >= R of the context: offsets
+// beyond R carry the saturated value, which is an exact candidate of the dense evaluation too).
+// ------------------------------------------------------------------------------------------------
+template <int LPT, int RW>
+__global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(128) float smem[];
+  ChainCtx ch;
+  if (!decode_chain(p, blockIdx.x, ch)) return;  // uniform for the CTA
+  constexpr int LP = 32 * LPT;                   // padded label count
+  constexpr int G = ((RW - 1 + 3) / 4) * 4;      // guard band (floats) on both sides of the window buffer
+  constexpr int NWV = (LPT + 2 * G) / 2;         // float2 loads covering a lane's window
+  const int L = p.L, D = p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_floats = A * K * L;
+  float* tiles = smem;                                   // [NS][A][K][L]
+  float* hwin = tiles + NS * tile_floats;                // [2][G + LP + G]
+  float* etile = hwin + 2 * (LP + 2 * G);                // [2][K]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(etile + 2 * K + ((2 * K) & 1));
+  unsigned long long* empty = full + NS;
+  const int len = ch.len;
+  const int nstages = (len + K - 1) / K;
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  const int pix0 = ch.h0 * p.W + ch.w0;
+  const bool contiguous = (ch.pstep == 1 || ch.pstep == -1);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < 2 * (LP + 2 * G); i += 64) hwin[i] = kInf;  // guards and padding labels
+  __syncthreads();
+
+  if (warp == 1) {
+    // ---------------------------------- producer ----------------------------------
+    const float* U = p.unary + ibase * L;
+    const float* Mr = p.msg_read + ibase * L;
+    for (int s = 0; s < nstages; ++s) {
+      const int slot = s % NS;
+      if (s >= NS && !mbar_wait(&empty[slot], ((s / NS) - 1) & 1)) {
+        if (lane == 0) atomicExch(p.status, 121);
+        break;
+      }
+      const int np = len - s * K < K ? len - s * K : K;
+      float* T = tiles + slot * tile_floats;
+      if (lane == 0) mbar_arrive_expect_tx(&full[slot], (unsigned)(np * A * L) * 4u);
+      __syncwarp();
+      if (contiguous) {
+        const int first = ch.pstep == 1 ? pix0 + s * K : pix0 - (s * K + np - 1);
+        if (lane < A) {
+          const float* src = (lane == 0 ? U : Mr + (long long)(lane - 1) * p.slice) + (long long)first * L;
+          bulk_g2s(T + lane * K * L, src, (unsigned)(np * L) * 4u, &full[slot]);
+        }
+      } else {
+        for (int q = lane; q < np * A; q += 32) {
+          const int k = q / A, a = q - k * A;
+          const int px = pix0 + (s * K + k) * ch.pstep;
+          const float* src = (a == 0 ? U : Mr + (long long)(a - 1) * p.slice) + (long long)px * L;
+          bulk_g2s(T + (a * K + k) * L, src, (unsigned)L * 4u, &full[slot]);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------- consumer warp ----------------------------------
+  const CtxInfo inf = *p.info;
+  const float cmax = inf.cmax;
+  float cw[RW];  // context at offsets 0 .. RW-1 (saturated value beyond the table)
+#pragma unroll
+  for (int k = 0; k < RW; ++k) cw[k] = k < L ? __ldg(p.ctx + k) : cmax;
+  float* Mw = p.msg_write + (long long)ch.dir * p.slice + ibase * L;
+  const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
+  const int c0 = lane * LPT;                    // first label of this lane
+  const int nl = L - c0 < 0 ? 0 : (L - c0 < LPT ? L - c0 : LPT);  // labels of this lane that exist
+  const int dir_off = (1 + ch.dir) * K * L, inv_off = (1 + ch.inv) * K * L;
+  const float rho = p.rho;
+  auto load_e = [&](int s) -> float {  // lane k < K: weight of chain pixel s*K + k
+    const int j = s * K + lane;
+    return (E && lane < K && j < len && j >= 1) ? E[pix0 + j * ch.pstep] : 1.f;
+  };
+  if (lane < K) etile[lane] = load_e(0);
+  float e_next = load_e(1);
+  float uu[LPT], r[LPT];
+#pragma unroll
+  for (int i = 0; i < LPT; ++i) uu[i] = 0.f, r[i] = 0.f;
+
+  for (int s = 0; s < nstages; ++s) {
+    const int slot = s % NS;
+    if (!mbar_wait(&full[slot], (s / NS) & 1)) {
+      if (lane == 0) atomicExch(p.status, 122);
+      return;
+    }
+    const int np = len - s * K < K ? len - s * K : K;
+    const float* T = tiles + slot * tile_floats;
+    const float* et = etile + (s & 1) * K;
+    const int kbase = (contiguous && ch.pstep == -1) ? np - 1 : 0;
+    const int kstep = (contiguous && ch.pstep == -1) ? -1 : 1;
+    __syncwarp();
+    for (int k = 0; k < np; ++k) {
+      const float* t = T + (kbase + k * kstep) * L + c0;
+      // inputs of this pixel -> UU (reference order of the additions), LPT labels per lane
+      float un[LPT];
+      if (nl == LPT) {
+        float v[LPT], md[LPT], mi[LPT];
+#pragma unroll
+        for (int q = 0; q < LPT / 2; ++q) {
+          const float2 x = reinterpret_cast<const float2*>(t)[q];
+          v[2 * q] = x.x, v[2 * q + 1] = x.y;
+          const float2 y = reinterpret_cast<const float2*>(t + dir_off)[q];
+          md[2 * q] = y.x, md[2 * q + 1] = y.y;
+          const float2 z = reinterpret_cast<const float2*>(t + inv_off)[q];
+          mi[2 * q] = z.x, mi[2 * q + 1] = z.y;
+        }
+        for (int a = 1; a <= D; ++a) {
+#pragma unroll
+          for (int q = 0; q < LPT / 2; ++q) {
+            const float2 x = reinterpret_cast<const float2*>(t + a * K * L)[q];
+            v[2 * q] += x.x, v[2 * q + 1] += x.y;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) un[i] = fmaf(v[i] - md[i], rho, -mi[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          un[i] = 0.f;
+          if (i < nl) {
+            float sum = t[i];
+            for (int a = 1; a <= D; ++a) sum += t[a * K * L + i];
+            sum -= t[dir_off + i];
+            un[i] = fmaf(sum, rho, -t[inv_off + i]);
+          }
+        }
+      }
+      if (s + k > 0) {
+        const float e = et[k];
+        float* hw = hwin + ((s * K + k) & 1) * (LP + 2 * G);
+        float hl = kInf;
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          const float h = fmaf(rho, r[i], uu[i]);
+          if (i < nl) {
+            hw[G + c0 + i] = h;
+            hl = fminf(hl, h);
+          }
+        }
+        const float gv = fmaf(e, cmax, warp_min(hl));  // candidate through the saturated value
+        __syncwarp();
+        // window of this lane: labels c0 - G .. c0 + LPT + G - 1 (guards read +inf)
+        float win[NWV * 2];
+        if constexpr (LPT % 4 == 0) {
+#pragma unroll
+          for (int q = 0; q < NWV / 2; ++q) {
+            const float4 x = reinterpret_cast<const float4*>(hw + c0)[q];
+            win[4 * q] = x.x, win[4 * q + 1] = x.y, win[4 * q + 2] = x.z, win[4 * q + 3] = x.w;
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < NWV; ++q) {
+            const float2 x = reinterpret_cast<const float2*>(hw + c0)[q];
+            win[2 * q] = x.x, win[2 * q + 1] = x.y;
+          }
+        }
+        float best[LPT];
+        float bl = kInf;
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          float cand[2 * RW];
+          cand[0] = gv;
+#pragma unroll
+          for (int kk = -(RW - 1); kk <= RW - 1; ++kk)
+            cand[kk + RW] = fmaf(e, cw[kk < 0 ? -kk : kk], win[G + i + kk]);
+          best[i] = min_tree<2 * RW>(cand);
+          if (i < nl) bl = fminf(bl, best[i]);
+        }
+        const float m = warp_min(bl);
+        float* out = Mw + (long long)(pix0 + (s * K + k) * ch.pstep) * L + c0;
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          r[i] = best[i] - m;
+          if (i < nl) out[i] = r[i];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < LPT; ++i) uu[i] = un[i];
+    }
+    if (lane < K) etile[((s + 1) & 1) * K + lane] = e_next;
+    e_next = load_e(s + 2);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[slot]);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -790,6 +1169,88 @@ cudaError_t launch_cta(const FwdParams& p, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+template <int MODE, bool TRAIN>
+cudaError_t launch_cta_tma(FwdParams p, cudaStream_t st) {
+  const int total = p.chain_off[p.ndirs];
+  const int NT = MODE == 2 ? 64 : ((p.L + 31) / 32) * 32;
+  const int A = p.D + 1;
+  int K = 16, NS = 3;
+  auto bytes = [&](int k, int ns) {
+    return ((size_t)ns * A * k * p.L + 2 * k + 2 * NT + 32) * sizeof(float) + 2 * ns * 8 + 16;
+  };
+  while (K > 4 && bytes(K, NS) > 100 * 1024) K >>= 1;
+  if (bytes(K, NS) > 100 * 1024) NS = 2;
+  if (tma_stage_override()) NS = tma_stage_override();
+  if (bytes(K, NS) > 200 * 1024) return cudaErrorInvalidConfiguration;
+  p.tma_k = K;
+  p.tma_stages = NS;
+  const size_t smem = bytes(K, NS);
+  cudaError_t e = ensure_smem(fwd_cta_tma_kernel<MODE, TRAIN>, smem);
+  if (e != cudaSuccess) return e;
+  ProfScope prof(kProfFwdSweep, st);
+  fwd_cta_tma_kernel<MODE, TRAIN><<<total, NT + 32, smem, st>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+template <int LPT, int RW>
+cudaError_t launch_wide(FwdParams p, cudaStream_t st) {
+  const int total = p.chain_off[p.ndirs];
+  const int A = p.D + 1;
+  constexpr int G = ((RW - 1 + 3) / 4) * 4;
+  int K = 8, NS = 3;
+  auto bytes = [&](int k, int ns) {
+    return ((size_t)ns * A * k * p.L + 2 * (32 * LPT + 2 * G) + 2 * k + 2) * sizeof(float) + 2 * ns * 8 + 16;
+  };
+  // keep every chain of the launch resident at once where possible (chains are equally long, so a
+  // partial second wave would double the time)
+  const int per_sm = (total + 147) / 148;
+  size_t limit = (size_t)220 * 1024 / (per_sm > 0 ? per_sm : 1);
+  if (limit > 100 * 1024) limit = 100 * 1024;
+  if (limit < 12 * 1024) limit = 12 * 1024;
+  while (bytes(K, NS) > limit) {
+    if (K > 4) {
+      K >>= 1;
+    } else if (NS > 2) {
+      NS = 2;
+    } else if (K > 1) {
+      K >>= 1;
+    } else {
+      break;
+    }
+  }
+  if (tma_stage_override()) NS = tma_stage_override();
+  p.tma_k = K;
+  p.tma_stages = NS;
+  const size_t smem = bytes(K, NS);
+  cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW>, smem);
+  if (e != cudaSuccess) return e;
+  ProfScope prof(kProfFwdSweep, st);
+  fwd_wide_kernel<LPT, RW><<<total, 64, smem, st>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+template <int LPT>
+cudaError_t launch_wide_r(const FwdParams& p, int R, cudaStream_t st) {
+  if (R <= 2) return launch_wide<LPT, 2>(p, st);
+  if (R <= 4) return launch_wide<LPT, 4>(p, st);
+  if (R <= 8) return launch_wide<LPT, 8>(p, st);
+  return launch_wide<LPT, 16>(p, st);
+}
+
+// Label rows of 16-byte multiples at 16-byte aligned bases: the bulk-copy CTA kernel applies.
+bool cta_tma_eligible(const FwdParams& p) {
+  if (p.L & 3) return false;
+  return (((uintptr_t)p.unary | (uintptr_t)p.msg_read) & 15) == 0;
+}
+
+template <int MODE, bool TRAIN>
+cudaError_t launch_cta_any(const FwdParams& p, cudaStream_t st) {
+  if (cta_tma_eligible(p)) return launch_cta_tma<MODE, TRAIN>(p, st);
+  return launch_cta<MODE, TRAIN>(p, st);
+}
+
 }  // namespace
 
 cudaError_t launch_analyze(const float* ctx, int L, int rank, const float* ew, long long n_ew,
@@ -829,9 +1290,18 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
     if (p.L == 21) return train ? launch_warp<21, true>(rest, st) : launch_warp<21, false>(rest, st);
     return train ? launch_warp<32, true>(rest, st) : launch_warp<32, false>(rest, st);
   }
-  if (p.ctx_rank == 1) return train ? launch_cta<1, true>(p, st) : launch_cta<1, false>(p, st);
-  if (p.L <= 64) return train ? launch_cta<2, true>(p, st) : launch_cta<2, false>(p, st);
-  return train ? launch_cta<0, true>(p, st) : launch_cta<0, false>(p, st);
+  if (p.ctx_rank == 1 && !train && p.host_windowed && p.host_R <= 16 && p.L <= 256 && cta_tma_eligible(p)) {
+    const int lpt = 2 * ((p.L + 63) / 64);
+    switch (lpt) {
+      case 2: return launch_wide_r<2>(p, p.host_R, st);
+      case 4: return launch_wide_r<4>(p, p.host_R, st);
+      case 6: return launch_wide_r<6>(p, p.host_R, st);
+      default: return launch_wide_r<8>(p, p.host_R, st);
+    }
+  }
+  if (p.ctx_rank == 1) return train ? launch_cta_any<1, true>(p, st) : launch_cta_any<1, false>(p, st);
+  if (p.L <= 64) return train ? launch_cta_any<2, true>(p, st) : launch_cta_any<2, false>(p, st);
+  return train ? launch_cta_any<0, true>(p, st) : launch_cta_any<0, false>(p, st);
 }
 
 cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, uint8_t* label,

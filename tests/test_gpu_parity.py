@@ -192,3 +192,30 @@ def test_bulk_copy_kernel_shapes(mode, D, H, W, L, kind):
             assert np.array_equal(got[k], want[k]), k
         ev = g.forward(mode, unary, ctx, ew, D, 3, training=False)
         assert np.array_equal(ev["cost"], want["cost"])
+
+
+@pytest.mark.parametrize("mode,D,H,W,L,kind,ewk", [
+    ("TRWP", 4, 11, 23, 192, "tl1d", "none"),    # config-2 style: 6 labels per lane, window 2
+    ("ISGMR", 4, 9, 10, 256, "tq1d", "none"),    # config-3 style: 8 labels per lane, window 16
+    ("ISGMR", 8, 10, 9, 64, "tl1d", "pos"),      # 2 labels per lane, diagonals, edge weights
+    ("TRWP", 16, 9, 8, 100, "tq1d", "pos"),      # L not a multiple of the lane block
+    ("TRWP", 4, 7, 19, 36, "tl1d", "pos"),       # just above one label per lane
+    ("ISGMR", 4, 8, 9, 128, "potts1d", "none"),  # Potts as a rank-1 function (window 1)
+])
+def test_wide_inference_kernel(mode, D, H, W, L, kind, ewk):
+    """Inference with a windowed rank-1 context and L % 4 == 0: warp-per-chain kernel with several
+    labels per lane.  Costs and messages must equal the dense evaluation bit for bit."""
+    g = _gpu()
+    rng = np.random.default_rng(900 + L + D)
+    unary = rng.standard_normal((2, 1, H, W, L)).astype(np.float32)
+    if kind == "potts1d":
+        ctx = np.ones(L, np.float32)
+        ctx[0] = 0
+    else:
+        ctx = cases.make_context(kind, L, rng)
+    ew = None if ewk == "none" else rng.uniform(0.2, 1.0, size=(D, 2, 1, H, W)).astype(np.float32)
+    got = g.forward(mode, unary, ctx, ew, D, 3, training=False, save_labels=True)
+    want = oracle.forward(mode, unary, ctx, ew, D, 3, training=False, save_labels=True)
+    assert np.array_equal(got["cost"], want["cost"])
+    assert np.array_equal(got["msg"], want["msg"])
+    assert np.array_equal(got["label_all"], want["label_all"])
