@@ -114,13 +114,37 @@ def units_per_step(cfg, batch):
 
 def algorithmic_bytes(cfg, batch, kind):
     """Bytes one sweep launch must move (fused model): forward 4L(D+2)+4 (+L+1 when indices are
-    saved) per pixel; backward 4L(2D+3)+L+9 per pixel."""
+    saved) per pixel and direction; backward 4L(2D+3)+L+9.  A TRWP launch covers one direction;
+    an ISGMR forward launch covers all D directions of an iteration."""
     _, _, L, H, W = cfg["unary"].shape
     D = cfg["n_dir"]
     n = batch * H * W
     if kind == "fwd":
-        return n * (4 * L * (D + 2) + 4 + ((L + 1) if cfg["training"] else 0))
+        per_dir = n * (4 * L * (D + 2) + 4 + ((L + 1) if cfg["training"] else 0))
+        return per_dir * (D if cfg["mode"] == "ISGMR" else 1)
     return n * (4 * L * (2 * D + 3) + L + 9)
+
+
+def dominant_kernel(cfg, kind):
+    """Name of the sweep kernel the workload spends its time in (see mplayers_b200/csrc)."""
+    L = cfg["unary"].shape[2]
+    if kind == "bwd":
+        return "bwd_tma_kernel" if (L <= 32 and cfg["mode"] == "TRWP") else \
+            ("bwd_warp_kernel" if L <= 32 else "bwd_cta_kernel")
+    if L <= 32:
+        return "fwd_tma_kernel"
+    if not cfg["training"] and cfg["label_context"].dim() == 1 and L % 4 == 0:
+        return "fwd_wide_kernel"
+    return "fwd_cta_tma_kernel" if L % 4 == 0 else "fwd_cta_kernel"
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (same workload, one GPU); None where no capture exists.
+NCU_TRAFFIC = {
+    ("seg_trwp_train", "bwd"): 149.3e6 + 80.9e6,
+    ("seg_trwp_train", "fwd"): 222.4e6 + 33.9e6,
+    ("stereo_trwp_infer", "fwd"): 1788.5e6 + 338.6e6,
+}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -290,9 +314,9 @@ def run_ours(a):
             per_launch_ms = t_dom / n_dom
             bytes_launch = algorithmic_bytes(cfg, batch, dom)
             achieved = bytes_launch / (per_launch_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": ("bwd_warp_kernel" if dom == "bwd" else "fwd sweep kernel"),
+            roof = {"bound": "hbm", "kernel": dominant_kernel(cfg, dom),
                     "achieved": round(achieved, 1), "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                    "frac": round(achieved / peak, 4), "traffic": None,
+                    "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC.get((a.workload, dom)),
                     "avg_launch_ms": round(per_launch_ms, 5), "algorithmic_bytes_per_launch": bytes_launch}
         other = {}
         for k in ("fwd", "bwd", "elementwise"):

@@ -811,7 +811,7 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
 // RW = compile-time window half-width (candidates |c-f| < RW; RW >= R of the context: offsets
 // beyond R carry the saturated value, which is an exact candidate of the dense evaluation too).
 // ------------------------------------------------------------------------------------------------
-template <int LPT, int RW>
+template <int LPT, int RW, int DT>
 __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(128) float smem[];
   ChainCtx ch;
@@ -819,7 +819,7 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
   constexpr int LP = 32 * LPT;                   // padded label count
   constexpr int G = ((RW - 1 + 3) / 4) * 4;      // guard band (floats) on both sides of the window buffer
   constexpr int NWV = (LPT + 2 * G) / 2;         // float2 loads covering a lane's window
-  const int L = p.L, D = p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
+  const int L = p.L, D = DT ? DT : p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_floats = A * K * L;
   float* tiles = smem;                                   // [NS][A][K][L]
@@ -924,11 +924,14 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
           const float2 z = reinterpret_cast<const float2*>(t + inv_off)[q];
           mi[2 * q] = z.x, mi[2 * q + 1] = z.y;
         }
-        for (int a = 1; a <= D; ++a) {
 #pragma unroll
-          for (int q = 0; q < LPT / 2; ++q) {
-            const float2 x = reinterpret_cast<const float2*>(t + a * K * L)[q];
-            v[2 * q] += x.x, v[2 * q + 1] += x.y;
+        for (int a = 1; a <= (DT ? DT : 16); ++a) {
+          if (a <= D) {
+#pragma unroll
+            for (int q = 0; q < LPT / 2; ++q) {
+              const float2 x = reinterpret_cast<const float2*>(t + a * K * L)[q];
+              v[2 * q] += x.x, v[2 * q + 1] += x.y;
+            }
           }
         }
 #pragma unroll
@@ -949,12 +952,24 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
         const float e = et[k];
         float* hw = hwin + ((s * K + k) & 1) * (LP + 2 * G);
         float hl = kInf;
+        if (nl == LPT) {
+          float hv[LPT];
 #pragma unroll
-        for (int i = 0; i < LPT; ++i) {
-          const float h = fmaf(rho, r[i], uu[i]);
-          if (i < nl) {
-            hw[G + c0 + i] = h;
-            hl = fminf(hl, h);
+          for (int i = 0; i < LPT; ++i) {
+            hv[i] = fmaf(rho, r[i], uu[i]);
+            hl = fminf(hl, hv[i]);
+          }
+#pragma unroll
+          for (int q = 0; q < LPT / 2; ++q)
+            reinterpret_cast<float2*>(hw + G + c0)[q] = make_float2(hv[2 * q], hv[2 * q + 1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) {
+            const float h = fmaf(rho, r[i], uu[i]);
+            if (i < nl) {
+              hw[G + c0 + i] = h;
+              hl = fminf(hl, h);
+            }
           }
         }
         const float gv = fmaf(e, cmax, warp_min(hl));  // candidate through the saturated value
@@ -989,9 +1004,14 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
         const float m = warp_min(bl);
         float* out = Mw + (long long)(pix0 + (s * K + k) * ch.pstep) * L + c0;
 #pragma unroll
-        for (int i = 0; i < LPT; ++i) {
-          r[i] = best[i] - m;
-          if (i < nl) out[i] = r[i];
+        for (int i = 0; i < LPT; ++i) r[i] = best[i] - m;
+        if (nl == LPT) {
+#pragma unroll
+          for (int q = 0; q < LPT / 2; ++q) reinterpret_cast<float2*>(out)[q] = make_float2(r[2 * q], r[2 * q + 1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < LPT; ++i)
+            if (i < nl) out[i] = r[i];
         }
       }
 #pragma unroll
@@ -1193,8 +1213,8 @@ cudaError_t launch_cta_tma(FwdParams p, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-template <int LPT, int RW>
-cudaError_t launch_wide(FwdParams p, cudaStream_t st) {
+template <int LPT, int RW, int DT>
+cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int A = p.D + 1;
   constexpr int G = ((RW - 1 + 3) / 4) * 4;
@@ -1223,12 +1243,19 @@ cudaError_t launch_wide(FwdParams p, cudaStream_t st) {
   p.tma_k = K;
   p.tma_stages = NS;
   const size_t smem = bytes(K, NS);
-  cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW>, smem);
+  cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW, DT>, smem);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
-  fwd_wide_kernel<LPT, RW><<<total, 64, smem, st>>>(p);
+  fwd_wide_kernel<LPT, RW, DT><<<total, 64, smem, st>>>(p);
   count_launch();
   return cudaGetLastError();
+}
+
+template <int LPT, int RW>
+cudaError_t launch_wide(const FwdParams& p, cudaStream_t st) {
+  if (p.D == 4) return launch_wide_d<LPT, RW, 4>(p, st);
+  if (p.D == 8) return launch_wide_d<LPT, RW, 8>(p, st);
+  return launch_wide_d<LPT, RW, 0>(p, st);
 }
 
 template <int LPT>
