@@ -235,7 +235,16 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
     fp.msg_read = rd;
     fp.msg_write = wr;
     if (isgmr) {
-      set_dirs(fp, 0, D);  // every direction reads the previous iteration's messages: one launch
+      // Every direction reads the previous iteration's messages.  Their sum with the unaries is
+      // formed once (in `cost_final`, which is otherwise unused until the end) so that a sweep
+      // stages three arrays instead of D+1; in the first iteration the messages are zero.
+      fp.agg = 1;
+      fp.unary = unary;
+      if (it > 0) {
+        MPL_CUDA(mpl::launch_aggregate(unary, rd, cost_final, nullptr, d.npix, L, D, d.slice, 1.f, 0, st));
+        fp.unary = cost_final;
+      }
+      set_dirs(fp, 0, D);
       MPL_CUDA(mpl::launch_forward_sweep(fp, train, st));
       float* t = rd;
       rd = wr;

@@ -94,6 +94,11 @@ struct FwdParams {
   int ctx_rank;
   int tma_stages;         // bulk-copy kernels: ring depth
   int tma_k;              // bulk-copy CTA kernel: chain pixels per stage
+  // agg != 0 (ISGMR): `unary` holds the per-iteration aggregate A = U + sum_k M_k of the messages
+  // being read (computed once per iteration in the reference order of the additions), so a sweep
+  // stages A, M_dir and M_inv only: UU = (A - M_dir) * rho - M_inv, bit-identical to the
+  // reference's ((U + M_0 + ... + M_{D-1}) - M_dir) * rho - M_inv.
+  int agg;
   int host_windowed;      // host copy of the context analysis (rank-1, L > 32): windowed path is exact
   int host_R;             //   ... and its window half-width
   int dir0, ndirs;        // this launch covers directions dir0 .. dir0+ndirs-1

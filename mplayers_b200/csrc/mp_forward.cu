@@ -43,7 +43,8 @@ __device__ __forceinline__ bool decode_chain(const FwdParams& p, int g, ChainCtx
 
 // UU of one pixel from its ring slot (rows: 0 = U, 1+k = M_k), column `col`, row stride `rs`.
 __device__ __forceinline__ float uu_from_ring(const float* slot, int rs, int col, int D, int dir,
-                                              int inv, float rho) {
+                                              int inv, float rho, int agg = 0) {
+  if (agg) return fmaf(slot[col] - slot[rs + col], rho, -slot[2 * rs + col]);  // rows: A, M_dir, M_inv
   float s = slot[col];
   for (int k = 0; k < D; ++k) s += slot[(1 + k) * rs + col];
   s -= slot[(1 + dir) * rs + col];
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   ChainCtx ch;
   if (!decode_chain(p, blockIdx.x * wpb + warp, ch)) return;
-  const int L = p.L, D = DT ? DT : p.D, rows = D + 2;
+  const int L = p.L, D = p.agg ? 2 : (DT ? DT : p.D), rows = D + 2;  // D = staged message slices
   const int slot_floats = rows * 32;
   float* ring = smem + warp * (kPF * slot_floats + 64);
   float* hbuf = ring + kPF * slot_floats;
@@ -196,12 +197,13 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
     cp_async4(dst, Ul + o);
 #pragma unroll
     for (int k = 0; k < (DT ? DT : 16); ++k)
-      if (k < D) cp_async4(dst + (1 + k) * 32, Ml + k * p.slice + o);
+      if (k < D) cp_async4(dst + (1 + k) * 32, Ml + (p.agg ? (k == 0 ? ch.dir : ch.inv) : k) * p.slice + o);
     cp_async4(dst + (D + 1) * 32, E + pxc);
     cp_async_commit();
     px_pf += ch.pstep;
   };
   auto uu_of = [&](const float* sl) {  // sl: this lane's column of a ring slot
+    if (p.agg) return fmaf(sl[0] - sl[32], rho, -sl[64]);  // rows: A, M_dir, M_inv
     float s = sl[0];
 #pragma unroll
     for (int k = 0; k < (DT ? DT : 16); ++k)
@@ -272,7 +274,8 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
   // pointer up by hand would hide its address space from the compiler and turn every shared
   // access into a slower generic one.)
   extern __shared__ __align__(128) float smem[];
-  constexpr int A = DT + 1;   // staged arrays: unary + D message slices
+  constexpr bool AGG = DT == 2;  // aggregate mode (see FwdParams::agg): arrays A, M_dir, M_inv
+  constexpr int A = DT + 1;      // staged arrays: unary (or aggregate) + DT message slices
   constexpr int AE = A + 1;   // ... + edge weights
   const int L = LT ? LT : p.L, H = p.H, W = p.W, NS = p.tma_stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -331,7 +334,8 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
           tma_load_2d(T, &maps.a, w0 * L, y0, &full[slot]);
 #pragma unroll
           for (int a = 1; a < A; ++a)
-            tma_load_2d(T + a * kTK * 4 * L, &maps.b, w0 * L, (a - 1) * p.nimg * H + y0, &full[slot]);
+            tma_load_2d(T + a * kTK * 4 * L, &maps.b, w0 * L,
+                        (AGG ? (a == 1 ? dir : inv) : a - 1) * p.nimg * H + y0, &full[slot]);
           if (has_e) tma_load_2d(ET, &maps.c, w0, dir * p.nimg * H + y0, &full[slot]);
         }
       } else {
@@ -344,7 +348,8 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
           const int wlo = FWD ? s * kTK : W - s * kTK - npix;
           const long long pix = (long long)(chain0 + q) * W + wlo;  // first pixel, over all images
           if (a < A) {
-            const float* src = (a == 0 ? p.unary : p.msg_read + (long long)(a - 1) * p.slice) + pix * L;
+            const int sid = AGG ? (a == 1 ? dir : inv) : a - 1;
+            const float* src = (a == 0 ? p.unary : p.msg_read + (long long)sid * p.slice) + pix * L;
             bulk_g2s(T + (q * A + a) * kTK * L, src, (unsigned)npix * 4u * L, &full[slot]);
           } else if (has_e) {
             bulk_g2s(ET + q * kTK, p.ew + (long long)dir * p.pslice + pix, (unsigned)npix * 4u, &full[slot]);
@@ -390,14 +395,16 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
   const int ek = (VERT ? 4 : 1) * (FWD ? 1 : -1);
   const int pstep = VERT ? (FWD ? W : -W) : (FWD ? 1 : -1);
   const int px0 = VERT ? (FWD ? 0 : H - 1) * W + fix : fix * W + (FWD ? 0 : W - 1);  // chain pixel 0
-  const int dir_off = (1 + dir) * sa, inv_off = (1 + inv) * sa;
+  const int dir_off = (AGG ? 1 : 1 + dir) * sa, inv_off = (AGG ? 2 : 1 + inv) * sa;
 
   float uu = 0.f, r = 0.f;
   // inputs of one chain pixel -> UU of that pixel (reference order of the additions)
   auto uu_at = [&](const float* t) {
     float sum = t[0];
+    if (!AGG) {
 #pragma unroll
-    for (int a = 1; a <= DT; ++a) sum += t[a * sa];
+      for (int a = 1; a <= DT; ++a) sum += t[a * sa];
+    }
     sum -= t[dir_off];
     return fmaf(sum, rho, -t[inv_off]);
   };
@@ -594,7 +601,7 @@ __global__ void __launch_bounds__(256) fwd_cta_kernel(const __grid_constant__ Fw
   extern __shared__ __align__(16) float smem[];
   ChainCtx ch;
   if (!decode_chain(p, blockIdx.x, ch)) return;  // uniform for the CTA
-  const int L = p.L, D = p.D, rows = D + 2, NT = blockDim.x, c = threadIdx.x, nw = NT >> 5;
+  const int L = p.L, D = p.agg ? 2 : p.D, rows = D + 2, NT = blockDim.x, c = threadIdx.x, nw = NT >> 5;
   float* ring = smem;                  // [kPF][rows][NT]
   float* hbuf = ring + kPF * rows * NT;  // [NT]
   float* ctx1 = hbuf + NT;             // [NT]   (MODE 1)
@@ -624,7 +631,9 @@ __global__ void __launch_bounds__(256) fwd_cta_kernel(const __grid_constant__ Fw
       const int px = pix0 + j * ch.pstep;
       if (act && j < len - 1) {
         cp_async4(dst, U + (long long)px * L + c);
-        for (int k = 0; k < D; ++k) cp_async4(dst + (1 + k) * NT, Mr + k * p.slice + (long long)px * L + c);
+        for (int k = 0; k < D; ++k)
+          cp_async4(dst + (1 + k) * NT,
+                    Mr + (p.agg ? (k == 0 ? ch.dir : ch.inv) : k) * p.slice + (long long)px * L + c);
       }
       if (E && j >= 1) cp_async4(dst + (D + 1) * NT, E + px);
     }
@@ -634,7 +643,7 @@ __global__ void __launch_bounds__(256) fwd_cta_kernel(const __grid_constant__ Fw
 #pragma unroll
   for (int j = 0; j < kPF; ++j) issue(j);
   cp_async_wait<kPF - 1>();
-  float uu = act ? uu_from_ring(ring, NT, c, D, ch.dir, ch.inv, p.rho) : 0.f;
+  float uu = act ? uu_from_ring(ring, NT, c, D, ch.dir, ch.inv, p.rho, p.agg) : 0.f;
   issue(kPF);
   float r = 0.f;
 
@@ -642,7 +651,7 @@ __global__ void __launch_bounds__(256) fwd_cta_kernel(const __grid_constant__ Fw
     cp_async_wait<kPF - 1>();
     const float* slot = ring + (i & (kPF - 1)) * rows * NT;
     const float e = E ? slot[(D + 1) * NT + c] : 1.f;
-    const float uu_next = (act && i < len - 1) ? uu_from_ring(slot, NT, c, D, ch.dir, ch.inv, p.rho) : 0.f;
+    const float uu_next = (act && i < len - 1) ? uu_from_ring(slot, NT, c, D, ch.dir, ch.inv, p.rho, p.agg) : 0.f;
     const float h = act ? fmaf(p.rho, r, uu) : kInf;
     float best, m;
     int bi, n;
@@ -671,7 +680,7 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
   extern __shared__ __align__(128) float smem[];
   ChainCtx ch;
   if (!decode_chain(p, blockIdx.x, ch)) return;  // uniform for the CTA
-  const int L = p.L, D = p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
+  const int L = p.L, D = p.agg ? 2 : p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
   const int NT = blockDim.x - 32, c = threadIdx.x, nw = NT >> 5;
   const bool producer = c >= NT;
   const int tile_floats = A * K * L;
@@ -725,14 +734,16 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
         // pixels s*K .. s*K+np-1 are adjacent in memory (ascending for pstep=1, descending for -1)
         const int first = ch.pstep == 1 ? pix0 + s * K : pix0 - (s * K + np - 1);
         if (lane < A) {
-          const float* src = (lane == 0 ? U : Mr + (long long)(lane - 1) * p.slice) + (long long)first * L;
+          const int sid = p.agg ? (lane == 1 ? ch.dir : ch.inv) : lane - 1;
+          const float* src = (lane == 0 ? U : Mr + (long long)sid * p.slice) + (long long)first * L;
           bulk_g2s(T + lane * K * L, src, (unsigned)(np * L) * 4u, &full[slot]);
         }
       } else {
         for (int q = lane; q < np * A; q += 32) {
           const int k = q / A, a = q - k * A;
           const int px = pix0 + (s * K + k) * ch.pstep;
-          const float* src = (a == 0 ? U : Mr + (long long)(a - 1) * p.slice) + (long long)px * L;
+          const int sid = p.agg ? (a == 1 ? ch.dir : ch.inv) : a - 1;
+          const float* src = (a == 0 ? U : Mr + (long long)sid * p.slice) + (long long)px * L;
           bulk_g2s(T + (a * K + k) * L, src, (unsigned)L * 4u, &full[slot]);
         }
       }
@@ -745,7 +756,7 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
   const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
   uint8_t* MI = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L : nullptr;
   uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
-  const int dir_off = (1 + ch.dir) * K * L, inv_off = (1 + ch.inv) * K * L;
+  const int dir_off = (p.agg ? 1 : 1 + ch.dir) * K * L, inv_off = (p.agg ? 2 : 1 + ch.inv) * K * L;
   auto load_e = [&](int s) -> float {  // thread k < K: weight of chain pixel s*K + k
     const int j = s * K + c;
     return (E && c < K && j < len && j >= 1) ? E[pix0 + j * ch.pstep] : 1.f;
@@ -771,7 +782,8 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
       float uu_next = 0.f;
       if (act) {
         float sum = t[0];
-        for (int a = 1; a <= D; ++a) sum += t[a * K * L];
+        if (!p.agg)
+          for (int a = 1; a <= D; ++a) sum += t[a * K * L];
         sum -= t[dir_off];
         uu_next = fmaf(sum, p.rho, -t[inv_off]);
       }
@@ -819,6 +831,7 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
   constexpr int LP = 32 * LPT;                   // padded label count
   constexpr int G = ((RW - 1 + 3) / 4) * 4;      // guard band (floats) on both sides of the window buffer
   constexpr int NWV = (LPT + 2 * G) / 2;         // float2 loads covering a lane's window
+  constexpr bool AGG = DT == 2;  // aggregate mode (FwdParams::agg): arrays A, M_dir, M_inv
   const int L = p.L, D = DT ? DT : p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_floats = A * K * L;
@@ -860,14 +873,16 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
       if (contiguous) {
         const int first = ch.pstep == 1 ? pix0 + s * K : pix0 - (s * K + np - 1);
         if (lane < A) {
-          const float* src = (lane == 0 ? U : Mr + (long long)(lane - 1) * p.slice) + (long long)first * L;
+          const int sid = AGG ? (lane == 1 ? ch.dir : ch.inv) : lane - 1;
+          const float* src = (lane == 0 ? U : Mr + (long long)sid * p.slice) + (long long)first * L;
           bulk_g2s(T + lane * K * L, src, (unsigned)(np * L) * 4u, &full[slot]);
         }
       } else {
         for (int q = lane; q < np * A; q += 32) {
           const int k = q / A, a = q - k * A;
           const int px = pix0 + (s * K + k) * ch.pstep;
-          const float* src = (a == 0 ? U : Mr + (long long)(a - 1) * p.slice) + (long long)px * L;
+          const int sid = AGG ? (a == 1 ? ch.dir : ch.inv) : a - 1;
+          const float* src = (a == 0 ? U : Mr + (long long)sid * p.slice) + (long long)px * L;
           bulk_g2s(T + (a * K + k) * L, src, (unsigned)L * 4u, &full[slot]);
         }
       }
@@ -885,7 +900,7 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
   const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
   const int c0 = lane * LPT;                    // first label of this lane
   const int nl = L - c0 < 0 ? 0 : (L - c0 < LPT ? L - c0 : LPT);  // labels of this lane that exist
-  const int dir_off = (1 + ch.dir) * K * L, inv_off = (1 + ch.inv) * K * L;
+  const int dir_off = (AGG ? 1 : 1 + ch.dir) * K * L, inv_off = (AGG ? 2 : 1 + ch.inv) * K * L;
   const float rho = p.rho;
   auto load_e = [&](int s) -> float {  // lane k < K: weight of chain pixel s*K + k
     const int j = s * K + lane;
@@ -926,7 +941,7 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
         }
 #pragma unroll
         for (int a = 1; a <= (DT ? DT : 16); ++a) {
-          if (a <= D) {
+          if (a <= D && !AGG) {
 #pragma unroll
             for (int q = 0; q < LPT / 2; ++q) {
               const float2 x = reinterpret_cast<const float2*>(t + a * K * L)[q];
@@ -942,7 +957,8 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
           un[i] = 0.f;
           if (i < nl) {
             float sum = t[i];
-            for (int a = 1; a <= D; ++a) sum += t[a * K * L + i];
+            if (!AGG)
+              for (int a = 1; a <= D; ++a) sum += t[a * K * L + i];
             sum -= t[dir_off + i];
             un[i] = fmaf(sum, rho, -t[inv_off + i]);
           }
@@ -1104,7 +1120,7 @@ template <int LMAX, int DT, bool TRAIN>
 cudaError_t launch_warp_d(const FwdParams& p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int wpb = total >= 148 * 32 ? 4 : 1;
-  const size_t smem = (size_t)wpb * (kPF * (p.D + 2) * 32 + 64) * sizeof(float);
+  const size_t smem = (size_t)wpb * (kPF * ((p.agg ? 2 : p.D) + 2) * 32 + 64) * sizeof(float);
   cudaError_t e = ensure_smem(fwd_warp_kernel<LMAX, DT, TRAIN>, smem);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
@@ -1115,6 +1131,7 @@ cudaError_t launch_warp_d(const FwdParams& p, cudaStream_t st) {
 
 template <int LMAX, bool TRAIN>
 cudaError_t launch_warp(const FwdParams& p, cudaStream_t st) {
+  if (p.agg) return launch_warp_d<LMAX, 0, TRAIN>(p, st);
   if (p.D == 4) return launch_warp_d<LMAX, 4, TRAIN>(p, st);
   if (p.D == 8) return launch_warp_d<LMAX, 8, TRAIN>(p, st);
   return launch_warp_d<LMAX, 0, TRAIN>(p, st);
@@ -1126,12 +1143,12 @@ size_t tma_smem_bytes(int L, int D, int stages) {
 
 // Can direction `dir` of this problem use the bulk-copy kernel?  Needs 16-byte aligned row segments.
 bool tma_eligible(const FwdParams& p, int dir, int* stages) {
-  if (dir > 3 || p.L > 32 || (p.D != 4 && p.D != 8)) return false;
+  if (dir > 3 || p.L > 32 || (!p.agg && p.D != 4 && p.D != 8)) return false;
   if ((p.W & 3) || (((long long)p.W * p.L) & 3)) return false;
   const uintptr_t bits = (uintptr_t)p.unary | (uintptr_t)p.msg_read | (uintptr_t)p.ew;
   if (bits & 15) return false;
   int ns = tma_stage_override() ? tma_stage_override() : 4;
-  while (ns >= 2 && tma_smem_bytes(p.L, p.D, ns) > (ns >= 3 ? 110 : 200) * 1024) --ns;
+  while (ns >= 2 && tma_smem_bytes(p.L, p.agg ? 2 : p.D, ns) > (ns >= 3 ? 110 : 200) * 1024) --ns;
   if (ns < 2) return false;
   *stages = ns;
   return true;
@@ -1143,7 +1160,7 @@ cudaError_t launch_tma_v(FwdParams p, int dir, int stages, cudaStream_t st) {
   p.ndirs = 1;
   p.tma_stages = stages;
   const int groups = VERT ? p.nimg * (p.W >> 2) : (p.nimg * p.H + 3) >> 2;
-  const size_t smem = tma_smem_bytes(p.L, p.D, stages);
+  const size_t smem = tma_smem_bytes(p.L, DT, stages);
   cudaError_t e = ensure_smem(fwd_tma_kernel<LMAX, LT, DT, TRAIN, VERT, FWD>, smem);
   if (e != cudaSuccess) return e;
   TmaMaps maps{};
@@ -1172,6 +1189,7 @@ cudaError_t launch_tma_d(const FwdParams& p, int dir, int stages, cudaStream_t s
 
 template <int LMAX, int LT, bool TRAIN>
 cudaError_t launch_tma(const FwdParams& p, int dir, int stages, cudaStream_t st) {
+  if (p.agg) return launch_tma_d<LMAX, LT, 2, TRAIN>(p, dir, stages, st);
   if (p.D == 4) return launch_tma_d<LMAX, LT, 4, TRAIN>(p, dir, stages, st);
   return launch_tma_d<LMAX, LT, 8, TRAIN>(p, dir, stages, st);
 }
@@ -1180,7 +1198,7 @@ template <int MODE, bool TRAIN>
 cudaError_t launch_cta(const FwdParams& p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int NT = MODE == 2 ? 64 : ((p.L + 31) / 32) * 32;
-  const size_t smem = ((size_t)kPF * (p.D + 2) * NT + 2 * NT + 32) * sizeof(float);
+  const size_t smem = ((size_t)kPF * ((p.agg ? 2 : p.D) + 2) * NT + 2 * NT + 32) * sizeof(float);
   cudaError_t e = ensure_smem(fwd_cta_kernel<MODE, TRAIN>, smem);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
@@ -1193,7 +1211,7 @@ template <int MODE, bool TRAIN>
 cudaError_t launch_cta_tma(FwdParams p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int NT = MODE == 2 ? 64 : ((p.L + 31) / 32) * 32;
-  const int A = p.D + 1;
+  const int A = (p.agg ? 2 : p.D) + 1;
   int K = 16, NS = 3;
   auto bytes = [&](int k, int ns) {
     return ((size_t)ns * A * k * p.L + 2 * k + 2 * NT + 32) * sizeof(float) + 2 * ns * 8 + 16;
@@ -1216,7 +1234,7 @@ cudaError_t launch_cta_tma(FwdParams p, cudaStream_t st) {
 template <int LPT, int RW, int DT>
 cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
-  const int A = p.D + 1;
+  const int A = (p.agg ? 2 : p.D) + 1;
   constexpr int G = ((RW - 1 + 3) / 4) * 4;
   int K = 8, NS = 3;
   auto bytes = [&](int k, int ns) {
@@ -1253,6 +1271,8 @@ cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
 
 template <int LPT, int RW>
 cudaError_t launch_wide(const FwdParams& p, cudaStream_t st) {
+  if (p.agg) return launch_wide_d<LPT, RW, 2>(p, st);
+  if (p.D == 2) return cudaErrorNotSupported;  // DT == 2 is reserved for the aggregate mode
   if (p.D == 4) return launch_wide_d<LPT, RW, 4>(p, st);
   if (p.D == 8) return launch_wide_d<LPT, RW, 8>(p, st);
   return launch_wide_d<LPT, RW, 0>(p, st);
@@ -1317,7 +1337,8 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
     if (p.L == 21) return train ? launch_warp<21, true>(rest, st) : launch_warp<21, false>(rest, st);
     return train ? launch_warp<32, true>(rest, st) : launch_warp<32, false>(rest, st);
   }
-  if (p.ctx_rank == 1 && !train && p.host_windowed && p.host_R <= 16 && p.L <= 256 && cta_tma_eligible(p)) {
+  if (p.ctx_rank == 1 && !train && p.host_windowed && p.host_R <= 16 && p.L <= 256 && cta_tma_eligible(p) &&
+      (p.agg || p.D != 2)) {
     const int lpt = 2 * ((p.L + 63) / 64);
     switch (lpt) {
       case 2: return launch_wide_r<2>(p, p.host_R, st);
