@@ -33,6 +33,9 @@ WORKLOADS = {
     "denoise_isgmr_infer": ("config3_denoise", {}, False),
     "large_isgmr_train": ("config5_large", {}, True),
     "config1_trwp_train": ("config1", {"mode": "TRWP"}, True),
+    "config1_isgmr_train": ("config1", {"mode": "ISGMR"}, True),
+    # reduced copy of large_isgmr_train (same labels / directions) that is small enough to profile
+    "large_isgmr_train_384": ("config5_large", {"H": 384, "W": 384, "n_iter": 4}, True),
 }
 
 
@@ -115,14 +118,14 @@ def units_per_step(cfg, batch):
 def algorithmic_bytes(cfg, batch, kind):
     """Bytes one sweep launch must move (fused model): forward 4L(D+2)+4 (+L+1 when indices are
     saved) per pixel and direction; backward 4L(2D+3)+L+9.  A TRWP launch covers one direction;
-    an ISGMR forward launch covers all D directions of an iteration."""
+    an ISGMR launch (forward or backward) covers all D directions of an iteration."""
     _, _, L, H, W = cfg["unary"].shape
     D = cfg["n_dir"]
     n = batch * H * W
     if kind == "fwd":
         per_dir = n * (4 * L * (D + 2) + 4 + ((L + 1) if cfg["training"] else 0))
         return per_dir * (D if cfg["mode"] == "ISGMR" else 1)
-    return n * (4 * L * (2 * D + 3) + L + 9)
+    return n * (4 * L * (2 * D + 3) + L + 9) * (D if cfg["mode"] == "ISGMR" else 1)
 
 
 def dominant_kernel(cfg, kind):

@@ -294,11 +294,10 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
   // TRWP with L <= 32 keeps the message gradients as dM_k = C + P_k (C in `dunary`, P in `dmsg`),
   // see BwdParams::cp_scheme; everything else updates dunary and the D slices directly.
-  const int cp = (!isgmr && L <= 32) ? 1 : 0;
+  const int cp = isgmr ? 2 : (L <= 32 ? 1 : 0);
   float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced
   float* Y = isgmr ? dmsg : dmsg;         // gradients of the messages the sweeps read
-  MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp, st));
-  if (isgmr) MPL_CUDA(cudaMemsetAsync(Y, 0, (size_t)D * d.slice * sizeof(float), st));
+  MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp == 1, st));
   int* status = reinterpret_cast<int*>(part + (size_t)n_slots * d.ctx_elems);
   MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
 
@@ -321,19 +320,27 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   bp.cp_scheme = cp;
   bp.status = status;
   for (int it = p->n_iter - 1; it >= 0; --it) {
-    for (int dir = D - 1; dir >= 0; --dir) {
-      bp.dir = dir;
-      bp.min_idx = msg_min_index + ((long long)it * D + dir) * d.slice;
-      bp.norm_idx = msg_norm_index + ((long long)it * D + dir) * d.npix;
+    bp.min_idx = msg_min_index + (long long)it * D * d.slice;
+    bp.norm_idx = msg_norm_index + (long long)it * D * d.npix;
+    bp.dew = (edge_weights && dedge_weights) ? dedge_weights : nullptr;
+    if (isgmr) {
+      // The D sweeps of an iteration are independent: one launch reads dMU (X) and stores the
+      // scatter fields q_d (Y); the combine kernel then rewrites X with the gradients of the
+      // messages this iteration read and adds rho * sum_d q_d to dunary.
+      bp.dir = 0;
+      bp.ndirs = D;
       bp.dm_read = X;
       bp.dm_acc = Y;
-      bp.dew = (edge_weights && dedge_weights) ? dedge_weights + (long long)dir * d.npix : nullptr;
       MPL_CUDA(mpl::launch_backward_sweep(bp, st));
-    }
-    if (isgmr) {  // every slice of X has been zeroed by its sweep: it becomes the next accumulator
-      float* t = X;
-      X = Y;
-      Y = t;
+      MPL_CUDA(mpl::launch_isgmr_combine(Y, X, dunary, d.slice, D, p->rho, st));
+    } else {
+      for (int dir = D - 1; dir >= 0; --dir) {
+        bp.dir = dir;
+        bp.ndirs = 1;
+        bp.dm_read = X;
+        bp.dm_acc = Y;
+        MPL_CUDA(mpl::launch_backward_sweep(bp, st));
+      }
     }
   }
   MPL_CUDA(mpl::launch_dctx_reduce(part, n_slots, L, p->context_rank, p->keep_diag, dcontext, st));

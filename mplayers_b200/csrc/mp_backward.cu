@@ -24,14 +24,18 @@ namespace mpl {
 namespace {
 
 struct BChain {
-  int img, h0, w0, len, pstep;
+  int dir, img, h0, w0, len, pstep;
 };
 
 __device__ __forceinline__ bool decode_bchain(const BwdParams& p, int g, BChain& c) {
-  const DirGeom geo = make_geom(p.dir, p.H, p.W);
-  if (g >= geo.n_chains * p.nimg) return false;
-  c.img = g / geo.n_chains;
-  chain_start(geo, p.H, p.W, g - c.img * geo.n_chains, c.h0, c.w0, c.len);
+  if (g >= p.chain_off[p.ndirs]) return false;
+  int di = 0;
+  while (g >= p.chain_off[di + 1]) ++di;
+  c.dir = p.dir + di;
+  const DirGeom geo = make_geom(c.dir, p.H, p.W);
+  const int local = g - p.chain_off[di];
+  c.img = local / geo.n_chains;
+  chain_start(geo, p.H, p.W, local - c.img * geo.n_chains, c.h0, c.w0, c.len);
   c.pstep = geo.hs * p.W + geo.ws;
   return true;
 }
@@ -114,11 +118,13 @@ __host__ __device__ inline int bwd_warp_floats(int L, int rank, int cp) {
   return (cp ? 2 : 1) * kRB * kRS + 32 * kRS + 128 + ((tab + 3) & ~3);
 }
 
-template <int DT, bool CP>
+template <int DT, int SCH>
 __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant__ BwdParams p) {
+  constexpr bool CP = SCH == 1;   // C + P bookkeeping
+  constexpr bool QM = SCH == 2;   // store the scatter field only
   extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int L = p.L, D = DT ? DT : p.D, dir = p.dir, inv = dir ^ 1;
+  const int L = p.L, D = DT ? DT : p.D;
   const int LS = L | 1;  // odd row stride: private rows without bank conflicts
   // full (symmetric / Toeplitz) context table shared by the CTA
   float* ctab = smem;
@@ -129,6 +135,7 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
   const int g = blockIdx.x * wpb + warp;
   BChain ch;
   if (!decode_bchain(p, g, ch)) return;
+  const int dir = ch.dir, inv = dir ^ 1;
   const int tab = p.ctx_rank == 2 ? L * LS : 32;
   float* ring = smem + ctab_floats + warp * bwd_warp_floats(L, p.ctx_rank, CP);  // [kRB][kRS] (x2 if CP)
   float* ring2 = ring + kRB * kRS;                                              // CP: P_dir rows
@@ -146,9 +153,9 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
   float* DMal = p.dm_acc + ibase * L + lane;
   float* DUl = p.dunary + ibase * L + lane;                              // dU, or C
   const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
-  float* DE = p.dew ? p.dew + ibase : nullptr;
-  const uint8_t* MIl = p.min_idx + ibase * L + lane;
-  const uint8_t* NI = p.norm_idx + ibase;
+  float* DE = p.dew ? p.dew + (long long)dir * p.pslice + ibase : nullptr;
+  const uint8_t* MIl = p.min_idx + (long long)dir * p.slice + ibase * L + lane;
+  const uint8_t* NI = p.norm_idx + (long long)dir * p.pslice + ibase;
   const int len = ch.len;
   const int pstep = ch.pstep, ostep = ch.pstep * L;
   const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * pstep;  // last pixel of the chain
@@ -251,7 +258,9 @@ __global__ void __launch_bounds__(128, 1) bwd_warp_kernel(const __grid_constant_
             qn = gather_q<0>(tb, ib, L, (float)lane);
           }
           if (act) {
-            if (CP) {
+            if (QM) {
+              DMal[(long long)dir * p.slice + of] = q;  // scatter field of this direction at this pixel
+            } else if (CP) {
               const float cnew = x0 + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
               DUl[of] = cnew;
               DMrl[of] = -cnew;            // dM_dir = C + P_dir = 0 after its sweep
@@ -426,9 +435,9 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
   float* Pdl = p.dm_read + (long long)dir * p.slice + ibase * L + lc;
   float* Pil = p.dm_read + (long long)inv * p.slice + ibase * L + lc;
   const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
-  float* DE = p.dew ? p.dew + ibase : nullptr;
-  const uint8_t* MIl = p.min_idx + ibase * L + lc;
-  const uint8_t* NI = p.norm_idx + ibase;
+  float* DE = p.dew ? p.dew + (long long)dir * p.pslice + ibase : nullptr;
+  const uint8_t* MIl = p.min_idx + (long long)dir * p.slice + ibase * L + lc;
+  const uint8_t* NI = p.norm_idx + (long long)dir * p.pslice + ibase;
   const float rho = p.rho;
   const int sa = VERT ? kBK * 4 * L : kBK * L;        // C -> P_dir inside a tile
   const int sk = (VERT ? 4 * L : L) * (REV ? -1 : 1);  // consecutive steps inside a tile
@@ -578,8 +587,9 @@ __global__ void __launch_bounds__(256) bwd_cta_kernel(const __grid_constant__ Bw
   extern __shared__ __align__(16) float smem[];
   BChain ch;
   if (!decode_bchain(p, blockIdx.x, ch)) return;  // uniform
-  const int L = p.L, D = p.D, dir = p.dir, inv = dir ^ 1, NT = blockDim.x, c = threadIdx.x;
+  const int L = p.L, D = p.D, dir = ch.dir, inv = dir ^ 1, NT = blockDim.x, c = threadIdx.x;
   const int nw = NT >> 5, lane = c & 31, warp = c >> 5;
+  const bool qmode = p.cp_scheme == 2;
   const int LS = L | 1;
   float* ring = smem;                          // [kPFB][NT]
   float* ts = ring + kPFB * NT;                // [2][NT]
@@ -598,9 +608,9 @@ __global__ void __launch_bounds__(256) bwd_cta_kernel(const __grid_constant__ Bw
   float* DMa = p.dm_acc + ibase * L;
   float* DU = p.dunary + ibase * L;
   const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
-  float* DE = p.dew ? p.dew + ibase : nullptr;
-  const uint8_t* MI = p.min_idx + ibase * L;
-  const uint8_t* NI = p.norm_idx + ibase;
+  float* DE = p.dew ? p.dew + (long long)dir * p.pslice + ibase : nullptr;
+  const uint8_t* MI = p.min_idx + (long long)dir * p.slice + ibase * L;
+  const uint8_t* NI = p.norm_idx + (long long)dir * p.pslice + ibase;
   const int len = ch.len;
   const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * ch.pstep;
   const float rho = p.rho;
@@ -690,12 +700,16 @@ __global__ void __launch_bounds__(256) bwd_cta_kernel(const __grid_constant__ Bw
         if (ib[k] == c) qn += tb[k];
     }
     if (act) {
-      for (int k = 0; k < D; ++k) {
-        if (k == dir) continue;
-        atomicAdd(DMa + k * p.slice + o, k == inv ? fmaf(rho, q, -q) : rq);
+      if (qmode) {
+        DMa[(long long)dir * p.slice + o] = q;  // scatter field of this direction at this pixel
+      } else {
+        for (int k = 0; k < D; ++k) {
+          if (k == dir) continue;
+          atomicAdd(DMa + k * p.slice + o, k == inv ? fmaf(rho, q, -q) : rq);
+        }
+        atomicAdd(DU + o, rq);
+        DMr[o] = 0.f;
       }
-      atomicAdd(DU + o, rq);
-      DMr[o] = 0.f;
     }
     issue(s + kPFB);
     i0 = i1;
@@ -728,6 +742,27 @@ __global__ void backward_init_kernel(const float* __restrict__ g, float* __restr
     const float v = g[i];
     dunary[i] = cp ? v : factor * v;
     for (int k = 0; k < D; ++k) dm[k * n + i] = cp ? 0.f : v;
+  }
+}
+
+// ISGMR, cp_scheme 2: after the D independent sweeps of an iteration have stored their scatter
+// fields q_d, the gradients of the messages that iteration read are
+//   dM_k = rho * Q - rho * q_k - q_inv(k),   Q = sum_d q_d,   and   dU += rho * Q
+// (what the reference accumulates with D+3 atomics per element and sweep,
+// MPLayers/ISGMR/ISGMR_backward.cu:39-60, followed by SumMsgKernel and a copy, :482-483).
+__global__ void isgmr_combine_kernel(const float* __restrict__ q, float* __restrict__ dm,
+                                     float* __restrict__ dunary, long long n, int D, float rho) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float qv[16];
+    float Q = 0.f;
+    for (int d = D - 1; d >= 0; --d) {  // the order in which the reference's sweeps add
+      qv[d] = q[d * n + i];
+      Q += qv[d];
+    }
+    const float rQ = rho * Q;
+    dunary[i] += rQ;
+    for (int k = 0; k < D; ++k) dm[k * n + i] = (rQ - rho * qv[k]) - qv[k ^ 1];
   }
 }
 
@@ -779,7 +814,7 @@ size_t bwd_tma_smem_bytes(int L, int rank, int stages) {
 }
 
 bool bwd_tma_eligible(const BwdParams& p) {
-  if (!p.cp_scheme || p.dir > 3 || p.L > 32) return false;
+  if (p.cp_scheme != 1 || p.dir > 3 || p.L > 32) return false;
   if ((p.W & 3) || (((long long)p.W * p.L) & 3)) return false;
   if (((uintptr_t)p.dunary | (uintptr_t)p.dm_read) & 15) return false;
   return true;
@@ -812,12 +847,26 @@ cudaError_t launch_bwd_tma(const BwdParams& p, cudaStream_t st) {
 
 }  // namespace
 
+cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long long n, int D, float rho,
+                                 cudaStream_t st) {
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ProfScope prof(kProfElementwise, st);
+  isgmr_combine_kernel<<<(int)blocks, 256, 0, st>>>(q, dm, dunary, n, D, rho);
+  count_launch();
+  return cudaGetLastError();
+}
+
 int backward_slots(int H, int W, int L, int D, int nimg) {
-  long long mx = 1;
+  // one partial table per chain of a launch where that stays modest (deterministic sums); a launch
+  // covers one direction (TRWP) or all of them (ISGMR), the larger count is provisioned
+  long long mx = 1, sum = 0;
   for (int d = 0; d < D; ++d) {
     const long long n = (long long)make_geom(d, H, W).n_chains * nimg;
     if (n > mx) mx = n;
+    sum += n;
   }
+  if (sum <= 4096) mx = sum;
   if (mx > 4096) mx = 4096;
   return (int)mx;
 }
@@ -834,7 +883,11 @@ cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, l
 
 cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
   BwdParams p = p0;
-  const int total = make_geom(p.dir, p.H, p.W).n_chains * p.nimg;
+  if (p.ndirs < 1) p.ndirs = 1;
+  p.chain_off[0] = 0;
+  for (int i = 0; i < p.ndirs; ++i)
+    p.chain_off[i + 1] = p.chain_off[i] + make_geom(p.dir + i, p.H, p.W).n_chains * p.nimg;
+  const int total = p.chain_off[p.ndirs];
   if (total == 0) return cudaSuccess;
   const int L = p.L, LS = L | 1;
   ProfScope prof(kProfBwdSweep, st);
@@ -844,7 +897,7 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
     if (e != cudaSuccess) return e;
   } else if (L <= 32) {
     const int wpb = total >= 148 * 32 ? 4 : 1;
-    const size_t smem = ((size_t)((L * LS + 3) & ~3) + (size_t)wpb * bwd_warp_floats(L, p.ctx_rank, p.cp_scheme)) *
+    const size_t smem = ((size_t)((L * LS + 3) & ~3) + (size_t)wpb * bwd_warp_floats(L, p.ctx_rank, p.cp_scheme == 1)) *
                         sizeof(float);
     auto go = [&](auto kernel) -> cudaError_t {
       if (smem > 48 * 1024) {
@@ -855,11 +908,12 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
       return cudaSuccess;
     };
     cudaError_t e;
-    if (p.cp_scheme) {
-      e = go(bwd_warp_kernel<0, true>);
+    if (p.cp_scheme == 1) {
+      e = go(bwd_warp_kernel<0, 1>);
+    } else if (p.cp_scheme == 2) {
+      e = go(bwd_warp_kernel<0, 2>);
     } else {
-      e = p.D == 4 ? go(bwd_warp_kernel<4, false>) : p.D == 8 ? go(bwd_warp_kernel<8, false>)
-                                                              : go(bwd_warp_kernel<0, false>);
+      e = p.D == 4 ? go(bwd_warp_kernel<4, 0>) : p.D == 8 ? go(bwd_warp_kernel<8, 0>) : go(bwd_warp_kernel<0, 0>);
     }
     if (e != cudaSuccess) return e;
   } else {

@@ -108,25 +108,30 @@ struct FwdParams {
 struct BwdParams {
   const float* ctx;
   const float* ew;        // or nullptr (= 1)
-  const uint8_t* min_idx; // slice [nimg,H,W,L] of (iter, dir)
-  const uint8_t* norm_idx;
+  const uint8_t* min_idx; // [D,nimg,H,W,L] of this iteration
+  const uint8_t* norm_idx; // [D,nimg,H,W]
   float* dm_read;         // [D,...]: slice `dir` holds the gradient of this sweep's messages; zeroed here
   float* dm_acc;          // [D,...]: gradient of the messages the sweep read (TRWP: == dm_read)
   float* dunary;
-  float* dew;             // slice of `dir`, or nullptr
+  float* dew;             // [D,nimg,H,W], or nullptr
   float* dctx_part;       // [n_slots, ctx_table] partial tables
   int n_slots;
   int H, W, L, D, nimg;
   long long slice, pslice;
   float rho;
   int ctx_rank, keep_diag;
-  int dir;
+  int dir;                // first direction of this launch
+  int ndirs;              // directions covered (more than one only with cp_scheme == 2)
+  int chain_off[17];      // prefix sums of nimg*n_chains over those directions
   int table_in_smem;      // CTA kernel: 1 = [L][L|1] table in shared memory
   // Gradient bookkeeping.  cp_scheme == 0: `dunary` and the D slices of `dm_acc` are updated with
   // one reduction each per pixel (the reference's UpdateUnaryKernelBack).  cp_scheme == 1 (TRWP,
   // L <= 32): the message gradients are kept as dM_k = C + P_k with the common part C stored in
   // `dunary` (dU and every dM_k receive the same increment rho*q) and P_k in `dm_read`; a sweep
-  // then rewrites C and P_dir and corrects P_inv only.
+  // then rewrites C and P_dir and corrects P_inv only.  cp_scheme == 2 (ISGMR): a sweep only stores
+  // its scatter field q_dir (into slice `dir` of `dm_acc`); the D sweeps of an iteration are
+  // independent and run in one launch, and isgmr_combine_kernel afterwards forms
+  // dM_k = rho*Q - rho*q_k - q_inv(k), dU += rho*Q with Q = sum_d q_d.
   int cp_scheme;
   int tma_stages;
   int* status;            // device word: 0 = ok, else the code of a wait that gave up
@@ -248,6 +253,8 @@ cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, 
 cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,
                                  float factor, int cp_scheme, cudaStream_t st);
 cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
+cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long long n, int D, float rho,
+                                 cudaStream_t st);
 cudaError_t launch_dctx_reduce(float* part, int n_slots, int L, int rank, int keep_diag,
                                float* dctx, cudaStream_t st);
 int backward_slots(int H, int W, int L, int D, int nimg);
