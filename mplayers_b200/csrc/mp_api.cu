@@ -294,7 +294,11 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
   // TRWP with L <= 32 keeps the message gradients as dM_k = C + P_k (C in `dunary`, P in `dmsg`),
   // see BwdParams::cp_scheme; everything else updates dunary and the D slices directly.
-  const int cp = isgmr ? 2 : (L <= 32 ? 1 : 0);
+  // (L <= 64 in multiples of four at 16-byte aligned buffers runs the two-labels-per-lane kernel,
+  // which knows the C + P scheme as well.)
+  const bool pair_cp = L <= 64 && (L & 3) == 0 && ((((uintptr_t)dunary | (uintptr_t)dmsg) & 15) == 0) &&
+                       !mpl::pair_kernels_disabled();
+  const int cp = isgmr ? 2 : ((L <= 32 || pair_cp) ? 1 : 0);
   float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced
   float* Y = isgmr ? dmsg : dmsg;         // gradients of the messages the sweeps read
   MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp == 1, st));

@@ -17,6 +17,8 @@
 //     one warp reduction per step.  The normalisation sum is taken over the stored gradient
 //     alone: the part carried from the successor pixel sums to zero (it is itself the output of
 //     a normalisation backward), so only rounding noise is dropped.
+#include <cstdlib>
+
 #include "mp_common.cuh"
 
 namespace mpl {
@@ -578,6 +580,294 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// 32 < L <= 64, L % 4 == 0: one WARP per chain, TWO labels per lane (2*lane, 2*lane + 1), schemes
+// 1 (C + P) and 2 (scatter field).  No block barrier: the CTA-per-chain kernel pays two per step
+// plus a cross-warp reduction.  The stored gradients are staged kPB steps per stage by the warp
+// itself (lane-parallel cp.async.bulk copies: one per array and stage for horizontal chains, one
+// label row per pixel otherwise) with completion on the warp's own mbarriers, bounded waits.
+// ------------------------------------------------------------------------------------------------
+constexpr int kPB = 16;   // steps per stage (and per block of per-pixel scalars)
+constexpr int kPNS = 2;   // stages in flight
+
+// floats of shared memory per warp (the CTA adds one [L][L|1] context table)
+__host__ __device__ inline int bwd_pair_floats(int L, int rank, int sch) {
+  const int tab = rank == 2 ? L * (L | 1) : 64;
+  return kPNS * (sch == 1 ? 2 : 1) * kPB * L + kPNS * kPB * L / 4 + kPB * 33 + 256 + ((tab + 3) & ~3) + 2 * kPNS + 2;
+}
+
+// q0 / q1: scatter sums of labels me0, me0 + 1 over the 64 (padded) labels of one pixel.
+// FULL: all 64 labels exist (no loop bound to test).
+template <bool FULL>
+__device__ __forceinline__ void gather_q2(const float* tb, const float* ib, int L, float me0, float& q0,
+                                          float& q1) {
+  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  const float me1 = me0 + 1.f;
+  auto body = [&](int v) {
+    const float4 t = reinterpret_cast<const float4*>(tb)[v];
+    const float4 i = reinterpret_cast<const float4*>(ib)[v];
+    a0 = fmaf(eq_flag(i.x, me0), t.x, a0);
+    b0 = fmaf(eq_flag(i.x, me1), t.x, b0);
+    a1 = fmaf(eq_flag(i.y, me0), t.y, a1);
+    b1 = fmaf(eq_flag(i.y, me1), t.y, b1);
+    a0 = fmaf(eq_flag(i.z, me0), t.z, a0);
+    b0 = fmaf(eq_flag(i.z, me1), t.z, b0);
+    a1 = fmaf(eq_flag(i.w, me0), t.w, a1);
+    b1 = fmaf(eq_flag(i.w, me1), t.w, b1);
+  };
+  if constexpr (FULL) {
+#pragma unroll
+    for (int v = 0; v < 16; ++v) body(v);
+  } else {
+    const int nv = L >> 2;
+#pragma unroll 3
+    for (int v = 0; v < nv; ++v) body(v);
+  }
+  q0 = a0 + a1;
+  q1 = b0 + b1;
+}
+
+// Nothing in the step loop loads from global memory into registers except the per-block scalars:
+// gradients arrive by bulk copy, argmin indices by cp.async, context values come from a table in
+// shared memory.  (Register prefetches of several kinds share the few hardware scoreboards, and a
+// use of a cached value then waits for the DRAM loads issued next to it.)
+template <int SCH, bool FULL>
+__global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant__ BwdParams p) {
+  constexpr bool CP = SCH == 1;
+  constexpr int NA = CP ? 2 : 1;  // staged arrays: (C, P_dir) or the gradient slice of the direction
+  extern __shared__ __align__(128) float smem[];
+  const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = FULL ? 64 : p.L, LS = L | 1;
+  const int ctab_floats = (L * LS + 3) & ~3;
+  float* ctab = smem;                              // [L][LS] full context table of the CTA
+  for (int i = threadIdx.x; i < L * L; i += blockDim.x)
+    ctab[(i / L) * LS + (i % L)] = ctx_value(p.ctx, p.ctx_rank, L, i / L, i % L);
+  const int per_warp = (bwd_pair_floats(L, p.ctx_rank, SCH) + 3) & ~3;
+  float* ring = smem + ctab_floats + warp * per_warp;  // [kPNS][NA][kPB][L]
+  const int stage_floats = NA * kPB * L;
+  uint8_t* itile = reinterpret_cast<uint8_t*>(ring + kPNS * stage_floats);  // [kPNS][kPB][L] argmin indices
+  float* dtile = ring + kPNS * stage_floats + kPNS * kPB * L / 4;           // [kPB][33]
+  float* ts = dtile + kPB * 33;                    // [2][64]  (kPB * 33 is a multiple of 4)
+  float* is = ts + 128;                            // [2][64] argmin as float
+  float* acc = is + 128;                           // context-gradient table of this chain
+  const int tab = p.ctx_rank == 2 ? L * LS : 64;
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(acc + ((tab + 3) & ~3));
+  if (lane == 0) {
+    for (int i = 0; i < kPNS; ++i) mbar_init(&full[i], 1);
+    mbar_fence_init();
+  }
+  for (int i = lane; i < tab; i += 32) acc[i] = 0.f;
+  for (int i = lane; i < 128; i += 32) ts[i] = 0.f, is[i] = -1.f;
+  __syncthreads();
+  const int g = blockIdx.x * wpb + warp;
+  BChain ch;
+  if (!decode_bchain(p, g, ch)) return;
+  const int dir = ch.dir, inv = dir ^ 1;
+  const int c0 = 2 * lane;
+  const bool act = c0 < L;  // L is even: a lane owns two labels or none
+
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  float* DMr = p.dm_read + (long long)dir * p.slice + ibase * L;  // dM_dir, or P_dir
+  float* DMa = p.dm_acc + ibase * L;
+  float* DU = p.dunary + ibase * L;                               // dU, or C
+  const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
+  float* DE = p.dew ? p.dew + (long long)dir * p.pslice + ibase : nullptr;
+  const uint8_t* MI = p.min_idx + (long long)dir * p.slice + ibase * L;
+  const uint8_t* NI = p.norm_idx + (long long)dir * p.pslice + ibase;
+  const int len = ch.len, pstep = ch.pstep, ostep = pstep * L;
+  const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * pstep;  // last pixel of the chain
+  const float rho = p.rho;
+  const int nsteps = len - 1;               // steps with a predecessor pixel
+  const int nrows = CP ? len : nsteps;      // staged pixels (C + P also rewrites the chain-start pixel)
+  const bool contiguous = pstep == 1 || pstep == -1;
+  const int nblocks = (len + kPB - 1) / kPB;
+
+  auto stage_rows = [&](int b) {
+    const int r = nrows - kPB * b;
+    return r < 0 ? 0 : (r > kPB ? kPB : r);
+  };
+  // step s = kPB*b + u visits image pixel pixl - s*pstep; its row in the stage tile is u, except
+  // for chains walked towards decreasing addresses in one copy (pstep == +1), which land reversed
+  auto issue_stage = [&](int b) {
+    const int rows = stage_rows(b);
+    const int slot = b % kPNS;
+    const int s0 = kPB * b;
+    if (rows > 0) {
+      float* T = ring + slot * stage_floats;
+      if (lane == 0) {
+        fence_proxy_async_smem();
+        mbar_arrive_expect_tx(&full[slot], (unsigned)(rows * NA * L) * 4u);
+      }
+      __syncwarp();
+      if (contiguous) {
+        const int first = pstep == 1 ? pixl - (s0 + rows - 1) : pixl + s0;
+        if (lane < NA)
+          bulk_g2s(T + lane * kPB * L, (CP && lane == 0 ? DU : DMr) + (long long)first * L,
+                   (unsigned)(rows * L) * 4u, &full[slot]);
+      } else {
+        for (int q = lane; q < rows * NA; q += 32) {
+          const int u = q / NA, a = q - u * NA;
+          const int px = pixl - (s0 + u) * pstep;
+          bulk_g2s(T + (a * kPB + u) * L, (CP && a == 0 ? DU : DMr) + (long long)px * L, (unsigned)L * 4u,
+                   &full[slot]);
+        }
+      }
+    }
+    // argmin indices of the steps with a predecessor: four labels per lane and step
+    if (4 * lane < L) {
+      uint8_t* dst = itile + (slot * kPB) * L + 4 * lane;
+      const uint8_t* src = MI + (long long)(pixl - s0 * pstep) * L + 4 * lane;
+#pragma unroll 4
+      for (int u = 0; u < kPB; ++u) {
+        if (s0 + u < nsteps)
+          cp_async4(reinterpret_cast<float*>(dst + u * L), reinterpret_cast<const float*>(src - (long long)u * ostep));
+      }
+    }
+    cp_async_commit();
+  };
+  auto load_blk = [&](int b, float& eb, int& nb) {  // lane l: scalars of step kPB*b + (l & 15)
+    const int s = kPB * b + (lane & (kPB - 1));
+    eb = 1.f;
+    nb = 0;
+    if (s < nsteps) {
+      const int px = pixl - s * pstep;
+      if (E) eb = E[px];
+      nb = NI[px];
+    }
+  };
+
+  for (int b = 0; b < kPNS; ++b) issue_stage(b);
+  float e_cur, e_nxt;
+  int n_cur, n_nxt;
+  load_blk(0, e_cur, n_cur);
+
+  float q0 = 0.f, q1 = 0.f;  // scatter sums carried from the successor pixel (labels c0, c0 + 1)
+  int of = pixl * L + c0;
+  for (int b = 0; b < nblocks; ++b) {
+    load_blk(b + 1, e_nxt, n_nxt);
+    const int rows = stage_rows(b);
+    const int slot = b % kPNS;
+    const float* T = ring + slot * stage_floats;
+    const uint8_t* IT = itile + (slot * kPB) * L + c0;
+    cp_async_wait<kPNS - 1>();
+    if (rows > 0 && !mbar_wait(&full[slot], (b / kPNS) & 1)) {
+      if (lane == 0) atomicExch(p.status, 141);
+      return;
+    }
+    __syncwarp();
+    const bool flip = contiguous && pstep == 1;
+    // normalisation sums of the block: lanes j and j + 16 each sum one half of the row of step j
+    float s_cur = 0.f;
+    {
+      const int u = lane & (kPB - 1), half = lane >> 4;
+      if (u < rows) {
+        const int hl = L >> 1;  // even halves (L % 4 == 0)
+        const float* row = T + (flip ? rows - 1 - u : u) * L + half * hl;
+        float sa = 0.f, sb = 0.f;
+        int c = lane >= hl ? lane - hl : lane;  // rotated start: lanes hit distinct banks
+#pragma unroll 4
+        for (int i = 0; i < hl; i += 2) {
+          sa += CP ? row[c] + row[c + kPB * L] : row[c];
+          c = c + 1 >= hl ? 0 : c + 1;
+          sb += CP ? row[c] + row[c + kPB * L] : row[c];
+          c = c + 1 >= hl ? 0 : c + 1;
+        }
+        s_cur = sa + sb;
+      }
+      s_cur += __shfl_xor_sync(0xffffffffu, s_cur, 16);
+    }
+    const int send = len - kPB * b < kPB ? len - kPB * b : kPB;
+    for (int sl = 0; sl < send; ++sl) {
+      const int s = kPB * b + sl;
+      const float rq0 = rho * q0, rq1 = rho * q1;
+      float qn0 = 0.f, qn1 = 0.f;
+      float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
+      if (act && sl < rows) {
+        const float* row = T + (flip ? rows - 1 - sl : sl) * L + c0;
+        x0 = *reinterpret_cast<const float2*>(row);
+        if (CP) x1 = *reinterpret_cast<const float2*>(row + kPB * L);
+      }
+      if (s < nsteps) {
+        const float e = __shfl_sync(0xffffffffu, e_cur, sl);
+        const int n = __shfl_sync(0xffffffffu, n_cur, sl);
+        const float S = __shfl_sync(0xffffffffu, s_cur, sl);
+        float t0 = 0.f, t1 = 0.f, cv0 = 0.f, cv1 = 0.f;
+        if (act) {
+          const uchar2 fi = *reinterpret_cast<const uchar2*>(IT + sl * L);
+          const int f0 = fi.x, f1 = fi.y;
+          t0 = x0.x + x1.x + rq0;
+          t1 = x0.y + x1.y + rq1;
+          t0 = (c0 == n) ? t0 - S : t0;  // MPLayers/commonCUDA.cuh:131-145
+          t1 = (c0 + 1 == n) ? t1 - S : t1;
+          cv0 = ctab[c0 * LS + f0];
+          cv1 = ctab[(c0 + 1) * LS + f1];
+          if (p.ctx_rank == 2) {
+            if (c0 != f0 || p.keep_diag) acc[c0 * LS + f0] += e * t0;
+            if (c0 + 1 != f1 || p.keep_diag) acc[(c0 + 1) * LS + f1] += e * t1;
+          } else {
+            if (c0 != f0 || p.keep_diag) atomicAdd(acc + (c0 > f0 ? c0 - f0 : f0 - c0), e * t0);
+            if (c0 + 1 != f1 || p.keep_diag) atomicAdd(acc + (c0 + 1 > f1 ? c0 + 1 - f1 : f1 - c0 - 1), e * t1);
+          }
+          float* tb = ts + (s & 1) * 64;
+          float* ib = is + (s & 1) * 64;
+          *reinterpret_cast<float2*>(tb + c0) = make_float2(t0, t1);
+          *reinterpret_cast<float2*>(ib + c0) = make_float2((float)f0, (float)f1);
+        }
+        dtile[sl * 33 + lane] = fmaf(cv0, t0, cv1 * t1);
+        __syncwarp();
+        gather_q2<FULL>(ts + (s & 1) * 64, is + (s & 1) * 64, L, (float)c0, qn0, qn1);
+      }
+      if (act) {
+        if (!CP) {
+          // scatter field of this direction at this pixel
+          *reinterpret_cast<float2*>(DMa + (long long)dir * p.slice + of) = make_float2(q0, q1);
+        } else {
+          const float2 cn = make_float2(x0.x + rq0, x0.y + rq1);  // dU and every dM_k (k != dir, inv) receive rho*q
+          *reinterpret_cast<float2*>(DU + of) = cn;
+          *reinterpret_cast<float2*>(DMr + of) = make_float2(-cn.x, -cn.y);  // dM_dir = C + P_dir = 0 after its sweep
+          atomicAdd(DMa + inv * p.slice + of, -q0);
+          atomicAdd(DMa + inv * p.slice + of + 1, -q1);
+        }
+      }
+      q0 = qn0;
+      q1 = qn1;
+      of -= ostep;
+    }
+    // edge-weight gradients of this block: lane j sums row j of the product tile
+    __syncwarp();
+    if (DE && lane < kPB) {
+      const int s = kPB * b + lane;
+      if (s < nsteps) {
+        const float* row = dtile + lane * 33;
+        float da = 0.f, db = 0.f;
+#pragma unroll 8
+        for (int c = 0; c < 32; c += 2) da += row[c], db += row[c + 1];
+        atomicAdd(DE + (pixl - s * pstep), da + db);
+      }
+    }
+    __syncwarp();
+    issue_stage(b + kPNS);  // this warp refills the slot it has just consumed
+    e_cur = e_nxt;
+    n_cur = n_nxt;
+  }
+  cp_async_wait<0>();
+
+  // flush the context-gradient table of this chain
+  __syncwarp();
+  float* part = p.dctx_part + (long long)(g % p.n_slots) * (p.ctx_rank == 2 ? L * L : L);
+  if (p.ctx_rank == 2) {
+    for (int i = lane; i < L * L; i += 32) {
+      const float v = acc[(i / L) * LS + (i % L)];
+      if (v != 0.f) atomicAdd(part + i, v);
+    }
+  } else {
+    for (int i = lane; i < L; i += 32) {
+      const float v = acc[i];
+      if (v != 0.f) atomicAdd(part + i, v);
+    }
+  }
+}
+
 constexpr int kPFB = 8;  // CTA kernel: pixels of dM_d staged ahead (power of two)
 
 // ------------------------------------------------------------------------------------------------
@@ -820,6 +1110,13 @@ bool bwd_tma_eligible(const BwdParams& p) {
   return true;
 }
 
+bool bwd_pair_eligible(const BwdParams& p) {
+  if (p.L <= 32 || p.L > 64 || (p.L & 3) || p.cp_scheme == 0) return false;
+  if (((uintptr_t)p.dunary | (uintptr_t)p.dm_read | (uintptr_t)p.dm_acc) & 15) return false;
+  const char* e = getenv("MPL_NO_PAIR");  // tuning / comparison knob
+  return !(e && e[0] == '1');
+}
+
 template <int LT>
 cudaError_t launch_bwd_tma(const BwdParams& p, cudaStream_t st) {
   const bool vert = p.dir >= 2;
@@ -914,6 +1211,25 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
       e = go(bwd_warp_kernel<0, 2>);
     } else {
       e = p.D == 4 ? go(bwd_warp_kernel<4, 0>) : p.D == 8 ? go(bwd_warp_kernel<8, 0>) : go(bwd_warp_kernel<0, 0>);
+    }
+    if (e != cudaSuccess) return e;
+  } else if (bwd_pair_eligible(p)) {
+    const size_t per_warp = (size_t)((bwd_pair_floats(L, p.ctx_rank, p.cp_scheme) + 3) & ~3) * sizeof(float);
+    const size_t table = (size_t)((L * LS + 3) & ~3) * sizeof(float);
+    int wpb = (int)((227 * 1024 - table) / per_warp);
+    wpb = wpb > 8 ? 8 : wpb;
+    const size_t smem = table + per_warp * wpb;
+    auto go = [&](auto kernel) -> cudaError_t {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+      kernel<<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+      return cudaSuccess;
+    };
+    cudaError_t e;
+    if (L == 64) {
+      e = p.cp_scheme == 1 ? go(bwd_pair_kernel<1, true>) : go(bwd_pair_kernel<2, true>);
+    } else {
+      e = p.cp_scheme == 1 ? go(bwd_pair_kernel<1, false>) : go(bwd_pair_kernel<2, false>);
     }
     if (e != cudaSuccess) return e;
   } else {

@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through the runtime)
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <stdint.h>
 
 namespace mpl {
@@ -232,6 +233,18 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
           smem_u32(dst)),
       "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
+}
+
+// MPL_NO_PAIR=1 keeps 32 < L <= 64 on the CTA-per-chain kernels (tuning / comparison knob).
+inline bool pair_kernels_disabled() {
+  const char* e = getenv("MPL_NO_PAIR");
+  return e && e[0] == '1';
+}
+
+// Orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy
+// (bulk-copy) accesses; used by warps that refill a tile they have just finished reading.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // Global -> shared bulk copy (no multicast), completion counted in bytes on `bar`.

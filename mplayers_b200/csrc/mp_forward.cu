@@ -15,6 +15,8 @@
 //
 // Arithmetic follows the reference order (see Appendix of the oracle header): UU = ((U + M_0 + ...
 // + M_{D-1}) - M_d) * rho - M_inv, candidate = fma(E, ctx, fma(rho, r, UU)); ties -> highest index.
+#include <cstdlib>
+
 #include "mp_common.cuh"
 
 namespace mpl {
@@ -105,8 +107,9 @@ __device__ __forceinline__ constexpr float pow2f(int k) {
 // tree); then every candidate contributes (val[f] == min) * 2^f to a float accumulator with one
 // set + one fma (groups of 24 labels per accumulator, exact in a 24-bit mantissa), and the wanted
 // index is the exponent of the accumulator.
-template <int LMAX, bool TRAIN>
-__device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr)[LMAX], float e,
+// CN / OFF: `cr` has CN entries of which LMAX starting at OFF are used (hb points at candidate OFF).
+template <int LMAX, bool TRAIN, int CN = LMAX, int OFF = 0>
+__device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr)[CN], float e,
                                                float& best, int& bi) {
   constexpr int NV = (LMAX + 3) / 4;
   float hv[NV * 4];
@@ -120,7 +123,7 @@ __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr
   }
   float val[LMAX];
 #pragma unroll
-  for (int f = 0; f < LMAX; ++f) val[f] = fmaf(e, cr[f], hv[f]);
+  for (int f = 0; f < LMAX; ++f) val[f] = fmaf(e, cr[OFF + f], hv[f]);
   best = min_tree<LMAX>(val);
   bi = 0;
   if (TRAIN) {
@@ -1041,6 +1044,167 @@ __global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__
 }
 
 // ------------------------------------------------------------------------------------------------
+// 32 < L <= 64, rank-2 (dense) context, L % 4 == 0: one WARP per chain, TWO labels per lane, both
+// context rows of the lane in registers.  No block barrier (the CTA-per-chain kernel needs two per
+// step and two warps per chain).  Every warp stages its own inputs: lane-parallel cp.async.bulk
+// copies (one per array and stage for horizontal chains, one label row per pixel otherwise) into a
+// private ring, completion on the warp's own mbarriers, refilled by the warp itself as soon as it
+// has consumed a stage (no producer warp: it would hold as many registers as a consumer).
+// ------------------------------------------------------------------------------------------------
+constexpr int kPairWarps = 4;  // chains per CTA
+
+template <bool TRAIN>
+__global__ void __launch_bounds__(kPairWarps * 32, 1) fwd_pair_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(128) float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = p.L, D = p.agg ? 2 : p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
+  const int tile_floats = A * K * L;
+  const int per_warp = NS * tile_floats + 2 * 64 + 2 * K + 2 * NS + 2;  // floats (barriers are 2 each)
+  float* wbase = smem + warp * ((per_warp + 3) & ~3);
+  float* tiles = wbase;                               // [NS][A][K][L]
+  float* hbuf = tiles + NS * tile_floats;             // [2][64]
+  float* etile = hbuf + 128;                          // [2][K]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(etile + 2 * K + ((2 * K) & 1));
+  if (lane == 0)
+    for (int i = 0; i < NS; ++i) mbar_init(&full[i], 1);
+  hbuf[lane] = kInf, hbuf[32 + lane] = kInf, hbuf[64 + lane] = kInf, hbuf[96 + lane] = kInf;
+  if (lane == 0) mbar_fence_init();
+  __syncwarp();
+  ChainCtx ch;
+  if (!decode_chain(p, blockIdx.x * kPairWarps + warp, ch)) return;
+
+  const int len = ch.len;
+  const int nstages = (len + K - 1) / K;
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  const int pix0 = ch.h0 * p.W + ch.w0;
+  const bool contiguous = (ch.pstep == 1 || ch.pstep == -1);
+  const float* U = p.unary + ibase * L;
+  const float* Mr = p.msg_read + ibase * L;
+
+  auto issue_stage = [&](int s) {  // copies of stage s into slot s % NS (all lanes call)
+    if (s >= nstages) return;
+    const int slot = s % NS;
+    const int np = len - s * K < K ? len - s * K : K;
+    float* T = tiles + slot * tile_floats;
+    if (lane == 0) {
+      fence_proxy_async_smem();
+      mbar_arrive_expect_tx(&full[slot], (unsigned)(np * A * L) * 4u);
+    }
+    __syncwarp();
+    if (contiguous) {
+      const int first = ch.pstep == 1 ? pix0 + s * K : pix0 - (s * K + np - 1);
+      if (lane < A) {
+        const int sid = p.agg ? (lane == 1 ? ch.dir : ch.inv) : lane - 1;
+        const float* src = (lane == 0 ? U : Mr + (long long)sid * p.slice) + (long long)first * L;
+        bulk_g2s(T + lane * K * L, src, (unsigned)(np * L) * 4u, &full[slot]);
+      }
+    } else {
+      for (int q = lane; q < np * A; q += 32) {
+        const int k = q / A, a = q - k * A;
+        const int px = pix0 + (s * K + k) * ch.pstep;
+        const int sid = p.agg ? (a == 1 ? ch.dir : ch.inv) : a - 1;
+        const float* src = (a == 0 ? U : Mr + (long long)sid * p.slice) + (long long)px * L;
+        bulk_g2s(T + (a * K + k) * L, src, (unsigned)L * 4u, &full[slot]);
+      }
+    }
+  };
+
+  const int c0 = 2 * lane;          // labels c0, c0 + 1 (L is a multiple of four: both or none exist)
+  const bool act = c0 < L;
+  const int lc0 = act ? c0 : L - 2;  // idle lanes shadow the last pair: loads need no predicate
+  float cr0[64], cr1[64];
+#pragma unroll
+  for (int f = 0; f < 64; ++f) {
+    cr0[f] = (act && f < L) ? ctx_value(p.ctx, p.ctx_rank, L, c0, f) : 0.f;
+    cr1[f] = (act && f < L) ? ctx_value(p.ctx, p.ctx_rank, L, c0 + 1, f) : 0.f;
+  }
+  float* Mw = p.msg_write + (long long)ch.dir * p.slice + ibase * L + c0;
+  const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
+  uint8_t* MI = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L + c0 : nullptr;
+  uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
+  const int dir_off = (p.agg ? 1 : 1 + ch.dir) * K * L, inv_off = (p.agg ? 2 : 1 + ch.inv) * K * L;
+  const float rho = p.rho;
+  auto load_e = [&](int s) -> float {  // lane k < K: weight of chain pixel s*K + k
+    const int j = s * K + lane;
+    return (E && lane < K && j < len && j >= 1) ? E[pix0 + j * ch.pstep] : 1.f;
+  };
+  // The 64 candidates are evaluated as two halves of 32 (the second wins ties: highest index), so
+  // that only 32 sums are alive next to the 128 context registers.
+  auto eval_label = [&](const float* hb, const float (&cr)[64], float e, float& best, int& bi) {
+    float ba, bb;
+    int ia, ib;
+    minplus_regrow<32, TRAIN, 64, 0>(hb, cr, e, ba, ia);
+    minplus_regrow<32, TRAIN, 64, 32>(hb + 32, cr, e, bb, ib);
+    best = fminf(ba, bb);
+    bi = bb <= ba ? ib + 32 : ia;
+  };
+
+  for (int s = 0; s < NS; ++s) issue_stage(s);
+  if (lane < K) etile[lane] = load_e(0);
+  float e_next = load_e(1);
+  float uu0 = 0.f, uu1 = 0.f, r0 = 0.f, r1 = 0.f;
+  int po = pix0 * L;             // element offset of the current pixel's label row
+  const int postep = ch.pstep * L;
+  int px = pix0;
+  for (int s = 0; s < nstages; ++s) {
+    const int slot = s % NS;
+    if (!mbar_wait(&full[slot], (s / NS) & 1)) {
+      if (lane == 0) atomicExch(p.status, 131);
+      return;
+    }
+    const int np = len - s * K < K ? len - s * K : K;
+    const float* T = tiles + slot * tile_floats + lc0;
+    const float* et = etile + (s & 1) * K;
+    const bool flip = contiguous && ch.pstep == -1;
+    __syncwarp();
+    for (int k = 0; k < np; ++k) {
+      const float* t = T + (flip ? np - 1 - k : k) * L;
+      float2 v = *reinterpret_cast<const float2*>(t);
+      if (!p.agg)
+        for (int a = 1; a <= D; ++a) {
+          const float2 x = *reinterpret_cast<const float2*>(t + a * K * L);
+          v.x += x.x, v.y += x.y;
+        }
+      const float2 md = *reinterpret_cast<const float2*>(t + dir_off);
+      const float2 mi = *reinterpret_cast<const float2*>(t + inv_off);
+      const float un0 = fmaf(v.x - md.x, rho, -mi.x);
+      const float un1 = fmaf(v.y - md.y, rho, -mi.y);
+      if (s + k > 0) {
+        const float e = et[k];
+        float* hb = hbuf + ((s * K + k) & 1) * 64;
+        if (act) *reinterpret_cast<float2*>(hb + c0) = make_float2(fmaf(rho, r0, uu0), fmaf(rho, r1, uu1));
+        __syncwarp();
+        float b0, b1;
+        int i0, i1;
+        eval_label(hb, cr0, e, b0, i0);
+        eval_label(hb, cr1, e, b1, i1);
+        const float x0 = act ? b0 : kInf, x1 = act ? b1 : kInf;
+        const float m = warp_min(fminf(x0, x1));
+        r0 = b0 - m;
+        r1 = b1 - m;
+        if (act) *reinterpret_cast<float2*>(Mw + po) = make_float2(r0, r1);
+        if (TRAIN) {
+          const unsigned bal0 = __ballot_sync(0xffffffffu, x0 == m);
+          const unsigned bal1 = __ballot_sync(0xffffffffu, x1 == m);
+          const int n0 = 2 * (31 - __clz(bal0));      // -2 when no even label attains the minimum
+          const int n1 = 2 * (31 - __clz(bal1)) + 1;  // -1 when no odd label does
+          if (act) *reinterpret_cast<uchar2*>(MI + po) = make_uchar2((unsigned char)i0, (unsigned char)i1);
+          if (lane == 0) NI[px] = (uint8_t)(n0 > n1 ? n0 : n1);
+        }
+      }
+      uu0 = un0;
+      uu1 = un1;
+      po += postep;
+      px += ch.pstep;
+    }
+    if (lane < K) etile[((s + 1) & 1) * K + lane] = e_next;
+    e_next = load_e(s + 2);
+    __syncwarp();
+    issue_stage(s + NS);  // this warp refills the slot it has just consumed
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Context / edge-weight analysis (rank-1 contexts with L > 32 only).
 // ------------------------------------------------------------------------------------------------
 __global__ void analyze_ctx_kernel(const float* ctx, int L, CtxInfo* info) {
@@ -1286,6 +1450,24 @@ cudaError_t launch_wide_r(const FwdParams& p, int R, cudaStream_t st) {
   return launch_wide<LPT, 16>(p, st);
 }
 
+template <bool TRAIN>
+cudaError_t launch_pair(FwdParams p, cudaStream_t st) {
+  const int total = p.chain_off[p.ndirs];
+  const int A = (p.agg ? 2 : p.D) + 1;
+  int K = 8, NS = 3;
+  auto per_warp = [&](int k, int ns) { return ((ns * A * k * p.L + 128 + 2 * k + 2 * ns + 2) + 3) & ~3; };
+  while (K > 2 && (size_t)kPairWarps * per_warp(K, NS) * sizeof(float) > 100 * 1024) K >>= 1;
+  p.tma_k = K;
+  p.tma_stages = NS;
+  const size_t smem = (size_t)kPairWarps * per_warp(K, NS) * sizeof(float);
+  cudaError_t e = ensure_smem(fwd_pair_kernel<TRAIN>, smem);
+  if (e != cudaSuccess) return e;
+  ProfScope prof(kProfFwdSweep, st);
+  fwd_pair_kernel<TRAIN><<<(total + kPairWarps - 1) / kPairWarps, kPairWarps * 32, smem, st>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
 // Label rows of 16-byte multiples at 16-byte aligned bases: the bulk-copy CTA kernel applies.
 bool cta_tma_eligible(const FwdParams& p) {
   if (p.L & 3) return false;
@@ -1347,6 +1529,8 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
       default: return launch_wide_r<8>(p, p.host_R, st);
     }
   }
+  if (p.L <= 64 && cta_tma_eligible(p) && !pair_kernels_disabled())
+    return train ? launch_pair<true>(p, st) : launch_pair<false>(p, st);
   if (p.ctx_rank == 1) return train ? launch_cta_any<1, true>(p, st) : launch_cta_any<1, false>(p, st);
   if (p.L <= 64) return train ? launch_cta_any<2, true>(p, st) : launch_cta_any<2, false>(p, st);
   return train ? launch_cta_any<0, true>(p, st) : launch_cta_any<0, false>(p, st);

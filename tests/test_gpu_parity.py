@@ -106,6 +106,13 @@ SHAPES = [
     ("ISGMR", 4, 1, 1, 9, 10, 40, 2, "nonmono1d", "pos"),  # non-monotone rank-1
     ("TRWP", 4, 1, 1, 9, 10, 40, 2, "neg1d", "pos"),      # value above the plateau -> dense
     ("ISGMR", 16, 1, 1, 9, 10, 70, 1, "tq1d", "pos"),
+    # two-labels-per-lane kernels (32 < L <= 64, L % 4 == 0): chains longer than the staging ring,
+    # partly filled warps, both gradient schemes, every direction class
+    ("ISGMR", 8, 1, 1, 45, 37, 64, 1, "sym2d", "pos"),
+    ("TRWP", 4, 2, 1, 11, 53, 36, 2, "sym2d", "pos"),
+    ("TRWP", 16, 1, 1, 21, 19, 64, 1, "sym2d", "pos"),
+    ("ISGMR", 16, 1, 1, 18, 35, 52, 2, "sym2d", "none"),
+    ("TRWP", 8, 1, 2, 33, 17, 44, 1, "nonmono1d", "pos"),
 ]
 
 
