@@ -3,6 +3,10 @@
     python oracle/build.py          # oracle/libmp_oracle.so  (C restatement, gcc + OpenMP)
     python oracle/build.py --ref    # additionally oracle/_ref/  (the reference's own C++ CPU
                                     #  extensions, compiled from its sources where they lie)
+    python oracle/build.py --ref-cuda   # additionally oracle/_ref/cuda/ (the reference's own CUDA
+                                    #  extensions, recompiled unmodified for sm_100a: the GPU
+                                    #  implementation this library replaces, for side-by-side
+                                    #  parity and timing on the same device)
 
 The reference sources are only read, never copied; the `--ref` outputs go to `oracle/_ref/`,
 which is git-ignored.  `--ref` needs the reference checkout (path in $MPL_REFERENCE_DIR,
@@ -75,7 +79,50 @@ def build_reference_cpu(force=False):
     return REF_OUT
 
 
+def build_reference_cuda(force=False, names=("TRWP", "ISGMR")):
+    """Compile the reference's TRWP / ISGMR CUDA extensions for sm_100a into oracle/_ref/cuda/.
+
+    Sources used (unmodified, read in place): MPLayers/<name>/<name>.cpp, <name>_forward.cu,
+    <name>_backward.cu, MPLayers/common.cpp, tools/cpp/utils.cpp, tools/cuda/cudaUtils.cu, with
+    the reference's own macros (USE_CUDA, MAX_DISPARITY=256 as in its "stereo" build,
+    MPLayers/setup.py:28,62-63,86) and its nvcc flags except the architecture (sm_35 there).
+    Returns the output directory, or None if the reference is absent.
+    """
+    ref = reference_dir()
+    if not os.path.isdir(os.path.join(ref, "MPLayers")):
+        return None
+    out = os.path.join(REF_OUT, "cuda")
+    os.makedirs(out, exist_ok=True)
+    os.environ["CXX"] = "/usr/bin/g++"
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+    from torch.utils.cpp_extension import load
+    mp = os.path.join(ref, "MPLayers")
+    for name in names:
+        bdir = os.path.join(out, "build_" + name)
+        so = os.path.join(out, name + ".so")
+        if os.path.exists(so) and not force:
+            continue
+        os.makedirs(bdir, exist_ok=True)
+        load(name=name,
+             sources=[os.path.join(mp, name, name + ".cpp"), os.path.join(mp, "common.cpp"),
+                      os.path.join(mp, name, name + "_forward.cu"),
+                      os.path.join(mp, name, name + "_backward.cu"),
+                      os.path.join(ref, "tools", "cpp", "utils.cpp"),
+                      os.path.join(ref, "tools", "cuda", "cudaUtils.cu")],
+             extra_include_paths=[mp, os.path.join(mp, name), os.path.join(ref, "tools", "cpp"),
+                                  os.path.join(ref, "tools", "cuda")],
+             extra_cflags=["-O3", "-fopenmp", "-w", "-DUSE_CUDA", "-DMAX_DISPARITY=256",
+                           "-DTORCH_VERSION_MAJOR=2"],
+             extra_cuda_cflags=["-O3", "--expt-relaxed-constexpr", "-w", "-DUSE_CUDA",
+                                "-DMAX_DISPARITY=256", "-DTORCH_VERSION_MAJOR=2"],
+             extra_ldflags=["-fopenmp"], with_cuda=True, build_directory=bdir, verbose=False)
+        os.replace(os.path.join(bdir, name + ".so"), so)
+    return out
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     if "--ref" in sys.argv:
         print(build_reference_cpu(force="--force" in sys.argv))
+    if "--ref-cuda" in sys.argv:
+        print(build_reference_cuda(force="--force" in sys.argv))
