@@ -16,6 +16,7 @@ sweep for training workloads, forward sweep otherwise) from per-launch CUDA-even
 `cpu_baseline` is the CPU implementation timed on this host on a bounded sample.
 """
 import argparse
+import types
 import json
 import os
 import subprocess
@@ -47,6 +48,10 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="seg_trwp_train", choices=list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard", default="batch", choices=["batch", "directions"],
+                    help="batch (default): every rank owns its own images, weak scaling; directions: ISGMR "
+                         "workloads only, ONE image set on all ranks with each iteration's directions spread "
+                         "over them (strong scaling, one all-reduce per iteration)")
     return ap.parse_args()
 
 
@@ -176,12 +181,20 @@ def run_ours(a):
 
     gen_name, kw, train = WORKLOADS[a.workload]
     kw = dict(kw)
-    if gen_name in ("config4_segmentation", "config5_large", "config1"):
+    by_dir = a.shard == "directions"
+    if gen_name in ("config4_segmentation", "config5_large", "config1") and not by_dir:
         kw["seed"] = rank  # every rank owns its own slice of the global batch
     cfg = getattr(synthetic, gen_name)(**kw)
     batch = cfg["unary"].shape[0]
     args = synthetic.make_args(cfg)
     layer = MPModule(args)
+    if by_dir:
+        if cfg["mode"] != "ISGMR":
+            raise SystemExit("--shard directions needs an ISGMR workload (TRWP directions are sequential)")
+        from mplayers_b200 import direction_sharding
+        dcomm = direction_sharding.TorchDistComm() if world > 1 else types.SimpleNamespace(
+            rank=0, world_size=1, all_reduce=lambda t: t)
+        layer.shard_directions(comm=dcomm)
     ctx_param = torch.nn.Parameter(cfg["label_context"].to(dev), requires_grad=train)
     layer.set_label_context(ctx_param, None, None)
     layer.train(train)
@@ -201,7 +214,7 @@ def run_ours(a):
     from mplayers_b200 import parallel
 
     def reduce_context_grad():
-        if world > 1:  # the only cross-GPU exchange of the batch-sharded layer
+        if world > 1 and not by_dir:  # the only cross-GPU exchange of the batch-sharded layer
             parallel.allreduce_label_context_grad(ctx_param.grad)
 
     def step_layer(u_hwl, e_dhw, g_hwl):
@@ -210,11 +223,16 @@ def run_ours(a):
             u = u_hwl.detach().requires_grad_(True)
             e = e_dhw.detach().requires_grad_(True) if e_dhw is not None else None
             ctx_param.grad = None
-            cost, _ = fn.apply(u, ctx_param, e, args)
+            if by_dir:
+                cost = direction_sharding.isgmr_direction_sharded(u, ctx_param, e, args, comm=dcomm)
+            else:
+                cost, _ = fn.apply(u, ctx_param, e, args)
             cost.backward(g_hwl)
             reduce_context_grad()
             return cost
         with torch.no_grad():
+            if by_dir:
+                return direction_sharding.isgmr_direction_sharded(u_hwl, ctx_param, e_dhw, args, comm=dcomm)
             return fn.apply(u_hwl, ctx_param, e_dhw, args)[0]
 
     def step(u, e):
@@ -308,7 +326,7 @@ def run_ours(a):
         launches = int(lt[0])
 
     if rank == 0:
-        units = units_per_step(cfg, batch) * world
+        units = units_per_step(cfg, batch) * (1 if by_dir else world)
         peak, peak_src = measured_peak()
         dom = "bwd" if train else "fwd"
         t_dom, n_dom = prof[dom]
@@ -333,10 +351,10 @@ def run_ours(a):
             "metric": "TRWP/ISGMR fwd+bwd pixel*label*iter/s" if train else "TRWP/ISGMR fwd pixel*label*iter/s",
             "value": units * a.steps / (ms * 1e-3), "unit": "pixel*label*iter/s",
             "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms / a.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": a.workload, "mode": cfg["mode"], "batch_per_gpu": batch,
-                       "global_batch": batch * world, "height": H, "width": W, "labels": Lb,
+            "higher_is_better": True, "scaling": "strong" if by_dir else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": a.workload, "mode": cfg["mode"], "shard": a.shard, "batch_per_gpu": batch,
+                       "global_batch": batch * (1 if by_dir else world), "height": H, "width": W, "labels": Lb,
                        "directions": cfg["n_dir"], "iterations": cfg["n_iter"],
                        "pass": "fwd+bwd" if train else "fwd",
                        "l2": "working set per step (messages, indices, gradients) exceeds the 126 MB L2"},

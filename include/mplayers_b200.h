@@ -102,6 +102,64 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
                        float* dedge_weights, float* dmsg, float* dmsg_update, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* ---- ISGMR one iteration at a time, over a subset of directions --------------------------------
+ * The D sweeps of an ISGMR iteration only read the previous iteration's messages
+ * (MPLayers/ISGMR/ISGMR_forward.cu:506-622), so they can run on different GPUs; what couples them
+ * is the per-pixel sum over ALL directions that the next iteration's update needs (and, in the
+ * backward, the sum of all scatter fields).  These entry points do one iteration for the
+ * directions [dir_first, dir_first + dir_count) -- whole pairs (d, d^1): dir_first and dir_count
+ * even -- and leave the two sums to the caller, who forms them with mpl_sum_directions and one
+ * all-reduce per iteration (mplayers_b200/parallel.py does it over torch.distributed).  The
+ * monolithic mpl_isgmr_forward / mpl_isgmr_backward are these loops with dir_count = D.  They
+ * replace, per iteration, the loop bodies of ForwardCUDA / BackwardCUDA of the reference
+ * (MPLayers/ISGMR/ISGMR_forward.cu:506-647, MPLayers/ISGMR/ISGMR_backward.cu:353-484). */
+
+/* Forward sweeps of one iteration.
+ *   aggregate   [B,cv,H,W,L]: unary + sum over ALL D directions of the previous messages
+ *               (the unaries themselves in the first iteration, when the messages are zero)
+ *   msg_read    [D,...] previous messages; only the slices d and d^1 of the given directions are read
+ *   msg_write   [D,...] (another buffer); the slices of the given directions are written
+ *   msg_min_index [D,B,cv,H,W,L], msg_norm_index [D,B,cv,H,W]: THIS iteration's part of the saved
+ *               indices (both NULL = inference); only the given directions' slices are written */
+int mpl_isgmr_forward_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_count,
+                                 const float* aggregate, const float* context,
+                                 const float* edge_weights, const float* msg_read, float* msg_write,
+                                 uint8_t* msg_min_index, uint8_t* msg_norm_index, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+
+/* out[B,cv,H,W,L] = base * base_factor + sum over the given directions of fields[d]
+ * (fields [D,B,cv,H,W,L]; base may be NULL: plain sum; any dir_first / dir_count inside 0..D). */
+int mpl_sum_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_count, const float* base,
+                       float base_factor, const float* fields, float* out, void* stream);
+
+/* Backward sweeps of one iteration: replays the given directions' chains from this iteration's
+ * saved indices.
+ *   dmsg_update [D,...] gradient w.r.t. the messages this iteration produced; given slices read
+ *   scatter     [D,...] out: slice d receives the field q_d the sweep scatters to the pixels'
+ *               predecessors (what the reference adds into dunary_update, ISGMR_backward.cu:101-103)
+ *   dedge_weights accumulated into (given slices); may be NULL when edge_weights is NULL
+ *   workspace   of mpl_backward_workspace_bytes(p): label-context partial tables, accumulated over
+ *               calls; pass clear_workspace = 1 on the first call of a backward pass */
+int mpl_isgmr_backward_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_count,
+                                  const float* context, const float* edge_weights,
+                                  float* dmsg_update, const uint8_t* msg_min_index,
+                                  const uint8_t* msg_norm_index, float* scatter,
+                                  float* dedge_weights, void* workspace, size_t workspace_bytes,
+                                  int32_t clear_workspace, void* stream);
+
+/* After the scatter fields of ALL directions have been summed into scatter_total [B,cv,H,W,L]:
+ * dmsg_update[k] = rho*Q - rho*q_k - q_(k^1) for the given directions (now the gradient w.r.t. the
+ * messages the iteration read) and dunary += rho*Q (skipped when dunary is NULL).  Restates
+ * UpdateUnaryKernelBack + SumMsgKernel (MPLayers/ISGMR/ISGMR_backward.cu:39-60,8-16). */
+int mpl_isgmr_backward_combine(const mpl_problem* p, int32_t dir_first, int32_t dir_count,
+                               const float* scatter_total, const float* scatter, float* dmsg_update,
+                               float* dunary, void* stream);
+
+/* Sums the label-context partial tables of `workspace` into dcontext (accumulating), with the
+ * reference's cell addressing (MPLayers/ISGMR/ISGMR_backward.cu:104-115). */
+int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t workspace_bytes,
+                                float* dcontext, void* stream);
+
 /* TRWP backward without any device allocation.  It has no counterpart in the reference.
  *
  * Same computation and arguments as mpl_trwp_backward, minus the workspace: the scratch (partial
@@ -114,7 +172,7 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
  * and no allocating library routine.
  *   - Problems whose mpl_backward_workspace_bytes() exceeds the 8 MiB are rejected with
  *     MPL_ERR_UNSUPPORTED and a message naming both sizes (the segmentation configuration, 2 x
- *     512 x 512 pixels with 21 labels, needs 1.8 MB).
+ *     512 x 512 pixels with 21 labels, needs 7.2 MB).
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress) with that device current; make that first call outside any stream
  *     capture.

@@ -146,8 +146,26 @@ class MPModule(torch.nn.Module):
         self.args.enable_min_a_dir = enable_min_a_dir
         self.args.enable_sgm = args.mpnet_mrf_mode == 'SGM'
         self.args.enable_seg = True if (args.n_classes == 21) else False
+        self.direction_comm = None
         if enable_create_label_context:
             self.create_label_context()
+
+    def shard_directions(self, group=None, comm=None):
+        """ISGMR / SGM only, no counterpart in the reference: from now on every rank of `group`
+        (torch.distributed; default the world) calls this module with the SAME tensors, each
+        iteration's directions are spread over the ranks, and every rank gets the complete result
+        (direction_sharding.py).  `shard_directions(comm=False)` switches it off."""
+        if comm is False:
+            self.direction_comm = None
+            return self
+        if self.args.mpnet_mrf_mode not in {'ISGMR', 'SGM'}:
+            raise RuntimeError("direction sharding needs independent directions: ISGMR / SGM only "
+                               "(TRWP updates them one after the other)")
+        if comm is None:
+            from .direction_sharding import TorchDistComm
+            comm = TorchDistComm(group)
+        self.direction_comm = comm
+        return self
 
     def get_label_context(self):
         return self.label_context, self.label_context_loc, self.label_context_diag_loc
@@ -188,7 +206,12 @@ class MPModule(torch.nn.Module):
         if edge_weights is not None:
             assert unary.size()[-3:-1] == edge_weights.size()[-2:]
         self.args.training = self.training
-        if self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'}:
+        if self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'} and self.direction_comm is not None:
+            from .direction_sharding import isgmr_direction_sharded
+            cost_final = isgmr_direction_sharded(unary, label_context, edge_weights, self.args,
+                                                 comm=self.direction_comm)
+            cost_all = _empty_u8(unary.device)
+        elif self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'}:
             cost_final, cost_all = ISGMRFunction.apply(unary, label_context, edge_weights, self.args)
         elif self.args.mpnet_mrf_mode == 'TRWP':
             cost_final, cost_all = TRWPFunction.apply(unary, label_context, edge_weights, self.args)

@@ -47,6 +47,17 @@ def lib():
         L.mpl_isgmr_forward.argtypes = [pp] + [vp] * 10 + [sz, vp]
         L.mpl_isgmr_backward.restype = ctypes.c_int
         L.mpl_isgmr_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
+        i32 = ctypes.c_int32
+        L.mpl_isgmr_forward_directions.restype = ctypes.c_int
+        L.mpl_isgmr_forward_directions.argtypes = [pp, i32, i32] + [vp] * 8 + [sz, vp]
+        L.mpl_sum_directions.restype = ctypes.c_int
+        L.mpl_sum_directions.argtypes = [pp, i32, i32, vp, ctypes.c_float, vp, vp, vp]
+        L.mpl_isgmr_backward_directions.restype = ctypes.c_int
+        L.mpl_isgmr_backward_directions.argtypes = [pp, i32, i32] + [vp] * 8 + [sz, i32, vp]
+        L.mpl_isgmr_backward_combine.restype = ctypes.c_int
+        L.mpl_isgmr_backward_combine.argtypes = [pp, i32, i32] + [vp] * 5
+        L.mpl_backward_context_finish.restype = ctypes.c_int
+        L.mpl_backward_context_finish.argtypes = [pp, vp, sz, vp, vp]
         L.mpl_trwp_backward_static.restype = ctypes.c_int
         L.mpl_trwp_backward_static.argtypes = [pp] + [vp] * 10
         L.mpl_static_scratch_bytes.restype = sz

@@ -186,6 +186,29 @@ void set_dirs(mpl::FwdParams& fp, int dir0, int ndirs) {
     fp.chain_off[i + 1] = fp.chain_off[i] + mpl::make_geom(dir0 + i, fp.H, fp.W).n_chains * fp.nimg;
 }
 
+// Fills the sweep parameters, clears the status word and runs the context / edge-weight analysis
+// (and, for inference with a rank-1 context, reads its verdict back: one small synchronising copy).
+int prepare_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, const float* unary,
+                    const float* context, const float* edge_weights, void* workspace, bool train,
+                    cudaStream_t st) {
+  const int D = p->n_dir, L = p->n_disp;
+  fill_forward(fp, p, d, unary, context, edge_weights, workspace);
+  MPL_CUDA(cudaMemsetAsync(fp.status, 0, sizeof(int), st));
+  MPL_CUDA(mpl::launch_analyze(context, L, p->context_rank, edge_weights, d.npix * D,
+                               static_cast<mpl::CtxInfo*>(workspace), st));
+  if (p->context_rank == 1 && L > 32 && !train) {
+    // Inference with a rank-1 context: the choice of the wide windowed kernel is made on the host,
+    // which costs one small device-to-host copy (the call synchronises with its stream here).
+    mpl::CtxInfo hi;
+    MPL_CUDA(cudaMemcpyAsync(&hi, workspace, sizeof(hi), cudaMemcpyDeviceToHost, st));
+    MPL_CUDA(cudaStreamSynchronize(st));
+    const float ew_min = hi.ew_min_bits >= 0 ? 1.f : -1.f;  // order bits: negative <=> negative float
+    fp.host_windowed = hi.windowed && (edge_weights == nullptr || ew_min >= 0.f);
+    fp.host_R = hi.R;
+  }
+  return MPL_OK;
+}
+
 int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const float* context,
                    const float* edge_weights, float* msg, float* msg_update, float* cost_final,
                    uint8_t* msg_min_index, uint8_t* msg_norm_index, uint8_t* label_all,
@@ -205,20 +228,7 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
   const int D = p->n_dir, L = p->n_disp;
 
   mpl::FwdParams fp{};
-  fill_forward(fp, p, d, unary, context, edge_weights, workspace);
-  MPL_CUDA(cudaMemsetAsync(fp.status, 0, sizeof(int), st));
-  MPL_CUDA(mpl::launch_analyze(context, L, p->context_rank, edge_weights, d.npix * D,
-                               static_cast<mpl::CtxInfo*>(workspace), st));
-  if (p->context_rank == 1 && L > 32 && !train) {
-    // Inference with a rank-1 context: the choice of the wide windowed kernel is made on the host,
-    // which costs one small device-to-host copy (the call synchronises with its stream here).
-    mpl::CtxInfo hi;
-    MPL_CUDA(cudaMemcpyAsync(&hi, workspace, sizeof(hi), cudaMemcpyDeviceToHost, st));
-    MPL_CUDA(cudaStreamSynchronize(st));
-    const float ew_min = hi.ew_min_bits >= 0 ? 1.f : -1.f;  // order bits: negative <=> negative float
-    fp.host_windowed = hi.windowed && (edge_weights == nullptr || ew_min >= 0.f);
-    fp.host_R = hi.R;
-  }
+  if (int rc = prepare_forward(fp, p, d, unary, context, edge_weights, workspace, train, st)) return rc;
 
   const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
   // ISGMR alternates between the two message buffers so that the last iteration writes `msg`.
@@ -269,6 +279,27 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
   return MPL_OK;
 }
 
+void fill_backward(mpl::BwdParams& bp, const mpl_problem* p, const Dims& d, const float* context,
+                   const float* edge_weights, float* dunary, float* part, int n_slots, int cp, int* status) {
+  bp.ctx = context;
+  bp.ew = edge_weights;
+  bp.dunary = dunary;
+  bp.dctx_part = part;
+  bp.n_slots = n_slots;
+  bp.H = p->height;
+  bp.W = p->width;
+  bp.L = p->n_disp;
+  bp.D = p->n_dir;
+  bp.nimg = (int)d.nimg;
+  bp.slice = d.slice;
+  bp.pslice = d.npix;
+  bp.rho = p->rho;
+  bp.ctx_rank = p->context_rank;
+  bp.keep_diag = p->keep_diag;
+  bp.cp_scheme = cp;
+  bp.status = status;
+}
+
 int backward_common(bool isgmr, const mpl_problem* p, const float* context, const float* edge_weights,
                     const float* dcost_final, const uint8_t* msg_min_index,
                     const uint8_t* msg_norm_index, float* dunary, float* dcontext,
@@ -306,23 +337,7 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
 
   mpl::BwdParams bp{};
-  bp.ctx = context;
-  bp.ew = edge_weights;
-  bp.dunary = dunary;
-  bp.dctx_part = part;
-  bp.n_slots = n_slots;
-  bp.H = p->height;
-  bp.W = p->width;
-  bp.L = L;
-  bp.D = D;
-  bp.nimg = (int)d.nimg;
-  bp.slice = d.slice;
-  bp.pslice = d.npix;
-  bp.rho = p->rho;
-  bp.ctx_rank = p->context_rank;
-  bp.keep_diag = p->keep_diag;
-  bp.cp_scheme = cp;
-  bp.status = status;
+  fill_backward(bp, p, d, context, edge_weights, dunary, part, n_slots, cp, status);
   for (int it = p->n_iter - 1; it >= 0; --it) {
     bp.min_idx = msg_min_index + (long long)it * D * d.slice;
     bp.norm_idx = msg_norm_index + (long long)it * D * d.npix;
@@ -402,6 +417,125 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
   return backward_common(true, p, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,
                          dunary, dcontext, dedge_weights, dmsg, dmsg_update, workspace,
                          workspace_bytes, stream);
+}
+
+// ---- ISGMR one iteration at a time over a subset of directions (direction sharding) -------------
+namespace {
+int check_dir_range(const mpl_problem* p, int32_t dir_first, int32_t dir_count) {
+  if (dir_first < 0 || dir_count < 0 || (dir_first & 1) || (dir_count & 1) || dir_first + dir_count > p->n_dir)
+    return fail(MPL_ERR_INVALID,
+                "directions [%d, %d) of %d: the range must start and end on a pair (d, d^1) boundary",
+                dir_first, dir_first + dir_count, p->n_dir);
+  return MPL_OK;
+}
+}  // namespace
+
+int mpl_isgmr_forward_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_count,
+                                 const float* aggregate, const float* context, const float* edge_weights,
+                                 const float* msg_read, float* msg_write, uint8_t* msg_min_index,
+                                 uint8_t* msg_norm_index, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (int rc = check_chain_count(p, d)) return rc;
+  if (int rc = check_dir_range(p, dir_first, dir_count)) return rc;
+  if (!aggregate || !context || !msg_read || !msg_write) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if (msg_read == msg_write) return fail(MPL_ERR_INVALID, "msg_read and msg_write must be different buffers");
+  if ((msg_min_index == nullptr) != (msg_norm_index == nullptr))
+    return fail(MPL_ERR_INVALID, "msg_min_index and msg_norm_index must both be given or both be NULL");
+  if (!workspace || workspace_bytes < mpl_forward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_forward_workspace_bytes(p));
+  if (dir_count == 0) return MPL_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool train = msg_min_index != nullptr;
+  mpl::FwdParams fp{};
+  if (int rc = prepare_forward(fp, p, d, aggregate, context, edge_weights, workspace, train, st)) return rc;
+  fp.agg = 1;
+  fp.min_idx = msg_min_index;
+  fp.norm_idx = msg_norm_index;
+  fp.msg_read = msg_read;
+  fp.msg_write = msg_write;
+  set_dirs(fp, dir_first, dir_count);
+  MPL_CUDA(mpl::launch_forward_sweep(fp, train, st));
+  return MPL_OK;
+}
+
+int mpl_sum_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_count, const float* base,
+                       float base_factor, const float* fields, float* out, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (dir_first < 0 || dir_count < 0 || dir_first + dir_count > p->n_dir)
+    return fail(MPL_ERR_INVALID, "directions [%d, %d) of %d", dir_first, dir_first + dir_count, p->n_dir);
+  if (!out || (dir_count > 0 && !fields)) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  MPL_CUDA(mpl::launch_sum_fields(base, base_factor, fields ? fields + (long long)dir_first * d.slice : nullptr,
+                                  dir_count, d.slice, out, static_cast<cudaStream_t>(stream)));
+  return MPL_OK;
+}
+
+int mpl_isgmr_backward_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_count,
+                                  const float* context, const float* edge_weights, float* dmsg_update,
+                                  const uint8_t* msg_min_index, const uint8_t* msg_norm_index,
+                                  float* scatter, float* dedge_weights, void* workspace,
+                                  size_t workspace_bytes, int32_t clear_workspace, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (int rc = check_chain_count(p, d)) return rc;
+  if (int rc = check_dir_range(p, dir_first, dir_count)) return rc;
+  if (!context || !dmsg_update || !msg_min_index || !msg_norm_index || !scatter)
+    return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if (edge_weights && !dedge_weights)
+    return fail(MPL_ERR_INVALID, "dedge_weights is NULL although edge_weights is given");
+  if (!workspace || workspace_bytes < mpl_backward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_backward_workspace_bytes(p));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
+  float* part = static_cast<float*>(workspace);
+  int* status = reinterpret_cast<int*>(part + (size_t)n_slots * d.ctx_elems);
+  if (clear_workspace) {
+    MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
+    MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  }
+  if (dir_count == 0) return MPL_OK;
+  mpl::BwdParams bp{};
+  fill_backward(bp, p, d, context, edge_weights, nullptr, part, n_slots, 2, status);
+  bp.min_idx = msg_min_index;
+  bp.norm_idx = msg_norm_index;
+  bp.dew = (edge_weights && dedge_weights) ? dedge_weights : nullptr;
+  bp.dir = dir_first;
+  bp.ndirs = dir_count;
+  bp.dm_read = dmsg_update;
+  bp.dm_acc = scatter;
+  MPL_CUDA(mpl::launch_backward_sweep(bp, st));
+  return MPL_OK;
+}
+
+int mpl_isgmr_backward_combine(const mpl_problem* p, int32_t dir_first, int32_t dir_count,
+                               const float* scatter_total, const float* scatter, float* dmsg_update,
+                               float* dunary, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (int rc = check_dir_range(p, dir_first, dir_count)) return rc;
+  if (!scatter_total || (dir_count > 0 && (!scatter || !dmsg_update)))
+    return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  MPL_CUDA(mpl::launch_isgmr_combine_total(scatter_total, scatter, dmsg_update, dunary, d.slice, dir_first,
+                                           dir_count, p->rho, static_cast<cudaStream_t>(stream)));
+  return MPL_OK;
+}
+
+int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t workspace_bytes,
+                                float* dcontext, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (!dcontext) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if (!workspace || workspace_bytes < mpl_backward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_backward_workspace_bytes(p));
+  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
+  MPL_CUDA(mpl::launch_dctx_reduce(static_cast<float*>(workspace), n_slots, p->n_disp, p->context_rank,
+                                   p->keep_diag, dcontext, static_cast<cudaStream_t>(stream)));
+  return MPL_OK;
 }
 
 int mpl_forward_status(const void* workspace, int32_t* status) {

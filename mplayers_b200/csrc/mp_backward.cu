@@ -1056,6 +1056,30 @@ __global__ void isgmr_combine_kernel(const float* __restrict__ q, float* __restr
   }
 }
 
+// The same with Q given (summed over ALL directions, possibly on other GPUs) and only the
+// directions [dir0, dir0 + ndirs) held here; dunary may be null (then only the messages' part).
+__global__ void isgmr_combine_total_kernel(const float* __restrict__ Qt, const float* __restrict__ q,
+                                           float* __restrict__ dm, float* __restrict__ dunary, long long n,
+                                           int dir0, int ndirs, float rho) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float rQ = rho * Qt[i];
+    if (dunary) dunary[i] += rQ;
+    for (int k = dir0; k < dir0 + ndirs; ++k) dm[k * n + i] = (rQ - rho * q[k * n + i]) - q[(k ^ 1) * n + i];
+  }
+}
+
+// out = base * factor + sum of nf consecutive fields (base may be null: plain sum), ascending order
+__global__ void sum_fields_kernel(const float* __restrict__ base, float factor, const float* __restrict__ f,
+                                  int nf, long long n, float* __restrict__ out) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float v = base ? base[i] * factor : 0.f;
+    for (int k = 0; k < nf; ++k) v += f[k * n + i];
+    out[i] = v;
+  }
+}
+
 // Sums the per-slot partial tables in slot order (two fixed-order levels) and folds them into the
 // caller's dcontext with the reference's addressing (MPLayers/TRWP/TRWP_backward.cu:102-112):
 // rank 2 -> cell [min(c,f)][max(c,f)], rank 1 -> cell |c-f|.
@@ -1150,6 +1174,26 @@ cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long 
   if (blocks > 148 * 16) blocks = 148 * 16;
   ProfScope prof(kProfElementwise, st);
   isgmr_combine_kernel<<<(int)blocks, 256, 0, st>>>(q, dm, dunary, n, D, rho);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, float* dm, float* dunary, long long n,
+                                       int dir0, int ndirs, float rho, cudaStream_t st) {
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ProfScope prof(kProfElementwise, st);
+  isgmr_combine_total_kernel<<<(int)blocks, 256, 0, st>>>(q_total, q, dm, dunary, n, dir0, ndirs, rho);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n, float* out,
+                              cudaStream_t st) {
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ProfScope prof(kProfElementwise, st);
+  sum_fields_kernel<<<(int)blocks, 256, 0, st>>>(base, factor, fields, nf, n, out);
   count_launch();
   return cudaGetLastError();
 }

@@ -266,6 +266,10 @@ cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, 
 cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,
                                  float factor, int cp_scheme, cudaStream_t st);
 cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
+cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, float* dm, float* dunary, long long n,
+                                       int dir0, int ndirs, float rho, cudaStream_t st);
+cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n, float* out,
+                              cudaStream_t st);
 cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long long n, int D, float rho,
                                  cudaStream_t st);
 cudaError_t launch_dctx_reduce(float* part, int n_slots, int L, int rank, int keep_diag,

@@ -1,0 +1,204 @@
+"""ISGMR on ONE image spread over several GPUs by direction.
+
+Within an ISGMR iteration every direction reads only the previous iteration's messages
+(MPLayers/ISGMR/ISGMR_forward.cu:514-619), so the D sweeps are independent; what couples them is
+the per-pixel sum of all directions' messages that the next iteration's update
+UU_d = (U + sum_k M_k - M_d) * rho - M_inv(d) needs (ISGMR_forward.cu:101-121), and in the
+backward pass the sum of all directions' scatter fields.  Rank r owns whole direction pairs
+(d, d^1) -- so the partner message of every owned direction is local -- runs their sweeps through
+the iteration-level C ABI (mpl_isgmr_forward_directions & co. of include/mplayers_b200.h), and the
+ranks exchange exactly one all-reduce (sum) of a [B,cv,H,W,L] field per iteration and pass, plus
+one small all-reduce of the label-context gradient and one of the edge-weight gradients at the
+end.  Every rank holds the whole image and ends with the whole result.
+
+The sum over directions is formed as (local partial sums) + all-reduce, not in the single-GPU
+order, so results agree with the single-GPU layer to rounding (costs ~1e-6 relative; a saved
+index can differ where two candidates are within rounding of each other), not bit for bit.
+
+The batch-sharded mode of `parallel.py` is the scaling mode for training; this one shortens the
+latency of one large image (batch 1), which batch sharding cannot split.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+def direction_shards(n_dir, world_size):
+    """[(first_direction, direction_count)] per rank: contiguous runs of whole pairs (d, d^1); the
+    first `pairs % world_size` ranks own one pair more; ranks beyond the pair count own nothing
+    (they still take part in the collectives)."""
+    if n_dir < 2 or n_dir % 2:
+        raise ValueError("n_dir must be even and >= 2, got %d" % n_dir)
+    if world_size < 1:
+        raise ValueError("world_size must be >= 1")
+    pairs = n_dir // 2
+    base, rem = divmod(pairs, world_size)
+    out, lo = [], 0
+    for r in range(world_size):
+        n = base + (1 if r < rem else 0)
+        out.append((2 * lo, 2 * n))
+        lo += n
+    return out
+
+
+class TorchDistComm:
+    """The collectives of this module over torch.distributed (NCCL on GPUs)."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+
+    def all_reduce(self, t):
+        if self.world_size > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+
+class CudaBackend:
+    """The iteration-level entry points of the C ABI on torch CUDA tensors (current stream)."""
+
+    @staticmethod
+    def problem(unary, n_iter, n_dir, context, rho, enable_sgm, keep_diag=0):
+        b, cv, h, w, l = unary.shape
+        return _lib.Problem(int(n_iter), int(n_dir), b, cv, h, w, l, _lib.context_rank(context, l), 0,
+                            int(enable_sgm), int(keep_diag), float(rho))
+
+    @staticmethod
+    def _ws(prob, dev, backward):
+        f = _lib.lib().mpl_backward_workspace_bytes if backward else _lib.lib().mpl_forward_workspace_bytes
+        n = f(ctypes.byref(prob))
+        return _lib.workspace(n, dev), n
+
+    def forward_directions(self, prob, d0, dc, aggregate, context, ew, msg_read, msg_write, min_idx, norm_idx):
+        dev = aggregate.device
+        with torch.cuda.device(dev):
+            ws, n = self._ws(prob, dev, False)
+            _lib.check(_lib.lib().mpl_isgmr_forward_directions(
+                ctypes.byref(prob), d0, dc, _lib.ptr(aggregate), _lib.ptr(context), _lib.ptr(ew),
+                _lib.ptr(msg_read), _lib.ptr(msg_write), _lib.ptr(min_idx), _lib.ptr(norm_idx),
+                _lib.ptr(ws), n, _lib.stream_ptr(dev)))
+            _lib.check_status(ws)
+
+    def sum_directions(self, prob, d0, dc, base, factor, fields, out):
+        dev = out.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().mpl_sum_directions(
+                ctypes.byref(prob), d0, dc, _lib.ptr(base), float(factor), _lib.ptr(fields), _lib.ptr(out),
+                _lib.stream_ptr(dev)))
+        return out
+
+    def backward_workspace(self, prob, dev):
+        return self._ws(prob, dev, True)[0]
+
+    def backward_directions(self, prob, d0, dc, context, ew, dmsg_update, min_idx, norm_idx, scatter, dew, ws,
+                            clear):
+        dev = scatter.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().mpl_isgmr_backward_directions(
+                ctypes.byref(prob), d0, dc, _lib.ptr(context), _lib.ptr(ew), _lib.ptr(dmsg_update),
+                _lib.ptr(min_idx), _lib.ptr(norm_idx), _lib.ptr(scatter), _lib.ptr(dew), _lib.ptr(ws),
+                ws.numel(), int(clear), _lib.stream_ptr(dev)))
+
+    def combine(self, prob, d0, dc, scatter_total, scatter, dmsg_update, dunary):
+        dev = scatter_total.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().mpl_isgmr_backward_combine(
+                ctypes.byref(prob), d0, dc, _lib.ptr(scatter_total), _lib.ptr(scatter), _lib.ptr(dmsg_update),
+                _lib.ptr(dunary), _lib.stream_ptr(dev)))
+
+    def context_finish(self, prob, ws, dcontext):
+        dev = dcontext.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().mpl_backward_context_finish(
+                ctypes.byref(prob), _lib.ptr(ws), ws.numel(), _lib.ptr(dcontext), _lib.stream_ptr(dev)))
+
+
+class DirectionShardedISGMRFunction(torch.autograd.Function):
+    """ISGMRFunction (pytorch/MP_module.py:89-161) with the directions of each iteration spread over
+    the ranks of `comm`.  Same tensors in and out on EVERY rank (unary [B,cv,H,W,L], label_context
+    [L] or [L,L], edge_weights [D,B,cv,H,W] or None); every rank returns the complete cost_final
+    and receives the complete gradients.  Saving per-iteration labels and `enable_min_a_dir` are
+    not offered in this mode."""
+
+    @staticmethod
+    def forward(ctx, unary, label_context, edge_weights, args, comm, backend):
+        if getattr(args, "enable_min_a_dir", False) or getattr(args, "enable_saving_label", False):
+            raise RuntimeError("direction sharding offers neither enable_min_a_dir nor per-iteration labels")
+        b, cv, h, w, l = unary.shape
+        rho, n_iter, n_dir, training = args.rho, int(args.mpnet_max_iter), int(args.mpnet_n_dirs), args.training
+        sgm = int(bool(getattr(args, "enable_sgm", False)))
+        factor = float(n_dir) if sgm else 1.0
+        unary = unary.contiguous()
+        label_context = label_context.contiguous()
+        ew = edge_weights.contiguous() if edge_weights is not None else None
+        d0, dc = direction_shards(n_dir, comm.world_size)[comm.rank]
+        prob = backend.problem(unary, n_iter, n_dir, label_context, rho, sgm)
+        rd = unary.new_zeros(n_dir, b, cv, h, w, l)
+        wr = unary.new_zeros(n_dir, b, cv, h, w, l)
+        if training:
+            min_idx = torch.zeros(n_iter, n_dir, b, cv, h, w, l, dtype=torch.uint8, device=unary.device)
+            norm_idx = torch.zeros(n_iter, n_dir, b, cv, h, w, dtype=torch.uint8, device=unary.device)
+        else:
+            min_idx = norm_idx = None
+        aggregate = unary
+        total = torch.zeros_like(unary)   # sum over ALL directions of the newest messages
+        buf = torch.empty_like(unary)
+        for it in range(n_iter):
+            backend.forward_directions(prob, d0, dc, aggregate, label_context, ew, rd, wr,
+                                       min_idx[it] if training else None, norm_idx[it] if training else None)
+            backend.sum_directions(prob, d0, dc, None, 0.0, wr, total)
+            comm.all_reduce(total)
+            torch.add(unary, total, out=buf)
+            aggregate = buf
+            rd, wr = wr, rd
+        cost_final = unary * factor + total if factor != 1.0 else (unary + total)
+        ctx.intermediate_results = (sgm, rho, min_idx, norm_idx, label_context, ew, comm, backend, d0, dc, n_dir)
+        return cost_final
+
+    @staticmethod
+    def backward(ctx, dcost_final):
+        sgm, rho, min_idx, norm_idx, label_context, ew, comm, backend, d0, dc, n_dir = ctx.intermediate_results
+        del ctx.intermediate_results
+        if min_idx is None:
+            raise RuntimeError("backward needs the indices saved by a training-mode forward "
+                               "(args.training was False)")
+        g = dcost_final.contiguous()
+        n_iter = min_idx.size(0)
+        b, cv, h, w, l = g.shape
+        factor = float(n_dir) if sgm else 1.0
+        prob = backend.problem(g, n_iter, n_dir, label_context, rho, sgm)
+        dunary = g * factor
+        x = g.new_zeros(n_dir, b, cv, h, w, l)     # gradient w.r.t. the messages an iteration produced
+        if dc:
+            x[d0:d0 + dc] = g
+        scatter = g.new_zeros(n_dir, b, cv, h, w, l)
+        q_total = torch.empty_like(g)
+        dew = torch.zeros_like(ew) if ew is not None else None
+        ws = backend.backward_workspace(prob, g.device)
+        for k, it in enumerate(range(n_iter - 1, -1, -1)):
+            backend.backward_directions(prob, d0, dc, label_context, ew, x, min_idx[it], norm_idx[it], scatter, dew,
+                                        ws, clear=(k == 0))
+            backend.sum_directions(prob, d0, dc, None, 0.0, scatter, q_total)
+            comm.all_reduce(q_total)
+            backend.combine(prob, d0, dc, q_total, scatter, x, dunary)
+        dcontext = torch.zeros_like(label_context)
+        if n_iter == 0:
+            backend.backward_directions(prob, d0, 0, label_context, ew, x, min_idx, norm_idx, scatter, dew, ws,
+                                        clear=True)
+        backend.context_finish(prob, ws, dcontext)
+        comm.all_reduce(dcontext)
+        if dew is not None:
+            comm.all_reduce(dew)   # every slice is non-zero on exactly one rank
+        return dunary, dcontext, dew, None, None, None
+
+
+def isgmr_direction_sharded(unary, label_context, edge_weights, args, group=None, comm=None, backend=None):
+    """Runs ISGMR (or single-iteration SGM) on `unary` with each iteration's directions spread over
+    the ranks of `group` (default: the world).  Call it on every rank with the same tensors."""
+    comm = comm if comm is not None else TorchDistComm(group)
+    backend = backend if backend is not None else CudaBackend()
+    return DirectionShardedISGMRFunction.apply(unary, label_context, edge_weights, args, comm, backend)

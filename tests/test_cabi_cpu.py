@@ -68,8 +68,9 @@ def test_workspace_sizes():
     lib = _lib.lib()
     p = _prob(batch=2, height=512, width=512)
     assert lib.mpl_forward_workspace_bytes(ctypes.byref(p)) >= 16
-    # one partial 21x21 table per chain of the direction with most chains (2 images x 512 rows)
-    assert lib.mpl_backward_workspace_bytes(ctypes.byref(p)) == 1024 * 441 * 4 + 64
+    # one partial 21x21 table per chain of all four directions (4 x 2 images x 512 rows; an ISGMR
+    # launch covers every direction at once) + the status word
+    assert lib.mpl_backward_workspace_bytes(ctypes.byref(p)) == 4096 * 441 * 4 + 64
 
 
 @pytest.mark.parametrize("hw", [(1, 1), (1, 7), (5, 1), (2, 3), (6, 7), (13, 4)])
