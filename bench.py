@@ -136,13 +136,17 @@ def algorithmic_bytes(cfg, batch, kind):
 def dominant_kernel(cfg, kind):
     """Name of the sweep kernel the workload spends its time in (see mplayers_b200/csrc)."""
     L = cfg["unary"].shape[2]
+    pair = 32 < L <= 64 and L % 4 == 0
     if kind == "bwd":
-        return "bwd_tma_kernel" if (L <= 32 and cfg["mode"] == "TRWP") else \
-            ("bwd_warp_kernel" if L <= 32 else "bwd_cta_kernel")
+        if L <= 32:
+            return "bwd_tma_kernel" if cfg["mode"] == "TRWP" else "bwd_warp_kernel"
+        return "bwd_pair_kernel" if pair else "bwd_cta_kernel"
     if L <= 32:
         return "fwd_tma_kernel"
     if not cfg["training"] and cfg["label_context"].dim() == 1 and L % 4 == 0:
         return "fwd_wide_kernel"
+    if pair:
+        return "fwd_pair_kernel"
     return "fwd_cta_tma_kernel" if L % 4 == 0 else "fwd_cta_kernel"
 
 
@@ -152,6 +156,13 @@ NCU_TRAFFIC = {
     ("seg_trwp_train", "bwd"): 149.3e6 + 80.9e6,
     ("seg_trwp_train", "fwd"): 222.4e6 + 33.9e6,
     ("stereo_trwp_infer", "fwd"): 1788.5e6 + 338.6e6,
+    # captured on the 384 x 384 copy of the workload (a full-size launch is too large to replay under
+    # the profiler); traffic is proportional to the pixel count, so the full-size figures are those
+    # times (1024 / 384)^2
+    ("large_isgmr_train_384", "fwd"): 748.7e6 + 354.4e6,
+    ("large_isgmr_train_384", "bwd"): 426.3e6 + 299.6e6,
+    ("large_isgmr_train", "fwd"): (748.7e6 + 354.4e6) * (1024 / 384) ** 2,
+    ("large_isgmr_train", "bwd"): (426.3e6 + 299.6e6) * (1024 / 384) ** 2,
 }
 
 
@@ -328,7 +339,8 @@ def run_ours(a):
     if rank == 0:
         units = units_per_step(cfg, batch) * (1 if by_dir else world)
         peak, peak_src = measured_peak()
-        dom = "bwd" if train else "fwd"
+        # the sweep kind the step spends most of its time in
+        dom = "bwd" if (train and prof["bwd"][0] >= prof["fwd"][0]) else "fwd"
         t_dom, n_dom = prof[dom]
         roof = None
         if n_dom:
