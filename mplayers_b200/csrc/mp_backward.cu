@@ -57,12 +57,12 @@ __device__ __forceinline__ float eq_flag(float a, float b) {
 }
 
 // q[f] = sum over labels c whose saved argmin is f of t[c], for f = `me`; fixed summation order
-// (three interleaved partial sums).  tb / ib: the t values and argmin indices (stored as floats)
+// (interleaved partial sums).  tb / ib: the t values and argmin indices (stored as floats)
 // of all labels of this pixel in shared memory.  One compare-to-flag plus one fused multiply-add
 // per label: compare/select instructions issue at half the rate of multiply-adds.
 template <int LT>
 __device__ __forceinline__ float gather_q(const float* tb, const float* ib, int L, float me) {
-  float q0 = 0.f, q1 = 0.f, q2 = 0.f;
+  float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
   if constexpr (LT > 0) {
     constexpr int NV = (LT + 3) / 4;
     float tv[NV * 4], iv[NV * 4];
@@ -73,13 +73,16 @@ __device__ __forceinline__ float gather_q(const float* tb, const float* ib, int 
       tv[4 * v] = a.x, tv[4 * v + 1] = a.y, tv[4 * v + 2] = a.z, tv[4 * v + 3] = a.w;
       iv[4 * v] = b.x, iv[4 * v + 1] = b.y, iv[4 * v + 2] = b.z, iv[4 * v + 3] = b.w;
     }
+    // two labels per packed fma, two alternating accumulator pairs
 #pragma unroll
-    for (int c = 0; c < LT; ++c) {
-      const float fl = eq_flag(iv[c], me);
-      if (c % 3 == 0) q0 = fmaf(fl, tv[c], q0);
-      if (c % 3 == 1) q1 = fmaf(fl, tv[c], q1);
-      if (c % 3 == 2) q2 = fmaf(fl, tv[c], q2);
+    for (int c = 0; c + 1 < LT; c += 2) {
+      if (c & 2) {
+        ffma2(q2, q3, eq_flag(iv[c], me), eq_flag(iv[c + 1], me), tv[c], tv[c + 1], q2, q3);
+      } else {
+        ffma2(q0, q1, eq_flag(iv[c], me), eq_flag(iv[c + 1], me), tv[c], tv[c + 1], q0, q1);
+      }
     }
+    if (LT & 1) q0 = fmaf(eq_flag(iv[LT - 1], me), tv[LT - 1], q0);
   } else {
     int c = 0;
     for (; c + 2 < L; c += 3) {
@@ -89,7 +92,7 @@ __device__ __forceinline__ float gather_q(const float* tb, const float* ib, int 
     }
     for (; c < L; ++c) q0 = fmaf(eq_flag(ib[c], me), tb[c], q0);
   }
-  return (q0 + q1) + q2;
+  return (q0 + q1) + (q2 + q3);
 }
 
 // Sum of n consecutive floats (n = LT when known at compile time).
@@ -601,19 +604,15 @@ __host__ __device__ inline int bwd_pair_floats(int L, int rank, int sch) {
 template <bool FULL>
 __device__ __forceinline__ void gather_q2(const float* tb, const float* ib, int L, float me0, float& q0,
                                           float& q1) {
-  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
   const float me1 = me0 + 1.f;
-  auto body = [&](int v) {
+  auto body = [&](int v) {  // four labels c: packed fmas over (c, c+1), accumulators a* for me0, b* for me1
     const float4 t = reinterpret_cast<const float4*>(tb)[v];
     const float4 i = reinterpret_cast<const float4*>(ib)[v];
-    a0 = fmaf(eq_flag(i.x, me0), t.x, a0);
-    b0 = fmaf(eq_flag(i.x, me1), t.x, b0);
-    a1 = fmaf(eq_flag(i.y, me0), t.y, a1);
-    b1 = fmaf(eq_flag(i.y, me1), t.y, b1);
-    a0 = fmaf(eq_flag(i.z, me0), t.z, a0);
-    b0 = fmaf(eq_flag(i.z, me1), t.z, b0);
-    a1 = fmaf(eq_flag(i.w, me0), t.w, a1);
-    b1 = fmaf(eq_flag(i.w, me1), t.w, b1);
+    ffma2(a0, a1, eq_flag(i.x, me0), eq_flag(i.y, me0), t.x, t.y, a0, a1);
+    ffma2(b0, b1, eq_flag(i.x, me1), eq_flag(i.y, me1), t.x, t.y, b0, b1);
+    ffma2(a2, a3, eq_flag(i.z, me0), eq_flag(i.w, me0), t.z, t.w, a2, a3);
+    ffma2(b2, b3, eq_flag(i.z, me1), eq_flag(i.w, me1), t.z, t.w, b2, b3);
   };
   if constexpr (FULL) {
 #pragma unroll
@@ -623,8 +622,8 @@ __device__ __forceinline__ void gather_q2(const float* tb, const float* ib, int 
 #pragma unroll 3
     for (int v = 0; v < nv; ++v) body(v);
   }
-  q0 = a0 + a1;
-  q1 = b0 + b1;
+  q0 = (a0 + a1) + (a2 + a3);
+  q1 = (b0 + b1) + (b2 + b3);
 }
 
 // Nothing in the step loop loads from global memory into registers except the per-block scalars:

@@ -147,6 +147,21 @@ __device__ __forceinline__ float ctx_value(const float* ctx, int rank, int L, in
   return __ldg(ctx + (k < 0 ? -k : k));
 }
 
+// Two independent fp32 fused multiply-adds in one instruction (fma.rn.f32x2, sm_100): d = a*b + c
+// on both halves, each rounded exactly like fmaf.  The chain kernels are bound by instruction
+// issue, not by the FMA pipe, so halving the count of their fmas shortens a step.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0,
+                                      float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+
 // Warp-wide float min in one instruction (sm_100a).
 __device__ __forceinline__ float warp_min(float v) {
   float m;

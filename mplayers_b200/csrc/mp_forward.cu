@@ -123,22 +123,30 @@ __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr
   }
   float val[LMAX];
 #pragma unroll
-  for (int f = 0; f < LMAX; ++f) val[f] = fmaf(e, cr[OFF + f], hv[f]);
+  for (int f = 0; f + 1 < LMAX; f += 2) ffma2(val[f], val[f + 1], e, e, cr[OFF + f], cr[OFF + f + 1], hv[f], hv[f + 1]);
+  if (LMAX & 1) val[LMAX - 1] = fmaf(e, cr[OFF + LMAX - 1], hv[LMAX - 1]);
   best = min_tree<LMAX>(val);
   bi = 0;
   if (TRAIN) {
     // Sums of distinct powers of two are exact in any order, so each group of 24 labels is
-    // accumulated in three interleaved partial sums (short dependency chains).
+    // accumulated in four interleaved partial sums (short dependency chains), two per packed fma.
     constexpr int NA = (LMAX + 23) / 24;
-    float acc[NA][3];
+    float acc[NA][4];
 #pragma unroll
-    for (int a = 0; a < NA; ++a) acc[a][0] = acc[a][1] = acc[a][2] = 0.f;
+    for (int a = 0; a < NA; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
 #pragma unroll
-    for (int f = 0; f < LMAX; ++f)
-      acc[f / 24][f % 3] = fmaf(eq_flag(val[f], best), pow2f(f % 24), acc[f / 24][f % 3]);
+    for (int f = 0; f + 1 < LMAX; f += 2) {  // 24 is even: a pair never straddles two groups
+      const int a = f / 24, j = f & 2;
+      ffma2(acc[a][j], acc[a][j + 1], eq_flag(val[f], best), eq_flag(val[f + 1], best), pow2f(f % 24),
+            pow2f((f + 1) % 24), acc[a][j], acc[a][j + 1]);
+    }
+    if (LMAX & 1) {
+      constexpr int f = LMAX - 1;
+      acc[f / 24][0] = fmaf(eq_flag(val[f], best), pow2f(f % 24), acc[f / 24][0]);
+    }
 #pragma unroll
     for (int a = 0; a < NA; ++a) {
-      const float sum = (acc[a][0] + acc[a][1]) + acc[a][2];
+      const float sum = (acc[a][0] + acc[a][1]) + (acc[a][2] + acc[a][3]);
       const int ex = ((__float_as_int(sum) >> 23) & 0xff) - 127 + 24 * a;
       if (a == 0) {
         bi = ex;
