@@ -146,7 +146,7 @@ def dominant_kernel(cfg, kind):
     if not cfg["training"] and cfg["label_context"].dim() == 1 and L % 4 == 0:
         return "fwd_wide_kernel"
     if pair:
-        return "fwd_pair_kernel"
+        return "fwd_pair_smem_kernel"
     return "fwd_cta_tma_kernel" if L % 4 == 0 else "fwd_cta_kernel"
 
 

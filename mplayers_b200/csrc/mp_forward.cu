@@ -1458,8 +1458,196 @@ cudaError_t launch_wide_r(const FwdParams& p, int R, cudaStream_t st) {
   return launch_wide<LPT, 16>(p, st);
 }
 
+// Variant with the context rows in shared memory (one [64][68] table per CTA; row stride 68 makes
+// the per-lane 16-byte row reads conflict-free): 164 registers instead of 255, so three chains
+// per SM sub-partition instead of two.  Lane l owns labels l and l + 32.  It is bound by shared
+// memory bandwidth (every step reads both 64-float rows of every lane: 16 KB per warp and step)
+// and still ~8 % faster than the register variant, which is bound by issue latency at two
+// warps per sub-partition.
+constexpr int kPairSWarps = 4;
+constexpr int kPairRS = 68;
+
+template <bool TRAIN>
+__device__ __forceinline__ void minplus_rows32(const float* hb, const float* crow, float e, float& best, int& bi) {
+  float cr[32];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 t = reinterpret_cast<const float4*>(crow)[q];
+    cr[4 * q] = t.x, cr[4 * q + 1] = t.y, cr[4 * q + 2] = t.z, cr[4 * q + 3] = t.w;
+  }
+  minplus_regrow<32, TRAIN>(hb, cr, e, best, bi);
+}
+
+template <bool TRAIN>
+__global__ void __launch_bounds__(kPairSWarps * 32, 3) fwd_pair_smem_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(128) float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = p.L, D = p.agg ? 2 : p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
+  float* ctab = smem;  // [64][kPairRS]
+  for (int i = threadIdx.x; i < 64 * kPairRS; i += blockDim.x) {
+    const int c = i / kPairRS, f = i - c * kPairRS;
+    ctab[i] = (c < L && f < L) ? ctx_value(p.ctx, p.ctx_rank, L, c, f) : 0.f;
+  }
+  const int tile_floats = A * K * L;
+  const int per_warp = NS * tile_floats + 2 * 64 + 2 * K + 2 * NS + 2;
+  float* wbase = smem + 64 * kPairRS + warp * ((per_warp + 3) & ~3);
+  float* tiles = wbase;                               // [NS][A][K][L]
+  float* hbuf = tiles + NS * tile_floats;             // [2][64]
+  float* etile = hbuf + 128;                          // [2][K]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(etile + 2 * K + ((2 * K) & 1));
+  if (lane == 0)
+    for (int i = 0; i < NS; ++i) mbar_init(&full[i], 1);
+  hbuf[lane] = kInf, hbuf[32 + lane] = kInf, hbuf[64 + lane] = kInf, hbuf[96 + lane] = kInf;
+  if (lane == 0) mbar_fence_init();
+  __syncthreads();
+  ChainCtx ch;
+  if (!decode_chain(p, blockIdx.x * kPairSWarps + warp, ch)) return;
+
+  const int len = ch.len;
+  const int nstages = (len + K - 1) / K;
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  const int pix0 = ch.h0 * p.W + ch.w0;
+  const bool contiguous = (ch.pstep == 1 || ch.pstep == -1);
+  const float* U = p.unary + ibase * L;
+  const float* Mr = p.msg_read + ibase * L;
+
+  auto issue_stage = [&](int s) {
+    if (s >= nstages) return;
+    const int slot = s % NS;
+    const int np = len - s * K < K ? len - s * K : K;
+    float* T = tiles + slot * tile_floats;
+    if (lane == 0) {
+      fence_proxy_async_smem();
+      mbar_arrive_expect_tx(&full[slot], (unsigned)(np * A * L) * 4u);
+    }
+    __syncwarp();
+    if (contiguous) {
+      const int first = ch.pstep == 1 ? pix0 + s * K : pix0 - (s * K + np - 1);
+      if (lane < A) {
+        const int sid = p.agg ? (lane == 1 ? ch.dir : ch.inv) : lane - 1;
+        const float* src = (lane == 0 ? U : Mr + (long long)sid * p.slice) + (long long)first * L;
+        bulk_g2s(T + lane * K * L, src, (unsigned)(np * L) * 4u, &full[slot]);
+      }
+    } else {
+      for (int q = lane; q < np * A; q += 32) {
+        const int k = q / A, a = q - k * A;
+        const int px = pix0 + (s * K + k) * ch.pstep;
+        const int sid = p.agg ? (a == 1 ? ch.dir : ch.inv) : a - 1;
+        const float* src = (a == 0 ? U : Mr + (long long)sid * p.slice) + (long long)px * L;
+        bulk_g2s(T + (a * K + k) * L, src, (unsigned)L * 4u, &full[slot]);
+      }
+    }
+  };
+
+  const int la = lane, lb = lane + 32;
+  const bool actb = lb < L;               // la < L always (L > 32)
+  const int lbc = actb ? lb : la;         // loads of a missing second label repeat the first
+  const float* rowa = ctab + la * kPairRS;
+  const float* rowb = ctab + lbc * kPairRS;
+  float* Mw = p.msg_write + (long long)ch.dir * p.slice + ibase * L;
+  const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
+  uint8_t* MI = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L : nullptr;
+  uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
+  const int dir_off = (p.agg ? 1 : 1 + ch.dir) * K * L, inv_off = (p.agg ? 2 : 1 + ch.inv) * K * L;
+  const float rho = p.rho;
+  auto load_e = [&](int s) -> float {
+    const int j = s * K + lane;
+    return (E && lane < K && j < len && j >= 1) ? E[pix0 + j * ch.pstep] : 1.f;
+  };
+  auto eval_label = [&](const float* hb, const float* row, float e, float& best, int& bi) {
+    float ba, bb;
+    int ia, ib;
+    minplus_rows32<TRAIN>(hb, row, e, ba, ia);
+    minplus_rows32<TRAIN>(hb + 32, row + 32, e, bb, ib);
+    best = fminf(ba, bb);
+    bi = bb <= ba ? ib + 32 : ia;   // the later half wins ties: highest index
+  };
+
+  for (int s = 0; s < NS; ++s) issue_stage(s);
+  if (lane < K) etile[lane] = load_e(0);
+  float e_next = load_e(1);
+  float uu0 = 0.f, uu1 = 0.f, r0 = 0.f, r1 = 0.f;
+  int po = pix0 * L;
+  const int postep = ch.pstep * L;
+  int px = pix0;
+  for (int s = 0; s < nstages; ++s) {
+    const int slot = s % NS;
+    if (!mbar_wait(&full[slot], (s / NS) & 1)) {
+      if (lane == 0) atomicExch(p.status, 132);
+      return;
+    }
+    const int np = len - s * K < K ? len - s * K : K;
+    const float* T = tiles + slot * tile_floats;
+    const float* et = etile + (s & 1) * K;
+    const bool flip = contiguous && ch.pstep == -1;
+    __syncwarp();
+    for (int k = 0; k < np; ++k) {
+      const float* t = T + (flip ? np - 1 - k : k) * L;
+      float va = t[la], vb = t[lbc];
+      if (!p.agg)
+        for (int a = 1; a <= D; ++a) va += t[a * K * L + la], vb += t[a * K * L + lbc];
+      const float un0 = fmaf(va - t[dir_off + la], rho, -t[inv_off + la]);
+      const float un1 = fmaf(vb - t[dir_off + lbc], rho, -t[inv_off + lbc]);
+      if (s + k > 0) {
+        const float e = et[k];
+        float* hb = hbuf + ((s * K + k) & 1) * 64;
+        hb[la] = fmaf(rho, r0, uu0);
+        if (actb) hb[lb] = fmaf(rho, r1, uu1);
+        __syncwarp();
+        float b0, b1;
+        int i0, i1;
+        eval_label(hb, rowa, e, b0, i0);
+        eval_label(hb, rowb, e, b1, i1);
+        const float x1 = actb ? b1 : kInf;
+        const float m = warp_min(fminf(b0, x1));
+        r0 = b0 - m;
+        r1 = b1 - m;
+        Mw[po + la] = r0;
+        if (actb) Mw[po + lb] = r1;
+        if (TRAIN) {
+          const unsigned bal0 = __ballot_sync(0xffffffffu, b0 == m);
+          const unsigned bal1 = __ballot_sync(0xffffffffu, x1 == m);
+          MI[po + la] = (uint8_t)i0;
+          if (actb) MI[po + lb] = (uint8_t)i1;
+          if (lane == 0) NI[px] = (uint8_t)(bal1 ? 63 - __clz(bal1) : 31 - __clz(bal0));
+        }
+      }
+      uu0 = un0;
+      uu1 = un1;
+      po += postep;
+      px += ch.pstep;
+    }
+    if (lane < K) etile[((s + 1) & 1) * K + lane] = e_next;
+    e_next = load_e(s + 2);
+    __syncwarp();
+    issue_stage(s + NS);
+  }
+}
+
+template <bool TRAIN>
+cudaError_t launch_pair_smem(FwdParams p, cudaStream_t st) {
+  const int total = p.chain_off[p.ndirs];
+  const int A = (p.agg ? 2 : p.D) + 1;
+  int K = 4, NS = 3;
+  auto per_warp = [&](int k, int ns) { return ((ns * A * k * p.L + 128 + 2 * k + 2 * ns + 2) + 3) & ~3; };
+  auto bytes = [&](int k) { return ((size_t)64 * kPairRS + (size_t)kPairSWarps * per_warp(k, NS)) * sizeof(float); };
+  while (K > 1 && bytes(K) > 72 * 1024) K >>= 1;
+  p.tma_k = K;
+  p.tma_stages = NS;
+  const size_t smem = bytes(K);
+  cudaError_t e = ensure_smem(fwd_pair_smem_kernel<TRAIN>, smem);
+  if (e != cudaSuccess) return e;
+  ProfScope prof(kProfFwdSweep, st);
+  fwd_pair_smem_kernel<TRAIN><<<(total + kPairSWarps - 1) / kPairSWarps, kPairSWarps * 32, smem, st>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
 template <bool TRAIN>
 cudaError_t launch_pair(FwdParams p, cudaStream_t st) {
+  // default: context rows in shared memory (three CTAs of four chains per SM); MPL_PAIR_REG=1 selects
+  // the variant that keeps both rows of a lane in registers (comparison knob)
+  if (!(getenv("MPL_PAIR_REG") && getenv("MPL_PAIR_REG")[0] == '1')) return launch_pair_smem<TRAIN>(p, st);
   const int total = p.chain_off[p.ndirs];
   const int A = (p.agg ? 2 : p.D) + 1;
   int K = 8, NS = 3;
