@@ -38,6 +38,8 @@ def lib():
         _lib.mpo_forward.restype = ctypes.c_int
         _lib.mpo_backward.restype = ctypes.c_int
         _lib.mpo_max_threads.restype = ctypes.c_int
+        _lib.mpo_forward_soft.restype = ctypes.c_int
+        _lib.mpo_backward_soft.restype = ctypes.c_int
     return _lib
 
 
@@ -103,6 +105,53 @@ def backward(mode, ctx, edge_weights, dcost, min_idx, norm_idx, rho=None, enable
                             _p(dew, ctypes.c_float))
     if rc:
         raise RuntimeError("mpo_backward failed with code %d" % rc)
+    return dict(dunary=dunary, dctx=dctx, dew=dew)
+
+
+def forward_soft(unary, ctx, edge_weights, n_dir, n_iter, rho=0.5, training=True, save_labels=False,
+                 n_threads=None):
+    """Soft (expected-value) TRWP.  Returns dict(cost, msg, edge_label, norm_idx, label_all);
+    edge_label [I,D,B,cv,H,W,L,L] holds entry [f][c] for even directions and [c][f] for odd ones."""
+    unary = np.ascontiguousarray(unary, np.float32)
+    ctx = np.ascontiguousarray(ctx, np.float32)
+    b, cv, h, w, l = unary.shape
+    if edge_weights is None:
+        edge_weights = np.ones((n_dir, b, cv, h, w), np.float32)
+    edge_weights = np.ascontiguousarray(edge_weights, np.float32)
+    prob = _problem("TRWP", unary, n_dir, n_iter, ctx, rho, 0, 0, 1, n_threads)
+    msg = np.zeros((n_dir, b, cv, h, w, l), np.float32)
+    cost = np.zeros_like(unary)
+    el = np.zeros((n_iter, n_dir, b, cv, h, w, l, l), np.float32) if training else None
+    ni = np.zeros((n_iter, n_dir, b, cv, h, w), np.uint8) if training else None
+    lab = np.zeros((n_iter, b, cv, h, w), np.uint8) if save_labels else None
+    rc = lib().mpo_forward_soft(ctypes.byref(prob), _p(unary, ctypes.c_float), _p(ctx, ctypes.c_float),
+                                _p(edge_weights, ctypes.c_float), _p(msg, ctypes.c_float),
+                                _p(cost, ctypes.c_float), _p(el, ctypes.c_float), _p(ni, ctypes.c_uint8),
+                                _p(lab, ctypes.c_uint8))
+    if rc:
+        raise RuntimeError("mpo_forward_soft failed with code %d" % rc)
+    return dict(cost=cost, msg=msg, edge_label=el, norm_idx=ni, label_all=lab)
+
+
+def backward_soft(ctx, edge_weights, dcost, edge_label, norm_idx, rho=0.5, n_threads=None):
+    """Returns dict(dunary, dctx, dew); dctx includes the diagonal (c == f)."""
+    dcost = np.ascontiguousarray(dcost, np.float32)
+    ctx = np.ascontiguousarray(ctx, np.float32)
+    n_iter, n_dir = norm_idx.shape[:2]
+    b, cv, h, w, l = dcost.shape
+    if edge_weights is None:
+        edge_weights = np.ones((n_dir, b, cv, h, w), np.float32)
+    edge_weights = np.ascontiguousarray(edge_weights, np.float32)
+    prob = _problem("TRWP", dcost, n_dir, n_iter, ctx, rho, 0, 0, 1, n_threads)
+    dunary = np.zeros_like(dcost)
+    dctx = np.zeros_like(ctx)
+    dew = np.zeros_like(edge_weights)
+    rc = lib().mpo_backward_soft(ctypes.byref(prob), _p(ctx, ctypes.c_float), _p(edge_weights, ctypes.c_float),
+                                 _p(dcost, ctypes.c_float), _p(np.ascontiguousarray(edge_label), ctypes.c_float),
+                                 _p(np.ascontiguousarray(norm_idx), ctypes.c_uint8), _p(dunary, ctypes.c_float),
+                                 _p(dctx, ctypes.c_float), _p(dew, ctypes.c_float))
+    if rc:
+        raise RuntimeError("mpo_backward_soft failed with code %d" % rc)
     return dict(dunary=dunary, dctx=dctx, dew=dew)
 
 

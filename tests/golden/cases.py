@@ -18,7 +18,15 @@ CASES = {
     # the reference's CPU-runnable configuration: B1 D4 64x64 L21 I5, Potts, E~U[0.5,1], seed 0
     "trwp_config1":    ("TRWP", 4, 1, 64, 64, 21, 5, "potts2d", 0),
     "isgmr_config1":   ("ISGMR", 4, 1, 64, 64, 21, 5, "potts2d", 0),
+    # soft (expected-value) TRWP: names start with "trwp_soft"
+    "trwp_soft_d4_small":  ("TRWP", 4, 2, 7, 9, 5, 3, "sym2d", 21),
+    "trwp_soft_d8_small":  ("TRWP", 8, 1, 6, 8, 6, 2, "sym2d", 22),
+    "trwp_soft_d4_tl1d":   ("TRWP", 4, 1, 6, 10, 12, 2, "tl1d", 23),
 }
+
+
+def is_soft(name):
+    return name.startswith("trwp_soft")
 
 
 def make_context(kind, L, rng):

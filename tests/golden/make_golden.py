@@ -60,7 +60,8 @@ def run_case(MessagePassingModule, name, store_indices):
                              ISGMR_parallel=(mode == "ISGMR"), enable_debug=False,
                              target="Stereo", graph_model="min_sum", label_context=lc,
                              n_edge_feats=1, llambda=1., enable_Gaussian=False,
-                             enable_message_vector=store_indices)
+                             enable_message_vector=store_indices,
+                             enable_soft_weight=cases.is_soft(name))
     out = m.forward(score, torch.zeros(B, 3, H, W, dtype=torch.float64), ew)
     cost = -out[0]                                            # [B,L,H,W]
     dcost = torch.from_numpy(inp["dcost"]).double()[:, 0].permute(0, 3, 1, 2)
@@ -80,6 +81,18 @@ def run_case(MessagePassingModule, name, store_indices):
         res["dctx_diag"] = np.array([dctx[0]])
         dctx[0] = 0.0
     res["dctx"] = dctx
+    if cases.is_soft(name):
+        # soft TRWP accumulates the label-context gradient on the diagonal as well
+        # (MPLayers/TRWP_hard_soft/TRWP_backward_soft.cu:114-126) and saves the edge values
+        # themselves ([f][c] for even directions, [c][f] for odd ones) instead of argmin indices
+        if ctx.ndim == 2:
+            res["dctx"] = dctx + np.diag(np.diag(Gs))
+        else:
+            res["dctx"] = dctx.copy()
+            res["dctx"][0] = res["dctx_diag"][0]
+        res["edge_label"] = out[5].detach().numpy()
+        res["norm_idx"] = out[6].detach().numpy().astype(np.uint8)
+        return res
     if store_indices:
         mv = out[5].detach().numpy()      # [I,D,B,1,H,W,L,L]
         ni = out[6].detach().numpy()      # [I,D,B,1,H,W]
@@ -106,7 +119,10 @@ def run_case(MessagePassingModule, name, store_indices):
 
 def main():
     MPM = import_reference_oracle()
+    only = [a for a in sys.argv[1:] if not a.startswith("-")]
     for name in cases.CASES:
+        if only and name not in only:
+            continue
         small = not name.endswith("config1")
         with torch.enable_grad():
             res = run_case(MPM, name, store_indices=small)
