@@ -102,6 +102,28 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
                        float* dedge_weights, float* dmsg, float* dmsg_update, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* ---- Soft (expected-value) TRWP ------------------------------------------------------------------
+ * The message is the expectation of the edge values under softmin weights instead of their
+ * minimum.  Replaces TRWP_hard_soft.forward_soft / backward_soft of the reference
+ * (MPLayers/TRWP_hard_soft/TRWP.cpp:433-436 -> ForwardCUDASoft / BackwardCUDASoft,
+ * MPLayers/TRWP_hard_soft/TRWP_forward_soft.cu:418-558, TRWP_backward_soft.cu:400-551).
+ *   msg_edge_label [I,D,B,cv,H,W,L,L] f32: the edge values of every visited pixel, entry [f][c]
+ *                  (front label f, label c) for even directions and [c][f] for odd ones, as the
+ *                  reference stores them; msg_norm_index [I,D,B,cv,H,W] u8.  Both NULL = inference.
+ *   n_disp <= 32 (MPL_ERR_UNSUPPORTED beyond: L*L values are saved per pixel, direction, iteration).
+ * Forward values agree with the reference kernels bit for bit (same intrinsics, same reduction
+ * order); the backward accumulates dcontext on the diagonal too, as the reference does
+ * (TRWP_backward_soft.cu:114-126).  dmsg is scratch [D,B,cv,H,W,L]. */
+int mpl_trwp_soft_forward(const mpl_problem* p, const float* unary, const float* context,
+                          const float* edge_weights, float* msg, float* cost_final,
+                          float* msg_edge_label, uint8_t* msg_norm_index, uint8_t* label_all,
+                          void* workspace, size_t workspace_bytes, void* stream);
+int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const float* edge_weights,
+                           const float* dcost_final, const float* msg_edge_label,
+                           const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                           float* dedge_weights, float* dmsg, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* ---- ISGMR one iteration at a time, over a subset of directions --------------------------------
  * The D sweeps of an ISGMR iteration only read the previous iteration's messages
  * (MPLayers/ISGMR/ISGMR_forward.cu:506-622), so they can run on different GPUs; what couples them

@@ -2,18 +2,73 @@
 mpnet.py imports for TRWP (mpnet.py:8,35).  Same interface and return tuple; relative to
 MP_module.MPModule it (i) multiplies `label_context` by `mpnet_term_weight` inside forward
 (:151), (ii) keeps the label-context gradient on the diagonal (the TRWP_hard_soft backward does
-not skip c == f), (iii) returns two extra values.  The soft (marginal) branch
-(`args.mpnet_enable_soft`) is not implemented and raises.
+not skip c == f), (iii) returns two extra values.  With `args.mpnet_enable_soft` the soft
+(expected-value) branch runs: the message is the expectation of the edge values under softmin
+weights; in training it saves the edge values [I,D,B,cv,H,W,L,L] (returned as `message_vector`)
+and the normalisation indices (returned as `message_index`), as the reference does
+(pytorch/MP_module_hard_soft.py:37-48,92-97); it is built for n_classes <= 32.
 """
 import torch
 import torch.nn as nn
 
+from . import TRWP as _TRWP
 from .MP_module import TRWPFunction as _TRWPFunctionBase
 from .label_context import create_label_context
 
 
 class TRWPFunction(_TRWPFunctionBase):
     keep_diag = True
+
+
+class TRWPSoftFunction(torch.autograd.Function):
+    """Soft branch of pytorch/MP_module_hard_soft.py:13-110.  Returns (cost_final, label_all,
+    message_edge_label, cost_index)."""
+
+    @staticmethod
+    def forward(ctx, unary, label_context, edge_weights, args):
+        batch, cv, h, w, n_disp = unary.size()
+        rho, n_iter, n_dir, is_training = args.rho, args.mpnet_max_iter, args.mpnet_n_dirs, args.training
+        dev = unary.device
+        unary = unary.contiguous()
+        label_context = label_context.contiguous()
+        message = unary.new_zeros(n_dir, batch, cv, h, w, n_disp)
+        cost_final = torch.empty_like(unary)
+        e0 = torch.empty(0, dtype=torch.float32, device=dev)
+        e8 = torch.empty(0, dtype=torch.uint8, device=dev)
+        enable_edge_weights = edge_weights is not None
+        ew = edge_weights.contiguous() if enable_edge_weights else e0
+        label_all = torch.zeros(n_iter, batch, cv, h, w, dtype=torch.uint8, device=dev) \
+            if args.enable_saving_label else e8
+        if is_training:
+            # entries of pixels without a predecessor are never written and stay 0, as in the reference
+            message_edge_label = unary.new_zeros(n_iter, n_dir, batch, cv, h, w, n_disp, n_disp)
+            cost_index = torch.zeros(n_iter, n_dir, batch, cv, h, w, dtype=torch.uint8, device=dev)
+        else:
+            message_edge_label, cost_index = e0, e8
+        _TRWP.forward_soft(rho, int(n_iter), unary, label_context, ew, message, message_edge_label,
+                           cost_index, cost_final, e0, label_all)
+        ctx.intermediate_results = rho, message_edge_label, cost_index, label_context, ew, enable_edge_weights
+        ctx.mark_non_differentiable(label_all, message_edge_label, cost_index)
+        return cost_final, label_all, message_edge_label, cost_index
+
+    @staticmethod
+    def backward(ctx, dcost_final, dlabel_all, dmessage_edge_label, dcost_index):
+        rho, message_edge_label, cost_index, label_context, ew, enable_edge_weights = ctx.intermediate_results
+        del ctx.intermediate_results
+        if cost_index.numel() == 0:
+            raise RuntimeError("backward needs the edge values saved by a training-mode forward "
+                               "(args.training was False)")
+        dcost_final = dcost_final.contiguous()
+        n_iter, n_dir, batch, cv, h, w = cost_index.size()
+        n_disp = dcost_final.size(-1)
+        dunary = torch.empty_like(dcost_final)
+        dmessage = dcost_final.new_empty(n_dir, batch, cv, h, w, n_disp)
+        dlabel_context = torch.zeros_like(label_context)
+        e0 = torch.empty(0, dtype=torch.float32, device=dcost_final.device)
+        dedge_weights = torch.zeros_like(ew) if enable_edge_weights else e0
+        _TRWP.backward_soft(rho, dcost_final, label_context, ew, message_edge_label, cost_index, dunary,
+                            dlabel_context, dedge_weights, dmessage, e0)
+        return dunary, dlabel_context, (dedge_weights if enable_edge_weights else None), None
 
 
 class MPModule(torch.nn.Module):
@@ -41,8 +96,6 @@ class MPModule(torch.nn.Module):
                                  enable_symmetric=self.args.enable_symmetric)
 
     def forward(self, unary, edge_weights=None, msg_norm_index=None, pairwise_terms=None):
-        if getattr(self.args, 'mpnet_enable_soft', False):
-            raise NotImplementedError("the soft (marginal) TRWP branch is not part of this library")
         if msg_norm_index is not None:
             raise NotImplementedError("externally supplied msg_norm_index (a debugging hook of the "
                                       "reference) is not supported")
@@ -64,6 +117,11 @@ class MPModule(torch.nn.Module):
         if edge_weights is not None:
             assert unary.size()[-3:-1] == edge_weights.size()[-2:]
         self.args.training = self.training
+        if getattr(self.args, 'mpnet_enable_soft', False):
+            cost_final, cost_all, message_vector, message_index = \
+                TRWPSoftFunction.apply(unary, label_context, edge_weights, self.args)
+            cost_final = cost_final.permute(0, 1, 4, 2, 3).contiguous()
+            return cost_final, label_context.unsqueeze(0), cost_all, message_vector, message_index
         cost_final, cost_all = TRWPFunction.apply(unary, label_context, edge_weights, self.args)
         cost_final = cost_final.permute(0, 1, 4, 2, 3).contiguous()
         label_context = label_context.unsqueeze(0)

@@ -66,3 +66,50 @@ def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_in
             ctypes.byref(prob), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(dcost_final),
             _lib.ptr(msg_min_index), _lib.ptr(msg_norm_index), _lib.ptr(dunary), _lib.ptr(dcontext),
             _lib.ptr(dedge_weights), _lib.ptr(dmsg), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+
+
+def forward_soft(rho, n_iter, unary, context, edge_weights, msg, msg_edge_label, msg_norm_index,
+                 cost_final, unary_update, label_all):
+    """TRWP_hard_soft.forward_soft of the reference (MPLayers/TRWP_hard_soft/TRWP.cpp:433; argument
+    order of pytorch/MP_module_hard_soft.py:44-46).  msg_edge_label [I,D,B,cv,H,W,L,L] and
+    msg_norm_index [I,D,B,cv,H,W] are empty tensors in inference."""
+    dev = unary.device
+    for t, n in ((unary, "unary"), (context, "context"), (edge_weights, "edge_weights"), (msg, "msg"),
+                 (cost_final, "cost_final"), (msg_edge_label, "msg_edge_label")):
+        _lib.require(t, n, torch.float32, dev)
+    for t, n in ((msg_norm_index, "msg_norm_index"), (label_all, "label_all")):
+        _lib.require(t, n, torch.uint8, dev)
+    if msg.dim() != 6 or tuple(unary.shape) != tuple(msg.shape[1:]):
+        raise RuntimeError("msg must be [D,B,cv,H,W,L] matching unary [B,cv,H,W,L]")
+    prob = _problem(n_iter, tuple(msg.shape), context, rho)
+    with torch.cuda.device(dev):
+        nbytes = _lib.lib().mpl_forward_workspace_bytes(ctypes.byref(prob))
+        ws = _lib.workspace(nbytes, dev)
+        _lib.check(_lib.lib().mpl_trwp_soft_forward(
+            ctypes.byref(prob), _lib.ptr(unary), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(msg),
+            _lib.ptr(cost_final), _lib.ptr(msg_edge_label), _lib.ptr(msg_norm_index), _lib.ptr(label_all),
+            _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+
+
+def backward_soft(rho, dcost_final, context, edge_weights, msg_edge_label, msg_norm_index, dunary,
+                  dcontext, dedge_weights, dmsg, dunary_update):
+    """TRWP_hard_soft.backward_soft (MPLayers/TRWP_hard_soft/TRWP.cpp:434; argument order of
+    pytorch/MP_module_hard_soft.py:95-97)."""
+    dev = dcost_final.device
+    for t, n in ((context, "context"), (edge_weights, "edge_weights"), (dcost_final, "dcost_final"),
+                 (msg_edge_label, "msg_edge_label"), (dunary, "dunary"), (dcontext, "dcontext"),
+                 (dedge_weights, "dedge_weights"), (dmsg, "dmsg")):
+        _lib.require(t, n, torch.float32, dev)
+    _lib.require(msg_norm_index, "msg_norm_index", torch.uint8, dev)
+    if msg_norm_index.dim() != 6 or msg_edge_label.dim() != 8:
+        raise RuntimeError("msg_norm_index must be [I,D,B,cv,H,W] and msg_edge_label [I,D,B,cv,H,W,L,L]")
+    n_iter = msg_norm_index.size(0)
+    shape = tuple(msg_norm_index.shape[1:]) + (msg_edge_label.size(-1),)
+    prob = _problem(n_iter, shape, context, rho)
+    with torch.cuda.device(dev):
+        nbytes = _lib.lib().mpl_backward_workspace_bytes(ctypes.byref(prob))
+        ws = _lib.workspace(nbytes, dev)
+        _lib.check(_lib.lib().mpl_trwp_soft_backward(
+            ctypes.byref(prob), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(dcost_final),
+            _lib.ptr(msg_edge_label), _lib.ptr(msg_norm_index), _lib.ptr(dunary), _lib.ptr(dcontext),
+            _lib.ptr(dedge_weights), _lib.ptr(dmsg), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))

@@ -58,6 +58,10 @@ def lib():
         L.mpl_isgmr_backward_combine.argtypes = [pp, i32, i32] + [vp] * 5
         L.mpl_backward_context_finish.restype = ctypes.c_int
         L.mpl_backward_context_finish.argtypes = [pp, vp, sz, vp, vp]
+        L.mpl_trwp_soft_forward.restype = ctypes.c_int
+        L.mpl_trwp_soft_forward.argtypes = [pp] + [vp] * 9 + [sz, vp]
+        L.mpl_trwp_soft_backward.restype = ctypes.c_int
+        L.mpl_trwp_soft_backward.argtypes = [pp] + [vp] * 10 + [sz, vp]
         L.mpl_trwp_backward_static.restype = ctypes.c_int
         L.mpl_trwp_backward_static.argtypes = [pp] + [vp] * 10
         L.mpl_static_scratch_bytes.restype = sz

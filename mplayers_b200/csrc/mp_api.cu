@@ -538,6 +538,88 @@ int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t wo
   return MPL_OK;
 }
 
+// ---- soft (expected-value) TRWP ------------------------------------------------------------------
+int mpl_trwp_soft_forward(const mpl_problem* p, const float* unary, const float* context,
+                          const float* edge_weights, float* msg, float* cost_final, float* msg_edge_label,
+                          uint8_t* msg_norm_index, uint8_t* label_all, void* workspace,
+                          size_t workspace_bytes, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (int rc = check_chain_count(p, d)) return rc;
+  if (p->n_disp > 32)
+    return fail(MPL_ERR_UNSUPPORTED, "soft TRWP is built for n_disp <= 32 (got %d): it saves n_disp^2 values per "
+                                     "pixel, direction and iteration", p->n_disp);
+  if (!unary || !context || !msg || !cost_final) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if ((msg_edge_label == nullptr) != (msg_norm_index == nullptr))
+    return fail(MPL_ERR_INVALID, "msg_edge_label and msg_norm_index must both be given or both be NULL");
+  if (!workspace || workspace_bytes < mpl_forward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_forward_workspace_bytes(p));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool train = msg_edge_label != nullptr;
+  const int D = p->n_dir, L = p->n_disp;
+  mpl::FwdParams fp{};
+  fill_forward(fp, p, d, unary, context, edge_weights, workspace);
+  MPL_CUDA(cudaMemsetAsync(fp.status, 0, sizeof(int), st));
+  fp.msg_read = msg;
+  fp.msg_write = msg;
+  for (int it = 0; it < p->n_iter; ++it) {
+    fp.norm_idx = train ? msg_norm_index + (long long)it * D * d.npix : nullptr;
+    fp.edge_label = train ? msg_edge_label + (long long)it * D * d.npix * L * L : nullptr;
+    for (int dir = 0; dir < D; ++dir) {  // later directions see earlier ones' new messages
+      set_dirs(fp, dir, 1);
+      MPL_CUDA(mpl::launch_forward_soft_sweep(fp, train, st));
+    }
+    if (label_all)
+      MPL_CUDA(mpl::launch_aggregate(unary, msg, cost_final, label_all + (long long)it * d.npix, d.npix, L, D,
+                                     d.slice, 1.f, 0, st));
+  }
+  MPL_CUDA(mpl::launch_aggregate(unary, msg, cost_final, nullptr, d.npix, L, D, d.slice, 1.f, 0, st));
+  return MPL_OK;
+}
+
+int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const float* edge_weights,
+                           const float* dcost_final, const float* msg_edge_label,
+                           const uint8_t* msg_norm_index, float* dunary, float* dcontext,
+                           float* dedge_weights, float* dmsg, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (int rc = check_chain_count(p, d)) return rc;
+  if (p->n_disp > 32) return fail(MPL_ERR_UNSUPPORTED, "soft TRWP is built for n_disp <= 32 (got %d)", p->n_disp);
+  if (!context || !dcost_final || !msg_edge_label || !msg_norm_index || !dunary || !dcontext || !dmsg)
+    return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if (edge_weights && !dedge_weights)
+    return fail(MPL_ERR_INVALID, "dedge_weights is NULL although edge_weights is given");
+  if (!workspace || workspace_bytes < mpl_backward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_backward_workspace_bytes(p));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int D = p->n_dir, L = p->n_disp;
+  const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg);
+  float* part = static_cast<float*>(workspace);
+  int* status = reinterpret_cast<int*>(part + (size_t)n_slots * d.ctx_elems);
+  MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
+  MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+  // C + P bookkeeping (BwdParams::cp_scheme == 1): C in dunary, P_k in dmsg
+  MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, dmsg, d.slice, D, 1.f, 1, st));
+  mpl::BwdParams bp{};
+  fill_backward(bp, p, d, context, edge_weights, dunary, part, n_slots, 1, status);
+  bp.dm_read = dmsg;
+  bp.dm_acc = dmsg;
+  bp.dew = (edge_weights && dedge_weights) ? dedge_weights : nullptr;
+  for (int it = p->n_iter - 1; it >= 0; --it) {
+    bp.norm_idx = msg_norm_index + (long long)it * D * d.npix;
+    bp.edge_label = msg_edge_label + (long long)it * D * d.npix * L * L;
+    for (int dir = D - 1; dir >= 0; --dir) {
+      bp.dir = dir;
+      MPL_CUDA(mpl::launch_backward_soft_sweep(bp, st));
+    }
+  }
+  MPL_CUDA(mpl::launch_dctx_reduce(part, n_slots, L, p->context_rank, 1, dcontext, st));
+  return MPL_OK;
+}
+
 int mpl_forward_status(const void* workspace, int32_t* status) {
   if (!workspace || !status) return fail(MPL_ERR_INVALID, "NULL pointer");
   MPL_CUDA(cudaMemcpy(status, static_cast<const char*>(workspace) + 64, sizeof(int32_t), cudaMemcpyDeviceToHost));

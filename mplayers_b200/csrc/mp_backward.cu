@@ -867,6 +867,131 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Soft (expected-value) TRWP backward, L <= 32: one warp per chain, lane = label c, C + P scheme.
+// Per step the softmin weights of every label are recomputed from the saved edge values,
+//   d(value[c][f]) = t[c] * w[c][f] * (1 - value[c][f] + message[c]),
+// the scatter q[f] = sum_c d(value[c][f]) goes through a shared-memory transpose and is carried to
+// the predecessor pixel in a register; the label-context gradient of row c lives in registers of
+// lane c for the whole chain (diagonal included, as in the reference,
+// MPLayers/TRWP_hard_soft/TRWP_backward_soft.cu:100-127).
+// ------------------------------------------------------------------------------------------------
+template <int LMAX>
+__global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant__ BwdParams p) {
+  __shared__ float tile_s[4][32 * 33];
+  const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = blockIdx.x * wpb + warp;
+  BChain ch;
+  if (!decode_bchain(p, g, ch)) return;
+  float* tile = tile_s[warp];
+  const int L = p.L, dir = ch.dir, inv = dir ^ 1;
+  const bool act = lane < L;
+  const int lc = act ? lane : L - 1;
+  const bool l2r = (dir & 1) == 0;
+
+  float cr[LMAX], acc[LMAX];
+#pragma unroll
+  for (int f = 0; f < LMAX; ++f) {
+    cr[f] = (act && f < L) ? ctx_value(p.ctx, p.ctx_rank, L, lane, f) : 0.f;
+    acc[f] = 0.f;
+  }
+  const long long ibase = (long long)ch.img * p.H * p.W;
+  float* C = p.dunary + ibase * L + lc;                                   // common part of dM_k
+  float* Pd = p.dm_read + (long long)dir * p.slice + ibase * L + lc;      // P_dir
+  float* Pi = p.dm_read + (long long)inv * p.slice + ibase * L + lc;      // P_inv
+  const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
+  float* DE = p.dew ? p.dew + (long long)dir * p.pslice + ibase : nullptr;
+  const uint8_t* NI = p.norm_idx + (long long)dir * p.pslice + ibase;
+  const float* EL = p.edge_label + ((long long)dir * p.pslice + ibase) * L * L;
+  const int len = ch.len, pstep = ch.pstep;
+  int px = ch.h0 * p.W + ch.w0 + (len - 1) * pstep;  // last pixel of the chain
+  const float rho = p.rho;
+
+  auto load_values = [&](int pxl, float (&d)[LMAX]) {  // edge values of row c = lane at pixel pxl
+    const float* el = EL + (long long)pxl * L * L;
+#pragma unroll
+    for (int f = 0; f < LMAX; ++f) d[f] = (f < L) ? (l2r ? el[f * L + lc] : el[lc * L + f]) : kInf;
+  };
+
+  float q = 0.f;
+  float dn[LMAX];
+  if (len > 1) load_values(px, dn);
+  float x_n = C[px * L] + Pd[px * L];
+  for (int s = 0; s < len; ++s) {
+    const int of = px * L;
+    const float c_old = C[of];
+    const float x0 = x_n;                 // C + P_dir of this pixel (read before they are rewritten)
+    const float rq = rho * q;
+    float qn = 0.f;
+    if (s < len - 1) {
+      float d[LMAX];
+#pragma unroll
+      for (int f = 0; f < LMAX; ++f) d[f] = dn[f];
+      const int pxf = px - pstep;
+      // prefetch the predecessor's inputs (it is the next pixel visited)
+      if (s < len - 2) load_values(pxf, dn);
+      x_n = C[pxf * L] + Pd[pxf * L];
+      const float e = E ? E[px] : 1.f;
+      const int n = NI[px];
+      float t = act ? x0 + rq : 0.f;
+      const float S = warp_sum(t);
+      t = (lane == n) ? t - S : t;
+      // softmin weights of row c
+      float m = d[0];
+#pragma unroll
+      for (int f = 1; f < LMAX; ++f) m = fminf(m, d[f]);
+      float ex[LMAX], se = 0.f, ms = 0.f;
+#pragma unroll
+      for (int f = 0; f < LMAX; ++f) {
+        ex[f] = (f < L) ? __expf(m - d[f]) : 0.f;
+        se += ex[f];
+      }
+      const float inv_se = 1.f / se;
+#pragma unroll
+      for (int f = 0; f < LMAX; ++f) ms = (f < L) ? fmaf(ex[f] * inv_se, d[f], ms) : ms;
+      float de = 0.f;
+#pragma unroll
+      for (int f = 0; f < LMAX; ++f) {
+        const float dd = (f < L && act) ? t * (ex[f] * inv_se) * (1.f - d[f] + ms) : 0.f;
+        tile[lane * 33 + f] = dd;
+        de = fmaf(cr[f], dd, de);
+        acc[f] = fmaf(e, dd, acc[f]);
+      }
+      de = warp_sum(de);
+      if (DE && lane == 0) atomicAdd(DE + px, de);
+      __syncwarp();
+      if (act) {
+#pragma unroll 4
+        for (int c = 0; c < L; ++c) qn += tile[c * 33 + lane];
+      }
+      __syncwarp();
+    }
+    if (act) {
+      const float cnew = c_old + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
+      C[of] = cnew;
+      Pd[of] = -cnew;                 // dM_dir = C + P_dir = 0 after its sweep
+      atomicAdd(Pi + of, -q);
+    }
+    q = qn;
+    px -= pstep;
+  }
+
+  // flush the label-context gradient of this chain (row c = lane)
+  float* part = p.dctx_part + (long long)(g % p.n_slots) * (p.ctx_rank == 2 ? L * L : L);
+  if (act) {
+#pragma unroll
+    for (int f = 0; f < LMAX; ++f) {
+      if (f < L && acc[f] != 0.f) {
+        if (p.ctx_rank == 2) {
+          atomicAdd(part + lane * L + f, acc[f]);
+        } else {
+          atomicAdd(part + (lane > f ? lane - f : f - lane), acc[f]);
+        }
+      }
+    }
+  }
+}
+
 constexpr int kPFB = 8;  // CTA kernel: pixels of dM_d staged ahead (power of two)
 
 // ------------------------------------------------------------------------------------------------
@@ -1285,6 +1410,25 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
       if (e != cudaSuccess) return e;
     }
     bwd_cta_kernel<<<total, NT, smem, st>>>(p);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_backward_soft_sweep(const BwdParams& p0, cudaStream_t st) {
+  BwdParams p = p0;
+  p.ndirs = 1;
+  p.chain_off[0] = 0;
+  p.chain_off[1] = make_geom(p.dir, p.H, p.W).n_chains * p.nimg;
+  const int total = p.chain_off[1];
+  if (total == 0) return cudaSuccess;
+  if (p.L > 32 || p.cp_scheme != 1) return cudaErrorNotSupported;
+  const int wpb = 4;
+  ProfScope prof(kProfBwdSweep, st);
+  if (p.L <= 21) {
+    bwd_soft_kernel<21><<<(total + wpb - 1) / wpb, wpb * 32, 0, st>>>(p);
+  } else {
+    bwd_soft_kernel<32><<<(total + wpb - 1) / wpb, wpb * 32, 0, st>>>(p);
   }
   count_launch();
   return cudaGetLastError();

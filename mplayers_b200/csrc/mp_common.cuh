@@ -84,6 +84,7 @@ struct FwdParams {
   float* msg_write;       // [D,nimg,H,W,L] slice `dir` receives the new messages
   const float* ctx;
   const float* ew;        // [D,nimg,H,W] or nullptr (= 1)
+  float* edge_label;      // soft TRWP, training: [D,nimg,H,W,L,L] edge values of this iteration, else nullptr
   uint8_t* min_idx;       // [D,nimg,H,W,L] of this iteration, or nullptr
   uint8_t* norm_idx;      // [D,nimg,H,W]
   const CtxInfo* info;
@@ -109,6 +110,7 @@ struct FwdParams {
 struct BwdParams {
   const float* ctx;
   const float* ew;        // or nullptr (= 1)
+  const float* edge_label; // soft TRWP: [D,nimg,H,W,L,L] edge values saved by the forward, else nullptr
   const uint8_t* min_idx; // [D,nimg,H,W,L] of this iteration
   const uint8_t* norm_idx; // [D,nimg,H,W]
   float* dm_read;         // [D,...]: slice `dir` holds the gradient of this sweep's messages; zeroed here
@@ -283,6 +285,8 @@ cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, l
 cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
 cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, float* dm, float* dunary, long long n,
                                        int dir0, int ndirs, float rho, cudaStream_t st);
+cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st);
+cudaError_t launch_backward_soft_sweep(const BwdParams& p, cudaStream_t st);
 cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n, float* out,
                               cudaStream_t st);
 cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long long n, int D, float rho,

@@ -157,6 +157,45 @@ __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr
   }
 }
 
+// Sum of 32 values in the order of a shuffle-down tree over a warp (x[i] += x[i + 16], then 8, 4,
+// 2, 1; lane 0 holds the total): the order in which the reference's soft kernels reduce a row
+// (MPLayers/TRWP_hard_soft/TRWP_soft.cuh:45-71), so sums agree with them bit for bit.
+__device__ __forceinline__ float tree32_sum(float (&x)[32]) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+    for (int i = 0; i < off; ++i) x[i] = __fadd_rn(x[i], x[i + off]);
+  return x[0];
+}
+
+// Soft (expected-value) step of label c = this thread: val[f] = e*ctx(c,f) + h[f], weights
+// softmin_f(val), message = sum_f weight * val (MPLayers/TRWP_hard_soft/TRWP_forward_soft.cu:55-92).
+// Same intrinsics and operation order as the reference: __expf(-val + min), (w * val) / sum.
+template <int LMAX>
+__device__ __forceinline__ float soft_regrow(const float* hb, const float (&cr)[LMAX], float e, int L,
+                                             float (&val)[LMAX]) {
+  constexpr int NV = (LMAX + 3) / 4;
+  float hv[NV * 4];
+#pragma unroll
+  for (int q = 0; q < NV; ++q) {
+    const float4 t = reinterpret_cast<const float4*>(hb)[q];
+    hv[4 * q] = t.x, hv[4 * q + 1] = t.y, hv[4 * q + 2] = t.z, hv[4 * q + 3] = t.w;
+  }
+#pragma unroll
+  for (int f = 0; f < LMAX; ++f) val[f] = fmaf(e, cr[f], hv[f]);   // +inf beyond L
+  const float m = min_tree<LMAX>(val);
+  float ex[32], sf[32];
+#pragma unroll
+  for (int f = 0; f < 32; ++f) ex[f] = (f < LMAX && f < L) ? __expf(-val[f < LMAX ? f : 0] + m) : 0.f;
+#pragma unroll
+  for (int f = 0; f < 32; ++f) sf[f] = ex[f];
+  const float se = tree32_sum(sf);
+#pragma unroll
+  for (int f = 0; f < 32; ++f)
+    sf[f] = (f < LMAX && f < L) ? __fdiv_rn(__fmul_rn(ex[f], val[f < LMAX ? f : 0]), se) : 0.f;
+  return tree32_sum(sf);
+}
+
 // ------------------------------------------------------------------------------------------------
 // L <= 32: one warp per chain.  DT = compile-time direction count (0: read it from the params).
 // ------------------------------------------------------------------------------------------------
@@ -164,7 +203,10 @@ __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr
 // cp.async copies kPF pixels ahead (a register ring of plain loads was measured slower: waiting on
 // a register load drains every younger load too, whereas cp.async groups retire in order).
 // DT = compile-time direction count (0: read it from the params).
-template <int LMAX, int DT, bool TRAIN>
+// SOFT: the soft (expected-value) message instead of the minimum; in training it saves the L x L
+// edge values of every pixel (entry [f][c] for even directions, [c][f] for odd ones, as the
+// reference does, MPLayers/TRWP_hard_soft/TRWP_forward_soft.cu:50-59) and no argmin indices.
+template <int LMAX, int DT, bool TRAIN, bool SOFT = false>
 __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -190,8 +232,10 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
   float* Mwl = p.msg_write + (long long)ch.dir * p.slice + ibase * L + lc;
   const bool has_e = p.ew != nullptr;
   const float* E = has_e ? p.ew + (long long)ch.dir * p.pslice + ibase : p.unary;
-  uint8_t* MIl = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L + lc : nullptr;
+  uint8_t* MIl = (TRAIN && !SOFT) ? p.min_idx + (long long)ch.dir * p.slice + ibase * L + lc : nullptr;
   uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
+  float* EL = (TRAIN && SOFT) ? p.edge_label + ((long long)ch.dir * p.pslice + ibase) * L * L : nullptr;
+  const bool l2r = (ch.dir & 1) == 0;  // layout of the saved edge values
   const int len = ch.len;
   const int ostep = ch.pstep * L;
   const int dir_row = (1 + ch.dir) * 32, inv_row = (1 + ch.inv) * 32;
@@ -243,14 +287,31 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
     hb[lane] = act ? fmaf(rho, r, uu) : kInf;
     __syncwarp();
     float best;
-    int bi;
-    minplus_regrow<LMAX, TRAIN>(hb, cr, e, best, bi);
+    int bi = 0;
+    if constexpr (SOFT) {
+      float val[LMAX];
+      best = soft_regrow<LMAX>(hb, cr, e, L, val);
+      if (TRAIN && act) {
+        float* el = EL + (long long)px * L * L;
+        if (l2r) {
+#pragma unroll
+          for (int f = 0; f < LMAX; ++f)
+            if (f < L) el[f * L + lane] = val[f];
+        } else {
+#pragma unroll
+          for (int f = 0; f < LMAX; ++f)
+            if (f < L) el[lane * L + f] = val[f];
+        }
+      }
+    } else {
+      minplus_regrow<LMAX, TRAIN>(hb, cr, e, best, bi);
+    }
     const float m = warp_min(act ? best : kInf);
     r = best - m;
     if (act) Mwl[of] = r;
     if (TRAIN) {
       const unsigned bal = __ballot_sync(0xffffffffu, act && best == m);
-      if (act) MIl[of] = (uint8_t)bi;
+      if (!SOFT && act) MIl[of] = (uint8_t)bi;
       if (lane == 0) NI[px] = (uint8_t)(31 - __clz(bal));
     }
     issue(i + kPF);
@@ -1309,6 +1370,19 @@ cudaError_t launch_warp(const FwdParams& p, cudaStream_t st) {
   return launch_warp_d<LMAX, 0, TRAIN>(p, st);
 }
 
+template <int LMAX, bool TRAIN>
+cudaError_t launch_warp_soft(const FwdParams& p, cudaStream_t st) {
+  const int total = p.chain_off[p.ndirs];
+  const int wpb = total >= 148 * 32 ? 4 : 1;
+  const size_t smem = (size_t)wpb * (kPF * (p.D + 2) * 32 + 64) * sizeof(float);
+  cudaError_t e = ensure_smem(fwd_warp_kernel<LMAX, 0, TRAIN, true>, smem);
+  if (e != cudaSuccess) return e;
+  ProfScope prof(kProfFwdSweep, st);
+  fwd_warp_kernel<LMAX, 0, TRAIN, true><<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
 size_t tma_smem_bytes(int L, int D, int stages) {
   return ((size_t)stages * ((size_t)(D + 1) * kTK * 4 * L + 64) + 4 * 64) * sizeof(float) + 2 * stages * 8 + 16 + 128;
 }
@@ -1730,6 +1804,14 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
   if (p.ctx_rank == 1) return train ? launch_cta_any<1, true>(p, st) : launch_cta_any<1, false>(p, st);
   if (p.L <= 64) return train ? launch_cta_any<2, true>(p, st) : launch_cta_any<2, false>(p, st);
   return train ? launch_cta_any<0, true>(p, st) : launch_cta_any<0, false>(p, st);
+}
+
+// Soft TRWP sweep of the directions described by p (L <= 32 only: one warp per chain).
+cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st) {
+  if (p.chain_off[p.ndirs] == 0) return cudaSuccess;
+  if (p.L > 32) return cudaErrorNotSupported;
+  if (p.L <= 21) return train ? launch_warp_soft<21, true>(p, st) : launch_warp_soft<21, false>(p, st);
+  return train ? launch_warp_soft<32, true>(p, st) : launch_warp_soft<32, false>(p, st);
 }
 
 cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, uint8_t* label,

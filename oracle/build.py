@@ -79,13 +79,24 @@ def build_reference_cpu(force=False):
     return REF_OUT
 
 
-def build_reference_cuda(force=False, names=("TRWP", "ISGMR")):
-    """Compile the reference's TRWP / ISGMR CUDA extensions for sm_100a into oracle/_ref/cuda/.
+_REF_CUDA = {
+    # name: (directory under MPLayers, .cpp, .cu files, extra macros) -- MPLayers/setup.py:86-128
+    "TRWP": ("TRWP", "TRWP.cpp", ["TRWP_forward.cu", "TRWP_backward.cu"], []),
+    "ISGMR": ("ISGMR", "ISGMR.cpp", ["ISGMR_forward.cu", "ISGMR_backward.cu"], []),
+    "TRWP_hard_soft": ("TRWP_hard_soft", "TRWP.cpp",
+                       ["TRWP_forward.cu", "TRWP_backward.cu", "TRWP_forward_soft.cu",
+                        "TRWP_backward_soft.cu", "TRWP_swbp.cu"], ["-DUSE_HARD", "-DUSE_SOFT"]),
+}
 
-    Sources used (unmodified, read in place): MPLayers/<name>/<name>.cpp, <name>_forward.cu,
-    <name>_backward.cu, MPLayers/common.cpp, tools/cpp/utils.cpp, tools/cuda/cudaUtils.cu, with
-    the reference's own macros (USE_CUDA, MAX_DISPARITY=256 as in its "stereo" build,
-    MPLayers/setup.py:28,62-63,86) and its nvcc flags except the architecture (sm_35 there).
+
+def build_reference_cuda(force=False, names=("TRWP", "ISGMR", "TRWP_hard_soft")):
+    """Compile the reference's TRWP / ISGMR / TRWP_hard_soft CUDA extensions for sm_100a into
+    oracle/_ref/cuda/.
+
+    Sources used (unmodified, read in place): the extension's .cpp and .cu files under MPLayers/,
+    MPLayers/common.cpp, tools/cpp/utils.cpp, tools/cuda/cudaUtils.cu, with the reference's own
+    macros (USE_CUDA, USE_HARD / USE_SOFT, MAX_DISPARITY=256 as in its "stereo" build,
+    MPLayers/setup.py:28,62-63,86,113) and its nvcc flags except the architecture (sm_35 there).
     Returns the output directory, or None if the reference is absent.
     """
     ref = reference_dir()
@@ -103,18 +114,18 @@ def build_reference_cuda(force=False, names=("TRWP", "ISGMR")):
         if os.path.exists(so) and not force:
             continue
         os.makedirs(bdir, exist_ok=True)
+        sub, cpp, cus, macros = _REF_CUDA[name]
         load(name=name,
-             sources=[os.path.join(mp, name, name + ".cpp"), os.path.join(mp, "common.cpp"),
-                      os.path.join(mp, name, name + "_forward.cu"),
-                      os.path.join(mp, name, name + "_backward.cu"),
-                      os.path.join(ref, "tools", "cpp", "utils.cpp"),
+             sources=[os.path.join(mp, sub, cpp), os.path.join(mp, "common.cpp")] +
+                     [os.path.join(mp, sub, c) for c in cus] +
+                     [os.path.join(ref, "tools", "cpp", "utils.cpp"),
                       os.path.join(ref, "tools", "cuda", "cudaUtils.cu")],
-             extra_include_paths=[mp, os.path.join(mp, name), os.path.join(ref, "tools", "cpp"),
+             extra_include_paths=[mp, os.path.join(mp, sub), os.path.join(ref, "tools", "cpp"),
                                   os.path.join(ref, "tools", "cuda")],
              extra_cflags=["-O3", "-fopenmp", "-w", "-DUSE_CUDA", "-DMAX_DISPARITY=256",
-                           "-DTORCH_VERSION_MAJOR=2"],
+                           "-DTORCH_VERSION_MAJOR=2"] + macros,
              extra_cuda_cflags=["-O3", "--expt-relaxed-constexpr", "-w", "-DUSE_CUDA",
-                                "-DMAX_DISPARITY=256", "-DTORCH_VERSION_MAJOR=2"],
+                                "-DMAX_DISPARITY=256", "-DTORCH_VERSION_MAJOR=2"] + macros,
              extra_ldflags=["-fopenmp"], with_cuda=True, build_directory=bdir, verbose=False)
         os.replace(os.path.join(bdir, name + ".so"), so)
     return out

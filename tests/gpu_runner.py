@@ -63,3 +63,41 @@ def backward(mode, ctx, edge_weights, dcost, min_idx, norm_idx, rho=None, enable
     torch.cuda.synchronize()
     return dict(dunary=dunary.cpu().numpy(), dctx=dctx.cpu().numpy(),
                 dew=dew.cpu().numpy() if edge_weights is not None else None)
+
+
+def forward_soft(unary, ctx, edge_weights, n_dir, n_iter, rho=0.5, training=True, save_labels=False):
+    u = _dev(unary)
+    b, cv, h, w, l = u.shape
+    c = _dev(ctx)
+    e0 = torch.empty(0, device="cuda")
+    e8 = torch.empty(0, dtype=torch.uint8, device="cuda")
+    ew = _dev(edge_weights) if edge_weights is not None else e0
+    msg = torch.zeros(n_dir, b, cv, h, w, l, device="cuda")
+    cost = torch.full((b, cv, h, w, l), float("nan"), device="cuda")
+    el = torch.zeros(n_iter, n_dir, b, cv, h, w, l, l, device="cuda") if training else e0
+    ni = torch.zeros(n_iter, n_dir, b, cv, h, w, dtype=torch.uint8, device="cuda") if training else e8
+    lab = torch.zeros(n_iter, b, cv, h, w, dtype=torch.uint8, device="cuda") if save_labels else e8
+    TRWP.forward_soft(rho, n_iter, u, c, ew, msg, el, ni, cost, e0, lab)
+    torch.cuda.synchronize()
+    return dict(cost=cost.cpu().numpy(), msg=msg.cpu().numpy(),
+                edge_label=el.cpu().numpy() if training else None,
+                norm_idx=ni.cpu().numpy() if training else None,
+                label_all=lab.cpu().numpy() if save_labels else None)
+
+
+def backward_soft(ctx, edge_weights, dcost, edge_label, norm_idx, rho=0.5):
+    g = _dev(dcost)
+    c = _dev(ctx)
+    el = _dev(edge_label)
+    ni = _dev(norm_idx, torch.uint8)
+    n_dir = ni.shape[1]
+    e0 = torch.empty(0, device="cuda")
+    ew = _dev(edge_weights) if edge_weights is not None else e0
+    dunary = torch.full_like(g, float("nan"))
+    dctx = torch.zeros_like(c)
+    dew = torch.zeros_like(ew)
+    dmsg = torch.full((n_dir,) + tuple(g.shape), float("nan"), device="cuda")
+    TRWP.backward_soft(rho, g, c, ew, el, ni, dunary, dctx, dew, dmsg, e0)
+    torch.cuda.synchronize()
+    return dict(dunary=dunary.cpu().numpy(), dctx=dctx.cpu().numpy(),
+                dew=dew.cpu().numpy() if edge_weights is not None else None)

@@ -31,7 +31,7 @@ def _check_backward(mode, ctx, ew, dcost, fwd, **kw):
     return got
 
 
-@pytest.mark.parametrize("name", list(cases.CASES))
+@pytest.mark.parametrize("name", [n for n in cases.CASES if not cases.is_soft(n)])
 def test_golden_cases(name):
     """CUDA vs golden vectors of the reference's PyTorch implementation, and vs the oracle."""
     g = _gpu()

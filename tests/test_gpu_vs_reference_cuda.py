@@ -171,3 +171,46 @@ def test_benchmark_configurations_full_size(name, gen, kw, train):
     g = torch.Generator().manual_seed(99)
     dcost = (torch.rand(B, cv, H, W, L, generator=g) - 0.5).cuda()
     _compare_tensors(cfg["mode"], unary, ctx, ew, dcost, D, cfg["n_iter"], train, 2, name + ": ")
+
+
+def _run_soft(mod, unary, ctx, ew, dcost, D, I, rho):
+    import torch
+    B, cv, H, W, L = unary.shape
+    z = lambda *s, **k: unary.new_zeros(*s, **k)  # noqa: E731
+    msg, cost, uu = z(D, B, cv, H, W, L), z(B, cv, H, W, L), z(B, cv, H, W, L)
+    el = z(I, D, B, cv, H, W, L, L)
+    ni = z(I, D, B, cv, H, W, dtype=torch.uint8)
+    lab = z(I, B, cv, H, W, dtype=torch.uint8)
+    _, t_f = _timed(lambda: mod.forward_soft(rho, I, unary, ctx, ew, msg, el, ni, cost, uu, lab))
+    dun, dmsg, duu, dew = z(B, cv, H, W, L), z(D, B, cv, H, W, L), z(B, cv, H, W, L), z(D, B, cv, H, W)
+    dctx = torch.zeros_like(ctx)
+    _, t_b = _timed(lambda: mod.backward_soft(rho, dcost, ctx, ew, el, ni, dun, dctx, dew, dmsg, duu))
+    return dict(cost=cost, msg=msg, edge_label=el, norm_idx=ni, label_all=lab, dunary=dun, dcontext=dctx,
+                dedge=dew, t_fwd=t_f, t_bwd=t_b)
+
+
+@pytest.mark.parametrize("shape", [(1, 40, 56, 21, 4, 2, True), (2, 24, 31, 21, 8, 2, True),
+                                   (1, 30, 44, 12, 16, 1, False), (1, 128, 160, 21, 4, 3, True)],
+                         ids=lambda s: "-".join(map(str, s)))
+def test_soft_trwp(shape):
+    """Soft (expected-value) TRWP against the reference's TRWP_hard_soft extension: forward costs,
+    messages, saved edge values and normalisation indices bit-identical (same intrinsics and the
+    same reduction order); gradients to the gradient tolerance."""
+    _need("TRWP_hard_soft")
+    import mplayers_b200
+    B, H, W, L, D, I, rank2 = shape
+    unary, ctx, ew, dcost = _inputs(5, B, H, W, L, D, rank2)
+    assert ref_cuda.expressible(L, ctx.dim(), I, D, B * H * W * L)
+    ref_mod = ref_cuda._load("TRWP_hard_soft")
+    for _ in range(2):
+        ref = _run_soft(ref_mod, unary, ctx, ew, dcost, D, I, 0.5)
+        got = _run_soft(mplayers_b200.TRWP, unary, ctx, ew, dcost, D, I, 0.5)
+    for k in ("cost", "msg", "edge_label", "norm_idx", "label_all"):
+        a, b = got[k].cpu().numpy(), ref[k].cpu().numpy()
+        assert np.array_equal(a, b), "%s differs from the reference CUDA kernels (%d entries)" % (k, (a != b).sum())
+    for k in ("dunary", "dcontext", "dedge"):
+        err = rel_err(got[k].cpu().numpy(), ref[k].cpu().numpy())
+        assert err < GRAD_RTOL, (k, err)
+    print("\n[vs reference CUDA] soft TRWP B%d %dx%d L%d D%d I%d: forward %.3f ms (reference CUDA %.3f ms), "
+          "backward %.3f ms (reference CUDA %.3f ms)" % (B, H, W, L, D, I, got["t_fwd"], ref["t_fwd"],
+                                                          got["t_bwd"], ref["t_bwd"]))
