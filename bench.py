@@ -35,6 +35,10 @@ WORKLOADS = {
     "large_isgmr_train": ("config5_large", {}, True),
     "config1_trwp_train": ("config1", {"mode": "TRWP"}, True),
     "config1_isgmr_train": ("config1", {"mode": "ISGMR"}, True),
+    # soft (expected-value) TRWP on the segmentation inputs: saves L*L edge values per pixel, direction and
+    # iteration (18.5 GB per step at full size); the 256 x 256 copy is the one small enough to profile
+    "seg_trwp_soft_train": ("config4_segmentation", {"soft": True}, True),
+    "seg_trwp_soft_train_256": ("config4_segmentation", {"soft": True, "H": 256, "W": 256, "n_iter": 2}, True),
     # reduced copy of large_isgmr_train (same labels / directions) that is small enough to profile
     "large_isgmr_train_384": ("config5_large", {"H": 384, "W": 384, "n_iter": 4}, True),
 }
@@ -127,6 +131,11 @@ def algorithmic_bytes(cfg, batch, kind):
     _, _, L, H, W = cfg["unary"].shape
     D = cfg["n_dir"]
     n = batch * H * W
+    if cfg.get("soft"):
+        # soft TRWP additionally writes (forward, training) / reads (backward) the L*L edge values
+        if kind == "fwd":
+            return n * (4 * L * (D + 2) + 4 + (4 * L * L + 1 if cfg["training"] else 0))
+        return n * (4 * L * (2 * D + 3) + 4 * L * L + 9)
     if kind == "fwd":
         per_dir = n * (4 * L * (D + 2) + 4 + ((L + 1) if cfg["training"] else 0))
         return per_dir * (D if cfg["mode"] == "ISGMR" else 1)
@@ -137,6 +146,8 @@ def dominant_kernel(cfg, kind):
     """Name of the sweep kernel the workload spends its time in (see mplayers_b200/csrc)."""
     L = cfg["unary"].shape[2]
     pair = 32 < L <= 64 and L % 4 == 0
+    if cfg.get("soft"):
+        return "bwd_soft_kernel" if kind == "bwd" else "fwd_warp_kernel<soft>"
     if kind == "bwd":
         if L <= 32:
             return "bwd_tma_kernel" if cfg["mode"] == "TRWP" else "bwd_warp_kernel"
@@ -192,13 +203,20 @@ def run_ours(a):
 
     gen_name, kw, train = WORKLOADS[a.workload]
     kw = dict(kw)
+    soft = bool(kw.pop("soft", False))
     by_dir = a.shard == "directions"
     if gen_name in ("config4_segmentation", "config5_large", "config1") and not by_dir:
         kw["seed"] = rank  # every rank owns its own slice of the global batch
     cfg = getattr(synthetic, gen_name)(**kw)
     batch = cfg["unary"].shape[0]
+    cfg["soft"] = soft
     args = synthetic.make_args(cfg)
-    layer = MPModule(args)
+    if soft:
+        from mplayers_b200.MP_module_hard_soft import MPModule as SoftModule
+        args.mpnet_enable_soft = True
+        layer = SoftModule(args)
+    else:
+        layer = MPModule(args)
     if by_dir:
         if cfg["mode"] != "ISGMR":
             raise SystemExit("--shard directions needs an ISGMR workload (TRWP directions are sequential)")
@@ -220,7 +238,11 @@ def run_ours(a):
 
     from mplayers_b200 import ISGMRFunction, TRWPFunction
     fn = TRWPFunction if cfg["mode"] == "TRWP" else ISGMRFunction
+    if soft:
+        from mplayers_b200.MP_module_hard_soft import TRWPSoftFunction
+        fn = TRWPSoftFunction
     args.training = train
+    args.enable_saving_label = False
 
     from mplayers_b200 import parallel
 
@@ -237,7 +259,7 @@ def run_ours(a):
             if by_dir:
                 cost = direction_sharding.isgmr_direction_sharded(u, ctx_param, e, args, comm=dcomm)
             else:
-                cost, _ = fn.apply(u, ctx_param, e, args)
+                cost = fn.apply(u, ctx_param, e, args)[0]
             cost.backward(g_hwl)
             reduce_context_grad()
             return cost
@@ -393,8 +415,11 @@ def _cpu_sample(workload, edge):
     import numpy as np
     from mplayers_b200 import synthetic
     gen_name, kw, train = WORKLOADS[workload]
+    kw = dict(kw)
+    soft = bool(kw.pop("soft", False))
     if workload not in _CFG_CACHE:
         _CFG_CACHE[workload] = getattr(synthetic, gen_name)(**kw)
+        _CFG_CACHE[workload]["soft"] = soft
     cfg = _CFG_CACHE[workload]
     u = cfg["unary"][:1]
     _, _, L, H, W = u.shape
@@ -414,6 +439,13 @@ def _time_cpu(workload, edge, use_reference=True):
     import numpy as np
     from oracle import oracle, ref_cpu
     cfg, train, u, ctx, e = _cpu_sample(workload, edge)
+    if cfg.get("soft"):  # the reference has no CPU implementation of the soft variant: C port
+        t0 = time.perf_counter()
+        fwd = oracle.forward_soft(u, ctx, e, cfg["n_dir"], cfg["n_iter"], training=train)
+        g = np.random.default_rng(0).uniform(0, 1, size=u.shape).astype(np.float32)
+        if train:
+            oracle.backward_soft(ctx, e, g, fwd["edge_label"], fwd["norm_idx"])
+        return u.shape[2] * u.shape[3] * u.shape[4] * cfg["n_iter"], time.perf_counter() - t0, False
     use_ref = use_reference and ref_cpu.available()
     fwd = None
     if use_ref:

