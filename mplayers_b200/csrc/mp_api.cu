@@ -611,6 +611,7 @@ int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const flo
   for (int it = p->n_iter - 1; it >= 0; --it) {
     bp.norm_idx = msg_norm_index + (long long)it * D * d.npix;
     bp.edge_label = msg_edge_label + (long long)it * D * d.npix * L * L;
+    bp.edge_label_end = msg_edge_label + (long long)p->n_iter * D * d.npix * L * L;
     for (int dir = D - 1; dir >= 0; --dir) {
       bp.dir = dir;
       MPL_CUDA(mpl::launch_backward_soft_sweep(bp, st));

@@ -878,9 +878,14 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
 // ------------------------------------------------------------------------------------------------
 constexpr int kSoftPF = 4;  // pixels staged ahead (power of two)
 
+__host__ __device__ inline int bwd_soft_slot_floats(int L) {
+  // L*L edge values copied as the 16-byte aligned superset of their (4-byte aligned) tile: up to 3
+  // floats of slack in front, rounded up to 16 bytes; then the C and P_dir rows (32 floats each)
+  return ((L * L + 6) & ~3) + 64;
+}
 __host__ __device__ inline int bwd_soft_warp_floats(int L) {
-  // ring of kSoftPF slots: L*L edge values + C + P_dir (32 each) ; transpose tile [32][33]
-  return kSoftPF * (((L * L + 3) & ~3) + 64) + 32 * 33;
+  // ring of kSoftPF slots, transpose tile [32][33], kSoftPF mbarriers (2 floats each)
+  return kSoftPF * bwd_soft_slot_floats(L) + 32 * 33 + 3 + 2 * kSoftPF;
 }
 
 template <int LMAX>
@@ -891,9 +896,16 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
   BChain ch;
   if (!decode_bchain(p, g, ch)) return;
   const int L = p.L, dir = ch.dir, inv = dir ^ 1;
-  const int n2 = L * L, slot_floats = ((n2 + 3) & ~3) + 64;
-  float* ring = smem + warp * bwd_soft_warp_floats(L);   // [kSoftPF][slot_floats]
+  const int n2 = L * L, slot_floats = bwd_soft_slot_floats(L);
+  float* ring = smem + warp * ((bwd_soft_warp_floats(L) + 3) & ~3);   // [kSoftPF][slot_floats]
   float* tile = ring + kSoftPF * slot_floats;            // [32][33]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(
+      ring + kSoftPF * slot_floats + ((32 * 33 + 1) & ~1));
+  if (lane == 0) {
+    for (int i = 0; i < kSoftPF; ++i) mbar_init(&full[i], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
   const bool act = lane < L;
   const int lc = act ? lane : L - 1;
   const bool l2r = (dir & 1) == 0;
@@ -916,16 +928,37 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
   const int pixl = ch.h0 * p.W + ch.w0 + (len - 1) * pstep;  // last pixel of the chain
   const float rho = p.rho;
 
-  // Staging of step s (pixel pixl - s*pstep): its L*L edge values as a flat, coalesced copy, and its
-  // C and P_dir rows; 4-byte cp.async, one commit group per step, kSoftPF steps ahead.  Nothing in
-  // the step loop loads from global memory into a register except the per-block scalars.
+  // Staging of step s (pixel pixl - s*pstep), kSoftPF steps ahead: its L*L edge values by ONE bulk
+  // copy of the 16-byte aligned superset of the tile (the tile itself is only 4-byte aligned; the
+  // consumer skips the slack), completion on the warp's own mbarrier; its C and P_dir rows by
+  // 4-byte cp.async.  Nothing in the step loop loads from global memory into a register except the
+  // per-block scalars.  A superset that would reach past the end of the saved tensor (the very
+  // last pixel) is copied element by element instead.
+  auto tile_src = [&](int s, unsigned& off_floats, unsigned& bytes, bool& bulk) -> const float* {
+    const float* src = EL + (long long)(pixl - s * pstep) * n2;
+    const uintptr_t a = reinterpret_cast<uintptr_t>(src);
+    off_floats = (unsigned)(a & 15) >> 2;
+    bytes = (unsigned)((off_floats + n2) * 4 + 15) & ~15u;
+    const float* al = src - off_floats;
+    bulk = reinterpret_cast<uintptr_t>(al) + bytes <= reinterpret_cast<uintptr_t>(p.edge_label_end);
+    return bulk ? al : src;
+  };
   auto issue = [&](int s) {
     if (s < len) {
       const int pxs = pixl - s * pstep;
-      float* dst = ring + (s & (kSoftPF - 1)) * slot_floats;
+      const int slot = s & (kSoftPF - 1);
+      float* dst = ring + slot * slot_floats;
       if (s < len - 1) {
-        const float* src = EL + (long long)pxs * n2;
-        for (int i = lane; i < n2; i += 32) cp_async4(dst + i, src + i);
+        unsigned off, bytes;
+        bool bulk;
+        const float* src = tile_src(s, off, bytes, bulk);
+        if (lane == 0) {
+          fence_proxy_async_smem();
+          mbar_arrive_expect_tx(&full[slot], bulk ? bytes : 0u);
+          if (bulk) bulk_g2s(dst, src, bytes, &full[slot]);
+        }
+        if (!bulk)
+          for (int i = lane; i < n2; i += 32) cp_async4(dst + i, src + i);
       }
       if (act) {
         cp_async4(dst + slot_floats - 64 + lane, C + pxs * L);
@@ -961,8 +994,19 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
       load_blk((s >> 5) + 1, e_nxt, n_nxt);
     }
     cp_async_wait<kSoftPF - 1>();
-    __syncwarp();
     const float* sl = ring + (s & (kSoftPF - 1)) * slot_floats;
+    const float* ev = sl;   // edge values of this pixel inside the slot
+    if (s < len - 1) {
+      unsigned off, bytes;
+      bool bulk;
+      tile_src(s, off, bytes, bulk);
+      if (!mbar_wait(&full[s & (kSoftPF - 1)], (s / kSoftPF) & 1)) {
+        if (lane == 0) atomicExch(p.status, 151);
+        return;
+      }
+      ev = sl + (bulk ? off : 0u);
+    }
+    __syncwarp();
     const int of = px * L;
     const float c_old = sl[slot_floats - 64 + lc];
     const float x0 = c_old + sl[slot_floats - 32 + lc];   // C + P_dir of this pixel
@@ -973,7 +1017,7 @@ __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant_
       const int n = __shfl_sync(0xffffffffu, n_cur, s & 31);
       float d[LMAX];
 #pragma unroll
-      for (int f = 0; f < LMAX; ++f) d[f] = (f < L) ? (l2r ? sl[f * L + lc] : sl[lc * L + f]) : kInf;
+      for (int f = 0; f < LMAX; ++f) d[f] = (f < L) ? (l2r ? ev[f * L + lc] : ev[lc * L + f]) : kInf;
       float t = act ? x0 + rq : 0.f;
       const float S = warp_sum(t);
       t = (lane == n) ? t - S : t;
@@ -1476,7 +1520,7 @@ cudaError_t launch_backward_soft_sweep(const BwdParams& p0, cudaStream_t st) {
   if (total == 0) return cudaSuccess;
   if (p.L > 32 || p.cp_scheme != 1) return cudaErrorNotSupported;
   const int wpb = 4;
-  const size_t smem = (size_t)wpb * bwd_soft_warp_floats(p.L) * sizeof(float);
+  const size_t smem = (size_t)wpb * ((bwd_soft_warp_floats(p.L) + 3) & ~3) * sizeof(float);
   auto go = [&](auto kernel) -> cudaError_t {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -111,6 +111,7 @@ struct BwdParams {
   const float* ctx;
   const float* ew;        // or nullptr (= 1)
   const float* edge_label; // soft TRWP: [D,nimg,H,W,L,L] edge values saved by the forward, else nullptr
+  const float* edge_label_end;  // one past the last element of the whole saved tensor (all iterations)
   const uint8_t* min_idx; // [D,nimg,H,W,L] of this iteration
   const uint8_t* norm_idx; // [D,nimg,H,W]
   float* dm_read;         // [D,...]: slice `dir` holds the gradient of this sweep's messages; zeroed here

@@ -243,6 +243,14 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
   uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
   float* EL = (TRAIN && SOFT) ? p.edge_label + ((long long)ch.dir * p.pslice + ibase) * L * L : nullptr;
   const bool l2r = (ch.dir & 1) == 0;  // layout of the saved edge values
+  // flat element lane + 32k of a pixel's [c][f] table -> its place in the padded shared tile
+  constexpr int kFlat = SOFT ? (LMAX * LMAX + 31) / 32 : 1;
+  int toff[kFlat];
+#pragma unroll
+  for (int k = 0; k < kFlat; ++k) {
+    const int i = lane + 32 * k, c = i / L;
+    toff[k] = c * 33 + (i - c * L);
+  }
   const int len = ch.len;
   const int ostep = ch.pstep * L;
   const int dir_row = (1 + ch.dir) * 32, inv_row = (1 + ch.inv) * 32;
@@ -316,10 +324,9 @@ __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant_
           }
           __syncwarp();
           const int n2 = L * L;
-          for (int i = lane; i < n2; i += 32) {
-            const int c = i / L;
-            el[i] = tile[c * 33 + (i - c * L)];
-          }
+#pragma unroll
+          for (int k = 0; k < kFlat; ++k)
+            if (lane + 32 * k < n2) el[lane + 32 * k] = tile[toff[k]];
         }
       }
     } else {
