@@ -888,14 +888,14 @@ __host__ __device__ inline int bwd_soft_warp_floats(int L) {
   return kSoftPF * bwd_soft_slot_floats(L) + 32 * 33 + 3 + 2 * kSoftPF;
 }
 
-template <int LMAX>
+template <int LMAX, bool EXACT>  // EXACT: L == LMAX, every "f < L" test folds away
 __global__ void __launch_bounds__(128, 1) bwd_soft_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.x * wpb + warp;
   BChain ch;
   if (!decode_bchain(p, g, ch)) return;
-  const int L = p.L, dir = ch.dir, inv = dir ^ 1;
+  const int L = EXACT ? LMAX : p.L, dir = ch.dir, inv = dir ^ 1;
   const int n2 = L * L, slot_floats = bwd_soft_slot_floats(L);
   float* ring = smem + warp * ((bwd_soft_warp_floats(L) + 3) & ~3);   // [kSoftPF][slot_floats]
   float* tile = ring + kSoftPF * slot_floats;            // [32][33]
@@ -1530,7 +1530,8 @@ cudaError_t launch_backward_soft_sweep(const BwdParams& p0, cudaStream_t st) {
     return cudaSuccess;
   };
   ProfScope prof(kProfBwdSweep, st);
-  cudaError_t e = p.L <= 21 ? go(bwd_soft_kernel<21>) : go(bwd_soft_kernel<32>);
+  cudaError_t e = p.L == 21 ? go(bwd_soft_kernel<21, true>)
+                  : p.L < 21 ? go(bwd_soft_kernel<21, false>) : go(bwd_soft_kernel<32, false>);
   if (e != cudaSuccess) return e;
   count_launch();
   return cudaGetLastError();

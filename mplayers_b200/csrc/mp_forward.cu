@@ -213,13 +213,14 @@ __device__ __forceinline__ float soft_regrow(const float* hb, const float (&cr)[
 // SOFT: the soft (expected-value) message instead of the minimum; in training it saves the L x L
 // edge values of every pixel (entry [f][c] for even directions, [c][f] for odd ones, as the
 // reference does, MPLayers/TRWP_hard_soft/TRWP_forward_soft.cu:50-59) and no argmin indices.
-template <int LMAX, int DT, bool TRAIN, bool SOFT = false>
+// EXACT: the label count equals LMAX (lets the compiler drop every "f < L" test; used by the soft path).
+template <int LMAX, int DT, bool TRAIN, bool SOFT = false, bool EXACT = false>
 __global__ void __launch_bounds__(128, 1) fwd_warp_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   ChainCtx ch;
   if (!decode_chain(p, blockIdx.x * wpb + warp, ch)) return;
-  const int L = p.L, D = p.agg ? 2 : (DT ? DT : p.D), rows = D + 2;  // D = staged message slices
+  const int L = EXACT ? LMAX : p.L, D = p.agg ? 2 : (DT ? DT : p.D), rows = D + 2;  // D = staged message slices
   const int slot_floats = rows * 32;
   float* ring = smem + warp * (kPF * slot_floats + 64 + (SOFT ? 32 * 33 : 0));
   float* hbuf = ring + kPF * slot_floats;
@@ -1396,15 +1397,15 @@ cudaError_t launch_warp(const FwdParams& p, cudaStream_t st) {
   return launch_warp_d<LMAX, 0, TRAIN>(p, st);
 }
 
-template <int LMAX, bool TRAIN>
+template <int LMAX, bool TRAIN, bool EXACT>
 cudaError_t launch_warp_soft(const FwdParams& p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int wpb = total >= 148 * 32 ? 4 : 1;
   const size_t smem = (size_t)wpb * (kPF * (p.D + 2) * 32 + 64 + 32 * 33) * sizeof(float);
-  cudaError_t e = ensure_smem(fwd_warp_kernel<LMAX, 0, TRAIN, true>, smem);
+  cudaError_t e = ensure_smem(fwd_warp_kernel<LMAX, 0, TRAIN, true, EXACT>, smem);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
-  fwd_warp_kernel<LMAX, 0, TRAIN, true><<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
+  fwd_warp_kernel<LMAX, 0, TRAIN, true, EXACT><<<(total + wpb - 1) / wpb, wpb * 32, smem, st>>>(p);
   count_launch();
   return cudaGetLastError();
 }
@@ -1836,8 +1837,9 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
 cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st) {
   if (p.chain_off[p.ndirs] == 0) return cudaSuccess;
   if (p.L > 32) return cudaErrorNotSupported;
-  if (p.L <= 21) return train ? launch_warp_soft<21, true>(p, st) : launch_warp_soft<21, false>(p, st);
-  return train ? launch_warp_soft<32, true>(p, st) : launch_warp_soft<32, false>(p, st);
+  if (p.L == 21) return train ? launch_warp_soft<21, true, true>(p, st) : launch_warp_soft<21, false, true>(p, st);
+  if (p.L < 21) return train ? launch_warp_soft<21, true, false>(p, st) : launch_warp_soft<21, false, false>(p, st);
+  return train ? launch_warp_soft<32, true, false>(p, st) : launch_warp_soft<32, false, false>(p, st);
 }
 
 cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, uint8_t* label,
