@@ -316,19 +316,34 @@ def run_ours(a):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end: host buffers in, loss (and the context gradient) out ---------------------
+    # Every step copies its inputs from pinned host memory and reads its result back inside the
+    # timed region; the copy of step i + 1 runs on a side stream while step i computes
+    # (mplayers_b200.host_feed.HostFeeder), the read-back of step i is awaited one step later.
+    from mplayers_b200.host_feed import HostFeeder
+    feeder = HostFeeder([unary_host, ew_host], dev)
+    host_in = [unary_host, ew_host]
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     d2h = 0
-    for _ in range(a.steps):
-        u = unary_host.to(dev, non_blocking=True)
-        e = ew_host.to(dev, non_blocking=True) if ew_host is not None else None
+    outs = []
+    feeder.prefetch(host_in)
+    for i in range(a.steps):
+        u, e = feeder.get()
+        if i + 1 < a.steps:
+            feeder.prefetch(host_in)
         loss = step(u, e)
-        out = loss.detach().cpu()
+        feeder.release()
+        out = torch.empty(loss.shape, dtype=loss.dtype, pin_memory=True)
+        out.copy_(loss.detach(), non_blocking=True)
         d2h = out.numel() * out.element_size()
         if train:
-            gh = ctx_param.grad.cpu()
+            gh = torch.empty(ctx_param.grad.shape, dtype=ctx_param.grad.dtype, pin_memory=True)
+            gh.copy_(ctx_param.grad, non_blocking=True)
             d2h += gh.numel() * gh.element_size()
+            outs.append((out, gh))
+        else:
+            outs.append((out,))
     e1.record()
     sync_all()
     ms_e2e = e0.elapsed_time(e1)
