@@ -182,6 +182,17 @@ int mpl_isgmr_backward_combine(const mpl_problem* p, int32_t dir_first, int32_t 
 int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t workspace_bytes,
                                 float* dcontext, void* stream);
 
+/* Energy of labellings on the MRF the layers minimise, for energy-versus-iteration curves from the
+ * per-iteration labels `label_all` of a forward call.  energy [n_labelings, 2] (f64, device):
+ * {sum_p U[p, x_p], sum over undirected edges (p - step_d, p), d even, of E_d[p] * ctx(x_p, x_front)}.
+ * For 4 directions this is what the reference's evaluation script computes from the saved
+ * labellings (tools/matlab/MRF/calEnergy.m:23-46: right and down links); the reference has no GPU
+ * counterpart.  labels [n_labelings, B, cv, H, W] u8; workspace of mpl_energy_workspace_bytes(p). */
+size_t mpl_energy_workspace_bytes(const mpl_problem* p);
+int mpl_labeling_energy(const mpl_problem* p, const float* unary, const float* context,
+                        const float* edge_weights, const uint8_t* labels, int32_t n_labelings,
+                        double* energy, void* workspace, size_t workspace_bytes, void* stream);
+
 /* TRWP backward without any device allocation.  It has no counterpart in the reference.
  *
  * Same computation and arguments as mpl_trwp_backward, minus the workspace: the scratch (partial

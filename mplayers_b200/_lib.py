@@ -62,6 +62,10 @@ def lib():
         L.mpl_trwp_soft_forward.argtypes = [pp] + [vp] * 9 + [sz, vp]
         L.mpl_trwp_soft_backward.restype = ctypes.c_int
         L.mpl_trwp_soft_backward.argtypes = [pp] + [vp] * 10 + [sz, vp]
+        L.mpl_energy_workspace_bytes.restype = sz
+        L.mpl_energy_workspace_bytes.argtypes = [pp]
+        L.mpl_labeling_energy.restype = ctypes.c_int
+        L.mpl_labeling_energy.argtypes = [pp] + [vp] * 4 + [ctypes.c_int32, vp, vp, sz, vp]
         L.mpl_trwp_backward_static.restype = ctypes.c_int
         L.mpl_trwp_backward_static.argtypes = [pp] + [vp] * 10
         L.mpl_static_scratch_bytes.restype = sz

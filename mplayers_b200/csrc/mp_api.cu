@@ -621,6 +621,30 @@ int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const flo
   return MPL_OK;
 }
 
+// ---- energy of labellings (evaluation of the minimisation, not part of the layer) -----------------
+size_t mpl_energy_workspace_bytes(const mpl_problem* p) {
+  Dims d;
+  if (validate(p, &d) != MPL_OK) return 256;
+  return (size_t)((d.npix + 255) / 256) * 2 * sizeof(double) + 256;
+}
+
+int mpl_labeling_energy(const mpl_problem* p, const float* unary, const float* context,
+                        const float* edge_weights, const uint8_t* labels, int32_t n_labelings,
+                        double* energy, void* workspace, size_t workspace_bytes, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (!unary || !context || !labels || !energy || n_labelings < 0)
+    return fail(MPL_ERR_INVALID, "NULL tensor pointer or negative count");
+  if (!workspace || workspace_bytes < mpl_energy_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes, mpl_energy_workspace_bytes(p));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < n_labelings; ++i)
+    MPL_CUDA(mpl::launch_energy(unary, context, edge_weights, labels + (long long)i * d.npix, d.npix, p->height,
+                                p->width, p->n_disp, p->n_dir, p->context_rank, static_cast<double*>(workspace),
+                                energy + 2 * i, st));
+  return MPL_OK;
+}
+
 int mpl_forward_status(const void* workspace, int32_t* status) {
   if (!workspace || !status) return fail(MPL_ERR_INVALID, "NULL pointer");
   MPL_CUDA(cudaMemcpy(status, static_cast<const char*>(workspace) + 64, sizeof(int32_t), cudaMemcpyDeviceToHost));

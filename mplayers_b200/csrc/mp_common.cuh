@@ -288,6 +288,9 @@ cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, flo
                                        int dir0, int ndirs, float rho, cudaStream_t st);
 cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st);
 cudaError_t launch_backward_soft_sweep(const BwdParams& p, cudaStream_t st);
+cudaError_t launch_energy(const float* unary, const float* ctx, const float* ew, const uint8_t* label,
+                          long long npix, int H, int W, int L, int D, int rank, double* part, double* out,
+                          cudaStream_t st);
 cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n, float* out,
                               cudaStream_t st);
 cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long long n, int D, float rho,

@@ -1842,6 +1842,66 @@ cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream
   return train ? launch_warp_soft<32, true, false>(p, st) : launch_warp_soft<32, false, false>(p, st);
 }
 
+// Energy of a labelling x on the grid MRF the layers minimise: sum_p U[p, x_p] (out[0]) and
+// sum over the undirected edges (p - step_d, p), d even, of E_d[p] * ctx(x_p, x_{p - step_d})
+// (out[1]); what the reference's evaluation script computes for the 4-connected case
+// (tools/matlab/MRF/calEnergy.m:23-46, right and down links).  One block per 256 pixels writes its
+// partial sums (fixed order inside the block), a second kernel adds the partials in order.
+__global__ void energy_partial_kernel(const float* __restrict__ unary, const float* __restrict__ ctx,
+                                      const float* __restrict__ ew, const uint8_t* __restrict__ label,
+                                      long long npix, int H, int W, int L, int D, int rank, double* part) {
+  __shared__ double su[256], sp[256];
+  const long long px = blockIdx.x * 256ll + threadIdx.x;
+  double eu = 0.0, ep = 0.0;
+  if (px < npix) {
+    const int x = label[px];
+    eu = unary[px * L + x];
+    const int w = (int)(px % W), h = (int)((px / W) % H);
+    for (int d = 0; d < D; d += 2) {
+      int hs, ws;
+      dir_step(d, hs, ws);
+      const int fh = h - hs, fw = w - ws;
+      if (fh < 0 || fh >= H || fw < 0 || fw >= W) continue;
+      const int xf = label[px - (long long)hs * W - ws];
+      const float e = ew ? ew[(long long)d * npix + px] : 1.f;
+      ep += (double)(e * ctx_value(ctx, rank, L, x, xf));
+    }
+  }
+  su[threadIdx.x] = eu;
+  sp[threadIdx.x] = ep;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      su[threadIdx.x] += su[threadIdx.x + o];
+      sp[threadIdx.x] += sp[threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    part[2 * blockIdx.x] = su[0];
+    part[2 * blockIdx.x + 1] = sp[0];
+  }
+}
+
+__global__ void energy_final_kernel(const double* __restrict__ part, int nblocks, double* out) {
+  if (threadIdx.x < 2) {
+    double s = 0.0;
+    for (int b = 0; b < nblocks; ++b) s += part[2 * b + threadIdx.x];
+    out[threadIdx.x] = s;
+  }
+}
+
+cudaError_t launch_energy(const float* unary, const float* ctx, const float* ew, const uint8_t* label,
+                          long long npix, int H, int W, int L, int D, int rank, double* part, double* out,
+                          cudaStream_t st) {
+  const int nblocks = (int)((npix + 255) / 256);
+  energy_partial_kernel<<<nblocks, 256, 0, st>>>(unary, ctx, ew, label, npix, H, W, L, D, rank, part);
+  count_launch();
+  energy_final_kernel<<<1, 32, 0, st>>>(part, nblocks, out);
+  count_launch();
+  return cudaGetLastError();
+}
+
 cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, uint8_t* label,
                              long long npix, int L, int D, long long slice, float factor,
                              int min_a_dir, cudaStream_t st) {
