@@ -182,6 +182,25 @@ int mpl_isgmr_backward_combine(const mpl_problem* p, int32_t dir_first, int32_t 
 int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t workspace_bytes,
                                 float* dcontext, void* stream);
 
+/* Layout glue around the layer.  Network code holds class scores as [B,L,H,W] planes; the layer
+ * takes costs [B,(cv=1),H,W,L].  The reference converts with six elementwise passes: costs = -scores,
+ * minus the per-pixel minimum, permute, layer, permute back, negate (mpnet.py:161-169,
+ * pytorch/MP_module.py:198,232).  Each of these is one pass, coalesced on both sides:
+ *   mpl_scores_to_costs            costs[b,p,l] = max_l scores[b,:,p] - scores[b,l,p]; argmax [B,H,W] u8
+ *                                  saved for the backward (lowest index among equal maxima)
+ *   mpl_scores_to_costs_backward   dscores[b,l,p] = -dcosts[b,p,l] + (l == argmax[b,p]) * sum_l dcosts[b,p,:]
+ *   mpl_negate_hwl_to_lhw          scores_out[b,l,p] = -cost_final[b,p,l]   (and its backward:)
+ *   mpl_negate_lhw_to_hwl          out[b,p,l] = -in[b,l,p] */
+int mpl_scores_to_costs(const float* scores, float* costs, uint8_t* argmax, int32_t batch,
+                        int32_t n_disp, int32_t height, int32_t width, void* stream);
+int mpl_scores_to_costs_backward(const float* dcosts, const uint8_t* argmax, float* dscores,
+                                 int32_t batch, int32_t n_disp, int32_t height, int32_t width,
+                                 void* stream);
+int mpl_negate_lhw_to_hwl(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                          int32_t width, void* stream);
+int mpl_negate_hwl_to_lhw(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                          int32_t width, void* stream);
+
 /* Energy of labellings on the MRF the layers minimise, for energy-versus-iteration curves from the
  * per-iteration labels `label_all` of a forward call.  energy [n_labelings, 2] (f64, device):
  * {sum_p U[p, x_p], sum over undirected edges (p - step_d, p), d even, of E_d[p] * ctx(x_p, x_front)}.

@@ -195,6 +195,18 @@ class MPModule(torch.nn.Module):
             label_context[self.label_context_diag_loc] = self.args.mpnet_diag_value
         return label_context
 
+    def forward_native(self, unary, edge_weights=None):
+        """The layer in the extension's own layouts, without the two permutes of forward():
+        unary [B,cv,H,W,L], edge_weights [D,B,cv,H,W] or None -> (cost_final [B,cv,H,W,L],
+        label_context).  Used by glue.mp_on_scores."""
+        label_context = self._transformed_label_context()
+        self.args.training = self.training
+        if self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'}:
+            cost_final, _ = ISGMRFunction.apply(unary, label_context, edge_weights, self.args)
+        else:
+            cost_final, _ = TRWPFunction.apply(unary, label_context, edge_weights, self.args)
+        return cost_final, label_context.unsqueeze(0)
+
     def forward(self, unary, edge_weights=None):
         # unary [B,cv,L,H,W]; edge_weights [B,D,H,W]
         unary = unary.permute(0, 1, 3, 4, 2).contiguous()

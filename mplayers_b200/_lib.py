@@ -62,6 +62,14 @@ def lib():
         L.mpl_trwp_soft_forward.argtypes = [pp] + [vp] * 9 + [sz, vp]
         L.mpl_trwp_soft_backward.restype = ctypes.c_int
         L.mpl_trwp_soft_backward.argtypes = [pp] + [vp] * 10 + [sz, vp]
+        L.mpl_scores_to_costs.restype = ctypes.c_int
+        L.mpl_scores_to_costs.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+        L.mpl_scores_to_costs_backward.restype = ctypes.c_int
+        L.mpl_scores_to_costs_backward.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+        L.mpl_negate_lhw_to_hwl.restype = ctypes.c_int
+        L.mpl_negate_lhw_to_hwl.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+        L.mpl_negate_hwl_to_lhw.restype = ctypes.c_int
+        L.mpl_negate_hwl_to_lhw.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.mpl_energy_workspace_bytes.restype = sz
         L.mpl_energy_workspace_bytes.argtypes = [pp]
         L.mpl_labeling_energy.restype = ctypes.c_int

@@ -621,6 +621,36 @@ int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const flo
   return MPL_OK;
 }
 
+// ---- layout glue: class scores [B,L,H,W] <-> costs [B,H,W,L] -------------------------------------
+namespace {
+int layout_call(int kind, const float* in, float* out, uint8_t* amax, int32_t batch, int32_t n_disp,
+                int32_t height, int32_t width, void* stream) {
+  if (!in || !out || ((kind == 1 || kind == 3) && !amax)) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if (batch < 1 || height < 1 || width < 1 || n_disp < 1 || n_disp > 256 || batch > 65535)
+    return fail(MPL_ERR_INVALID, "bad shape: batch=%d n_disp=%d height=%d width=%d", batch, n_disp, height, width);
+  MPL_CUDA(mpl::launch_layout(kind, in, out, amax, batch, n_disp, (long long)height * width,
+                              static_cast<cudaStream_t>(stream)));
+  return MPL_OK;
+}
+}  // namespace
+
+int mpl_scores_to_costs(const float* scores, float* costs, uint8_t* argmax, int32_t batch, int32_t n_disp,
+                        int32_t height, int32_t width, void* stream) {
+  return layout_call(1, scores, costs, argmax, batch, n_disp, height, width, stream);
+}
+int mpl_scores_to_costs_backward(const float* dcosts, const uint8_t* argmax, float* dscores, int32_t batch,
+                                 int32_t n_disp, int32_t height, int32_t width, void* stream) {
+  return layout_call(3, dcosts, dscores, const_cast<uint8_t*>(argmax), batch, n_disp, height, width, stream);
+}
+int mpl_negate_lhw_to_hwl(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                          int32_t width, void* stream) {
+  return layout_call(0, in, out, nullptr, batch, n_disp, height, width, stream);
+}
+int mpl_negate_hwl_to_lhw(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                          int32_t width, void* stream) {
+  return layout_call(2, in, out, nullptr, batch, n_disp, height, width, stream);
+}
+
 // ---- energy of labellings (evaluation of the minimisation, not part of the layer) -----------------
 size_t mpl_energy_workspace_bytes(const mpl_problem* p) {
   Dims d;

@@ -288,6 +288,8 @@ cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, flo
                                        int dir0, int ndirs, float rho, cudaStream_t st);
 cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st);
 cudaError_t launch_backward_soft_sweep(const BwdParams& p, cudaStream_t st);
+cudaError_t launch_layout(int kind, const float* in, float* out, uint8_t* amax, int B, int L, long long HW,
+                          cudaStream_t st);
 cudaError_t launch_energy(const float* unary, const float* ctx, const float* ew, const uint8_t* label,
                           long long npix, int H, int W, int L, int D, int rank, double* part, double* out,
                           cudaStream_t st);

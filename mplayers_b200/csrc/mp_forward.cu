@@ -1842,6 +1842,90 @@ cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream
   return train ? launch_warp_soft<32, true, false>(p, st) : launch_warp_soft<32, false, false>(p, st);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Layout glue around the layer: network code holds class scores as [B,L,H,W] planes, the layer wants
+// costs [B,H,W,L] with the labels innermost.  The reference does score -> cost (negate, subtract
+// the per-pixel minimum), permute, layer, permute, negate as six elementwise passes
+// (mpnet.py:161-169, pytorch/MP_module.py:198,232); here each side is one pass through a
+// shared-memory tile of 32 pixels x L labels, coalesced on both ends.
+//   MODE 0: out = -in            MODE 1: out = max_l(in) - in, argmax saved (lowest index on ties)
+//   MODE 2 (backward of 1, direction hwl -> lhw): out[l] = -in[l] + (l == argmax) * sum_l in[l]
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void lhw_to_hwl_kernel(const float* __restrict__ in, float* __restrict__ out, uint8_t* __restrict__ amax,
+                                  int L, long long HW) {
+  extern __shared__ float tile[];  // [L][33]
+  __shared__ float mx[32];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const long long b = blockIdx.y, p0 = blockIdx.x * 32ll;
+  const float* src = in + b * L * HW;
+  const int np = HW - p0 < 32 ? (int)(HW - p0) : 32;
+  for (int l = ty; l < L; l += 8) tile[l * 33 + tx] = tx < np ? src[(long long)l * HW + p0 + tx] : 0.f;
+  __syncthreads();
+  if (MODE == 1) {
+    if (ty == 0) {
+      float m = tile[tx];
+      int k = 0;
+      for (int l = 1; l < L; ++l) {
+        const float v = tile[l * 33 + tx];
+        if (v > m) m = v, k = l;
+      }
+      mx[tx] = m;
+      if (tx < np) amax[b * HW + p0 + tx] = (uint8_t)k;
+    }
+    __syncthreads();
+  }
+  float* dst = out + (b * HW + p0) * L;
+  for (int i = threadIdx.x; i < np * L; i += 256) {
+    const int px = i / L, l = i - px * L;
+    const float v = tile[l * 33 + px];
+    dst[i] = MODE == 1 ? mx[px] - v : -v;
+  }
+}
+
+template <int MODE>
+__global__ void hwl_to_lhw_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                  const uint8_t* __restrict__ amax, int L, long long HW) {
+  extern __shared__ float tile[];  // [L][33]
+  __shared__ float sm[32];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long b = blockIdx.y, p0 = blockIdx.x * 32ll;
+  const int np = HW - p0 < 32 ? (int)(HW - p0) : 32;
+  const float* src = in + (b * HW + p0) * L;
+  for (int i = threadIdx.x; i < np * L; i += 256) {
+    const int px = i / L, l = i - px * L;
+    tile[l * 33 + px] = src[i];
+  }
+  __syncthreads();
+  if (MODE == 2) {
+    if (ty == 0 && tx < np) {
+      float s = 0.f;
+      for (int l = 0; l < L; ++l) s += tile[l * 33 + tx];
+      sm[tx] = s;
+    }
+    __syncthreads();
+  }
+  float* dst = out + b * L * HW;
+  const int k = (MODE == 2 && tx < np) ? (int)amax[b * HW + p0 + tx] : -1;
+  for (int l = ty; l < L; l += 8)
+    if (tx < np) dst[(long long)l * HW + p0 + tx] = -tile[l * 33 + tx] + ((MODE == 2 && l == k) ? sm[tx] : 0.f);
+}
+
+cudaError_t launch_layout(int kind, const float* in, float* out, uint8_t* amax, int B, int L, long long HW,
+                          cudaStream_t st) {
+  const dim3 grid((unsigned)((HW + 31) / 32), (unsigned)B);
+  const size_t smem = (size_t)L * 33 * sizeof(float);
+  ProfScope prof(kProfElementwise, st);
+  switch (kind) {
+    case 0: lhw_to_hwl_kernel<0><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
+    case 1: lhw_to_hwl_kernel<1><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
+    case 2: hwl_to_lhw_kernel<0><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
+    default: hwl_to_lhw_kernel<2><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
 // Energy of a labelling x on the grid MRF the layers minimise: sum_p U[p, x_p] (out[0]) and
 // sum over the undirected edges (p - step_d, p), d even, of E_d[p] * ctx(x_p, x_{p - step_d})
 // (out[1]); what the reference's evaluation script computes for the 4-connected case
