@@ -35,6 +35,9 @@ WORKLOADS = {
     "large_isgmr_train": ("config5_large", {}, True),
     "config1_trwp_train": ("config1", {"mode": "TRWP"}, True),
     "config1_isgmr_train": ("config1", {"mode": "ISGMR"}, True),
+    # the segmentation inputs run through ISGMR instead of TRWP (21 labels: the per-direction launches of an
+    # iteration run side by side)
+    "seg_isgmr_train": ("config4_segmentation", {"mode": "ISGMR"}, True),
     # soft (expected-value) TRWP on the segmentation inputs: saves L*L edge values per pixel, direction and
     # iteration (18.5 GB per step at full size); the 256 x 256 copy is the one small enough to profile
     "seg_trwp_soft_train": ("config4_segmentation", {"soft": True}, True),

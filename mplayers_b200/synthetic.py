@@ -110,7 +110,7 @@ def config3_denoise(seed=0, H=256, W=256, L=256, n_iter=50):
                 unary=unary.view(1, 1, L, H, W).contiguous(), label_context=ctx, edge_weights=None)
 
 
-def config4_segmentation(batch=2, seed=0, H=512, W=512, L=21, n_dir=4, n_iter=5):
+def config4_segmentation(batch=2, seed=0, H=512, W=512, L=21, n_dir=4, n_iter=5, mode="TRWP"):
     """Segmentation training step (TRWP fwd+bwd): DeepLab-like logits N(0,1) + 3 on a blob class
     map, turned into non-negative costs as mpnet.py:162-163 does; learned dense 21x21 context
     U[0,2] with zero diagonal; edge weights exp(-|grad I|^2 / 2 sigma^2), sigma = 0.1."""
@@ -125,7 +125,7 @@ def config4_segmentation(batch=2, seed=0, H=512, W=512, L=21, n_dir=4, n_iter=5)
     ctx = a + a.t()
     img = _smooth_noise(g, batch, 3, H, W, sigma=4.0)
     ew = edge_weights_from_image(img, n_dir, sigma=0.1)
-    return dict(mode="TRWP", n_dir=n_dir, n_iter=n_iter, training=True,
+    return dict(mode=mode, n_dir=n_dir, n_iter=n_iter, training=True,
                 unary=cost.unsqueeze(1).contiguous(), label_context=ctx, edge_weights=ew)
 
 
