@@ -334,7 +334,9 @@ __host__ __device__ inline int bwd_tma_warp_floats(int L, int rank) {
   return kBK * kDS + 128 + ((L * (L | 1) + 3) & ~3);
 }
 
-template <int LT, bool VERT, bool REV>
+// QM: scatter-field scheme (ISGMR): only the gradient slice of the direction is staged and only the
+// scatter field is stored.
+template <int LT, bool VERT, bool REV, bool QM = false>
 __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__ BwdParams p,
                                                          const __grid_constant__ TmaMaps maps) {
   // No static shared memory in this kernel: the dynamic region starts at the CTA's shared window
@@ -394,17 +396,18 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
       if (VERT) {
         // 2-D tiled TMA: one copy per array brings kBK image rows of the 4-pixel column group
         if (lane == 0) {
-          mbar_arrive_expect_tx(&full[slot], 2u * kBK * row_bytes);
+          mbar_arrive_expect_tx(&full[slot], (QM ? 1u : 2u) * kBK * row_bytes);
           const int y0 = img0 * H + (REV ? H - (s + 1) * kBK : s * kBK);
-          tma_load_2d(T, &maps.a, w0 * L, y0, &full[slot]);
+          if (!QM) tma_load_2d(T, &maps.a, w0 * L, y0, &full[slot]);
           tma_load_2d(T + kBK * 4 * L, &maps.b, w0 * L, dir * p.nimg * H + y0, &full[slot]);
         }
       } else {
-        if (lane == 0) mbar_arrive_expect_tx(&full[slot], (unsigned)nact * (unsigned)npix * 8u * L);
+        if (lane == 0) mbar_arrive_expect_tx(&full[slot], (unsigned)nact * (unsigned)npix * (QM ? 4u : 8u) * L);
         __syncwarp();
         const int ncopy = nact * 2;
         for (int c = lane; c < ncopy; c += 32) {
           const int qd = c >> 1, a = c & 1;
+          if (QM && a == 0) continue;
           const int wlo = REV ? W - s * kBK - npix : s * kBK;
           const long long pix = (long long)(chain0 + qd) * W + wlo;
           const float* src = (a == 0 ? p.dunary : p.dm_read + (long long)dir * p.slice) + pix * L;
@@ -436,9 +439,10 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
     fix = (chain0 + wc) - img * H;
   }
   const long long ibase = (long long)img * H * W;
-  float* Cl = p.dunary + ibase * L + lc;
+  float* Cl = QM ? nullptr : p.dunary + ibase * L + lc;
   float* Pdl = p.dm_read + (long long)dir * p.slice + ibase * L + lc;
   float* Pil = p.dm_read + (long long)inv * p.slice + ibase * L + lc;
+  float* Ql = p.dm_acc + (long long)dir * p.slice + ibase * L + lc;   // QM: scatter field of this direction
   const float* E = p.ew ? p.ew + (long long)dir * p.pslice + ibase : nullptr;
   float* DE = p.dew ? p.dew + (long long)dir * p.pslice + ibase : nullptr;
   const uint8_t* MIl = p.min_idx + (long long)dir * p.slice + ibase * L + lc;
@@ -486,7 +490,7 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
 
   // one step: t = tile pointer of this pixel (C at t[0], P_dir at t[sa]), k = step inside the stage
   auto step = [&](const float* t, int k, int f, float S_st, int px, bool has_front) {
-    const float cval = t[0];
+    const float cval = QM ? 0.f : t[0];
     const float rq = rho * q;
     float qn = 0.f;
     if (has_front) {
@@ -506,11 +510,15 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
       __syncwarp();
       qn = gather_q<LT>(tb, ib, L, mef);
     }
-    const float cnew = cval + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
     const int of = px * L;
-    Cl[of] = cnew;
-    Pdl[of] = -cnew;               // dM_dir = C + P_dir = 0 after its sweep
-    if (act) atomicAdd(Pil + of, -q);
+    if constexpr (QM) {
+      Ql[of] = q;
+    } else {
+      const float cnew = cval + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
+      Cl[of] = cnew;
+      Pdl[of] = -cnew;               // dM_dir = C + P_dir = 0 after its sweep
+      if (act) atomicAdd(Pil + of, -q);
+    }
     q = qn;
   };
 
@@ -536,9 +544,9 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
       const float* row = t0p + lane * sk;
       if constexpr (LT > 0) {
 #pragma unroll
-        for (int c = 0; c < LT; ++c) S_st += row[c] + row[sa + c];
+        for (int c = 0; c < LT; ++c) S_st += QM ? row[sa + c] : row[c] + row[sa + c];
       } else {
-        for (int c = 0; c < L; ++c) S_st += row[c] + row[sa + c];
+        for (int c = 0; c < L; ++c) S_st += QM ? row[sa + c] : row[c] + row[sa + c];
       }
     }
     const float* tl = t0p + lc;
@@ -1348,9 +1356,9 @@ size_t bwd_tma_smem_bytes(int L, int rank, int stages) {
 }
 
 bool bwd_tma_eligible(const BwdParams& p) {
-  if (p.cp_scheme != 1 || p.dir > 3 || p.L > 32) return false;
+  if (p.cp_scheme == 0 || p.dir > 3 || p.L > 32 || p.ndirs > 1) return false;
   if ((p.W & 3) || (((long long)p.W * p.L) & 3)) return false;
-  if (((uintptr_t)p.dunary | (uintptr_t)p.dm_read) & 15) return false;
+  if (((uintptr_t)(p.cp_scheme == 1 ? p.dunary : nullptr) | (uintptr_t)p.dm_read) & 15) return false;
   return true;
 }
 
@@ -1368,9 +1376,10 @@ cudaError_t launch_bwd_tma(const BwdParams& p, cudaStream_t st) {
   const int groups = vert ? p.nimg * (p.W >> 2) : (p.nimg * p.H + 3) >> 2;
   const size_t smem = bwd_tma_smem_bytes(p.L, p.ctx_rank, p.tma_stages);
   TmaMaps maps{};
+  const bool qm = p.cp_scheme == 2;
   if (vert) {
     const unsigned long long inner = (unsigned long long)p.W * p.L, rows = (unsigned long long)p.nimg * p.H;
-    if (!encode_tmap_2d(&maps.a, p.dunary, inner, rows, 4 * p.L, kBK) ||
+    if ((!qm && !encode_tmap_2d(&maps.a, p.dunary, inner, rows, 4 * p.L, kBK)) ||
         !encode_tmap_2d(&maps.b, p.dm_read, inner, rows * p.D, 4 * p.L, kBK))
       return cudaErrorNotSupported;
   }
@@ -1382,6 +1391,10 @@ cudaError_t launch_bwd_tma(const BwdParams& p, cudaStream_t st) {
     kernel<<<groups, 160, smem, st>>>(p, maps);
     return cudaSuccess;
   };
+  if (qm) {
+    if (vert) return rev ? go(bwd_tma_kernel<LT, true, true, true>) : go(bwd_tma_kernel<LT, true, false, true>);
+    return rev ? go(bwd_tma_kernel<LT, false, true, true>) : go(bwd_tma_kernel<LT, false, false, true>);
+  }
   if (vert) return rev ? go(bwd_tma_kernel<LT, true, true>) : go(bwd_tma_kernel<LT, true, false>);
   return rev ? go(bwd_tma_kernel<LT, false, true>) : go(bwd_tma_kernel<LT, false, false>);
 }
@@ -1445,6 +1458,24 @@ cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, l
 cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
   BwdParams p = p0;
   if (p.ndirs < 1) p.ndirs = 1;
+  if (p.cp_scheme == 2 && p.L <= 32 && p.ndirs > 1 && (long long)p.nimg * (p.H < p.W ? p.H : p.W) >= 256) {
+    // ISGMR, L <= 32: the axis directions whose rows are 16-byte aligned go to the bulk-copy kernel
+    // one by one (the sweeps are independent), the rest to one launch of the generic kernel.
+    // Small problems (few chains per direction) stay with one launch over all directions.
+    int d = p.dir;
+    const int end = p.dir + p.ndirs;
+    for (; d < end && d <= 3; ++d) {
+      BwdParams one = p;
+      one.dir = d;
+      one.ndirs = 1;
+      if (!bwd_tma_eligible(one)) break;
+      cudaError_t e = launch_backward_sweep(one, st);
+      if (e != cudaSuccess) return e;
+    }
+    if (d == end) return cudaSuccess;
+    p.ndirs = end - d;  // the remaining range continues below
+    p.dir = d;
+  }
   p.chain_off[0] = 0;
   for (int i = 0; i < p.ndirs; ++i)
     p.chain_off[i + 1] = p.chain_off[i] + make_geom(p.dir + i, p.H, p.W).n_chains * p.nimg;

@@ -1799,7 +1799,10 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
     // remaining contiguous range of directions to the generic kernel
     FwdParams rest = p;
     int first_generic = p.dir0;
-    for (int d = p.dir0; d < p.dir0 + p.ndirs; ++d) {
+    // several independent directions (ISGMR) of a small problem: one launch of the generic kernel
+    // over all of them beats one small launch per direction
+    const bool few_chains = p.ndirs > 1 && (long long)p.nimg * (p.H < p.W ? p.H : p.W) < 256;
+    for (int d = p.dir0; d < p.dir0 + p.ndirs && !few_chains; ++d) {
       int stages = 0;
       if (d != first_generic || !tma_eligible(p, d, &stages)) break;
       cudaError_t e = p.L == 21 ? (train ? launch_tma<21, 21, true>(p, d, stages, st) : launch_tma<21, 21, false>(p, d, stages, st))
