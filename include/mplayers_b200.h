@@ -242,6 +242,59 @@ int mpl_trwp_backward_static(const mpl_problem* p, const float* context, const f
  * reference, whose kernels never wait on anything. */
 int mpl_forward_status(const void* workspace, int32_t* status);
 
+/* Stand-alone soft-weighted message ops of the reference's TRWP_hard_soft extension
+ * (`soft_weighted_message`, `soft_weighted_message_back`: MPLayers/TRWP_hard_soft/TRWP.cpp:382-419,
+ * kernels TRWP_swbp.cu:135-245).  message [n_tables, n_disp(front), n_disp(current)]:
+ *   soft[t,c] = sum_f softmax_f(-message[t,:,c])[f] * message[t,f,c];  min_ind[t] = argmin_c soft[t,c]
+ *   (highest index among equal minima);  norm[t,c] = soft[t,c] - soft[t,min_ind[t]].
+ * The backward call writes dmessage [n_tables,n_disp,n_disp] = d norm / d message applied to
+ * dmessage_soft_sum_norm [n_tables,n_disp]. */
+int mpl_soft_weighted_message(const float* message, int64_t n_tables, int32_t n_disp,
+                              float* message_soft_sum_norm, uint8_t* message_soft_sum_min_ind, void* stream);
+int mpl_soft_weighted_message_backward(const float* dmessage_soft_sum_norm, const float* message,
+                                       const uint8_t* message_soft_sum_min_ind, int64_t n_tables,
+                                       int32_t n_disp, float* dmessage, void* stream);
+
+/* Builders of the layers' inputs.  The reference builds them on the host CPU
+ * (MPLayers/aux/aux.cpp, called through MPLayers/aux/auxPy.cpp:9-112) or with chains of torch
+ * slicing ops (utils/edge_weights.py); here each is one pass whose output is already in the layout
+ * the layers read.  Images are device buffers; reading image files stays with the caller.
+ *
+ * mpl_stereo_data_cost   computeDSI (aux.cpp:6-91): matching cost of left pixel x against right
+ *     pixel x - d for d in [0, n_disp), summed over min(3, channels) colours, either the
+ *     Birchfield-Tomasi sampling-insensitive difference (integer half-sample neighbours) or the
+ *     absolute difference, optionally squared, truncated at trunc_diffs (per colour when not
+ *     squared), and the truncation value where x - d < 0.  left/right: u8 [height,width,channels]
+ *     interleaved; data_cost: f32 [height,width,n_disp] = the layers' unary [1,1,H,W,L].  Values
+ *     are integers and identical to the reference's.
+ * mpl_gradient_cues      computeCues (aux.cpp:93-158): grad_penalty where the squared colour
+ *     difference to the right (h_cue) / lower (v_cue) neighbour is below channels*grad_thresh^2,
+ *     else 1.  compact = 0: both [height,width]; compact = 1: what the reference returns to Python
+ *     (auxPy.cpp:86-99), h_cue [height*(width-1)] row-major, v_cue [(height-1)*width] column-major.
+ * mpl_smoothness_context computeSmoothnessContext (aux.cpp:160-214): context [n_disp,n_disp] for
+ *     method "L", "Q", "TL", "TQ", "Cauchy" or "Huber" with truncation smoothness_max.
+ * mpl_edge_weights       getEdgeShift (utils/edge_weights.py:45-111): for each direction d the weight
+ *     of the edge (p - step_d, p) stored at p, 0 where p - step_d is outside; image f32
+ *     [batch,channels,height,width]; mode from mpl_edge_mode(name), the reference's edge_mode
+ *     strings plus "shifted" (its fall-through branch) and "cue_penalty"
+ *     (MPLayers/extra_exp_edge_weights.py:115-121).  Output [n_dir,batch,Cout,height,width] with
+ *     Cout = mpl_edge_mode_channels(mode, channels): 1 for the modes that reduce over channels
+ *     (superpixel_edge, kernel_cue_real, kernel_cue_binary, threshold, cue_penalty) -- the layers'
+ *     edge_weights [D,B,cv=1,H,W] -- else `channels`.  kernel_cue_binary needs a 128-byte workspace. */
+int mpl_stereo_data_cost(const uint8_t* left, const uint8_t* right, int32_t height, int32_t width,
+                         int32_t channels, int32_t n_disp, int32_t birchfield, int32_t squared_diffs,
+                         int32_t trunc_diffs, float* data_cost, void* stream);
+int mpl_gradient_cues(const uint8_t* image, int32_t height, int32_t width, int32_t channels,
+                      int32_t grad_thresh, int32_t grad_penalty, int32_t compact, float* h_cue, float* v_cue,
+                      void* stream);
+int mpl_smoothness_context(int32_t n_disp, const char* method, float smoothness_max, float* context,
+                           void* stream);
+int32_t mpl_edge_mode(const char* name);                       /* -1 for an unknown name */
+int32_t mpl_edge_mode_channels(int32_t mode, int32_t channels); /* -1 on bad arguments */
+int mpl_edge_weights(int32_t mode, const float* image, int32_t batch, int32_t channels, int32_t height,
+                     int32_t width, int32_t n_dir, float sigma, float threshold, float penalty,
+                     float* edge_weights, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Message of the last error on the calling thread ("" if none).  Replaces the reference's
  * printf-and-return error reporting (MPLayers/TRWP/TRWP.cpp:269-273,316). */
 const char* mpl_last_error(void);

@@ -113,3 +113,39 @@ def backward_soft(rho, dcost_final, context, edge_weights, msg_edge_label, msg_n
             ctypes.byref(prob), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(dcost_final),
             _lib.ptr(msg_edge_label), _lib.ptr(msg_norm_index), _lib.ptr(dunary), _lib.ptr(dcontext),
             _lib.ptr(dedge_weights), _lib.ptr(dmsg), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+
+
+def soft_weighted_message(message, message_soft_sum_norm, message_soft_sum_min_ind):
+    """TRWP_hard_soft.soft_weighted_message (MPLayers/TRWP_hard_soft/TRWP.cpp:382-397; call of
+    pytorch/unittest_mp.py:126).  message [T,L,L] (front, current); writes the normalised
+    soft-weighted column sums [T,L] and the index of each table's minimum [T,1] (uint8)."""
+    dev = message.device
+    _lib.require(message, "message", torch.float32, dev)
+    _lib.require(message_soft_sum_norm, "message_soft_sum_norm", torch.float32, dev)
+    _lib.require(message_soft_sum_min_ind, "message_soft_sum_min_ind", torch.uint8, dev)
+    if message.dim() != 3 or message.size(1) != message.size(2):
+        raise RuntimeError("message must be [T,L,L], got %s" % (tuple(message.shape),))
+    t, l = message.size(0), message.size(1)
+    if message_soft_sum_norm.numel() != t * l or message_soft_sum_min_ind.numel() != t:
+        raise RuntimeError("outputs must hold T*L values and T indices")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().mpl_soft_weighted_message(
+            _lib.ptr(message), t, l, _lib.ptr(message_soft_sum_norm), _lib.ptr(message_soft_sum_min_ind),
+            _lib.stream_ptr(dev)))
+
+
+def soft_weighted_message_back(dmessage_soft_sum_norm, message, message_soft_sum_min_ind, dmessage):
+    """TRWP_hard_soft.soft_weighted_message_back (TRWP.cpp:399-419): writes dmessage [T,L,L]."""
+    dev = message.device
+    for x, n in ((dmessage_soft_sum_norm, "dmessage_soft_sum_norm"), (message, "message"), (dmessage, "dmessage")):
+        _lib.require(x, n, torch.float32, dev)
+    _lib.require(message_soft_sum_min_ind, "message_soft_sum_min_ind", torch.uint8, dev)
+    if message.dim() != 3 or message.size(1) != message.size(2) or dmessage.shape != message.shape:
+        raise RuntimeError("message and dmessage must be [T,L,L]")
+    t, l = message.size(0), message.size(1)
+    if dmessage_soft_sum_norm.numel() != t * l or message_soft_sum_min_ind.numel() != t:
+        raise RuntimeError("dmessage_soft_sum_norm must hold T*L values and message_soft_sum_min_ind T indices")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().mpl_soft_weighted_message_backward(
+            _lib.ptr(dmessage_soft_sum_norm), _lib.ptr(message), _lib.ptr(message_soft_sum_min_ind), t, l,
+            _lib.ptr(dmessage), _lib.stream_ptr(dev)))

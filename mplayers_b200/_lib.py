@@ -74,6 +74,23 @@ def lib():
         L.mpl_energy_workspace_bytes.argtypes = [pp]
         L.mpl_labeling_energy.restype = ctypes.c_int
         L.mpl_labeling_energy.argtypes = [pp] + [vp] * 4 + [ctypes.c_int32, vp, vp, sz, vp]
+        f32 = ctypes.c_float
+        L.mpl_soft_weighted_message.restype = ctypes.c_int
+        L.mpl_soft_weighted_message.argtypes = [vp, ctypes.c_int64, i32, vp, vp, vp]
+        L.mpl_soft_weighted_message_backward.restype = ctypes.c_int
+        L.mpl_soft_weighted_message_backward.argtypes = [vp, vp, vp, ctypes.c_int64, i32, vp, vp]
+        L.mpl_stereo_data_cost.restype = ctypes.c_int
+        L.mpl_stereo_data_cost.argtypes = [vp, vp] + [i32] * 7 + [vp, vp]
+        L.mpl_gradient_cues.restype = ctypes.c_int
+        L.mpl_gradient_cues.argtypes = [vp] + [i32] * 6 + [vp, vp, vp]
+        L.mpl_smoothness_context.restype = ctypes.c_int
+        L.mpl_smoothness_context.argtypes = [i32, ctypes.c_char_p, f32, vp, vp]
+        L.mpl_edge_mode.restype = i32
+        L.mpl_edge_mode.argtypes = [ctypes.c_char_p]
+        L.mpl_edge_mode_channels.restype = i32
+        L.mpl_edge_mode_channels.argtypes = [i32, i32]
+        L.mpl_edge_weights.restype = ctypes.c_int
+        L.mpl_edge_weights.argtypes = [i32, vp] + [i32] * 5 + [f32] * 3 + [vp, vp, sz, vp]
         L.mpl_trwp_backward_static.restype = ctypes.c_int
         L.mpl_trwp_backward_static.argtypes = [pp] + [vp] * 10
         L.mpl_static_scratch_bytes.restype = sz

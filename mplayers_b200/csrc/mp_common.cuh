@@ -288,6 +288,20 @@ cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, flo
                                        int dir0, int ndirs, float rho, cudaStream_t st);
 cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st);
 cudaError_t launch_backward_soft_sweep(const BwdParams& p, cudaStream_t st);
+// Stand-alone soft-weighted message ops (mp_swbp.cu).
+cudaError_t launch_soft_weighted_message(const float* msg, long long n_tables, int L, float* norm,
+                                         uint8_t* min_ind, cudaStream_t st);
+cudaError_t launch_soft_weighted_message_back(const float* dnorm, const float* msg, const uint8_t* min_ind,
+                                              long long n_tables, int L, float* dmsg, cudaStream_t st);
+// Input builders (mp_terms.cu).
+cudaError_t launch_stereo_data_cost(const uint8_t* left, const uint8_t* right, int H, int W, int nB, int L,
+                                    int birchfield, int squared, int trunc, float* out, cudaStream_t st);
+cudaError_t launch_gradient_cues(const uint8_t* img, int H, int W, int nB, int grad_thresh, int grad_penalty,
+                                 int compact, float* hcue, float* vcue, cudaStream_t st);
+cudaError_t launch_smoothness_context(int L, int method, float smax, float* out, cudaStream_t st);
+bool edge_weights_reduces(int mode);
+cudaError_t launch_edge_weights(const float* img, int B, int C, int H, int W, int D, int mode, float sigma,
+                                float threshold, float penalty, float* out, double* sums, cudaStream_t st);
 cudaError_t launch_layout(int kind, const float* in, float* out, uint8_t* amax, int B, int L, long long HW,
                           cudaStream_t st);
 cudaError_t launch_energy(const float* unary, const float* ctx, const float* ew, const uint8_t* label,

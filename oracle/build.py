@@ -8,6 +8,9 @@
                                     #  implementation this library replaces, for side-by-side
                                     #  parity and timing on the same device)
 
+    python oracle/build.py --ref-terms  # additionally oracle/_ref/libref_terms.so (the reference's
+                                    #  stereo term builders, MPLayers/aux/aux.cpp, unmodified)
+
 The reference sources are only read, never copied; the `--ref` outputs go to `oracle/_ref/`,
 which is git-ignored.  `--ref` needs the reference checkout (path in $MPL_REFERENCE_DIR,
 default the directory mounted next to this repository) and is skipped when it is absent.
@@ -131,9 +134,38 @@ def build_reference_cuda(force=False, names=("TRWP", "ISGMR", "TRWP_hard_soft"))
     return out
 
 
+def build_reference_terms(force=False):
+    """Compile the reference's stereo term builders (MPLayers/aux/aux.cpp: computeDSI, computeCues,
+    computeSmoothnessContext) into oracle/_ref/libref_terms.so, with the macros of its own build
+    (USE_OPENCV, USE_FLOAT; MPLayers/setup.py:39-56).
+
+    aux.cpp is a template over the image container and only touches rows, cols, channels() and
+    ptr(y, x); OpenCV's C++ headers are not installed here, so the include path carries a stand-in
+    container with exactly those members (oracle/mat_standin/), and oracle/ref_terms_shim.cpp wraps
+    the three functions in C entry points.  The arithmetic compiled is the reference's, unmodified.
+    Returns the library path, or None if the reference is absent.
+    """
+    ref = reference_dir()
+    src = os.path.join(ref, "MPLayers", "aux", "aux.cpp")
+    if not os.path.exists(src):
+        return None
+    os.makedirs(REF_OUT, exist_ok=True)
+    so = os.path.join(REF_OUT, "libref_terms.so")
+    if os.path.exists(so) and not force:
+        return so
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    subprocess.check_call([cxx, "-O3", "-std=c++11", "-w", "-fPIC", "-shared", "-DUSE_OPENCV", "-DUSE_FLOAT",
+                           "-I", os.path.join(HERE, "mat_standin"), "-I", os.path.join(ref, "MPLayers", "aux"),
+                           "-I", os.path.join(ref, "tools", "cpp"), os.path.join(HERE, "ref_terms_shim.cpp"), src,
+                           os.path.join(ref, "tools", "cpp", "utils.cpp"), "-o", so])
+    return so
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     if "--ref" in sys.argv:
         print(build_reference_cpu(force="--force" in sys.argv))
+    if "--ref-terms" in sys.argv:
+        print(build_reference_terms(force="--force" in sys.argv))
     if "--ref-cuda" in sys.argv:
         print(build_reference_cuda(force="--force" in sys.argv))
