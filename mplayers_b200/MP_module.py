@@ -39,6 +39,24 @@ def _alloc_indices(unary, n_iter, n_dir, is_training, enable_saving_label):
     return message_index, cost_index, label_all
 
 
+def _norm_index_override(args, cost_index, n_disp):
+    """The `msg_norm_index` hook of pytorch/MP_module_hard_soft.py:76,169-171: normalisation
+    indices supplied by the caller replace the saved ones in the backward pass (the forward pass
+    is unaffected).  Returns the tensor to use, or None."""
+    given = getattr(args, "msg_norm_index", None)
+    if given is None:
+        return None
+    if cost_index.numel() == 0:
+        return None   # inference: there is no backward
+    given = given.to(device=cost_index.device, dtype=torch.uint8).contiguous()
+    if given.shape != cost_index.shape:
+        raise RuntimeError("msg_norm_index must be [I,D,B,cv,H,W] = %s, got %s" %
+                           (tuple(cost_index.shape), tuple(given.shape)))
+    if int(given.max()) >= n_disp:
+        raise RuntimeError("msg_norm_index holds a label >= n_disp (%d)" % n_disp)
+    return given
+
+
 class TRWPFunction(torch.autograd.Function):
     """pytorch/MP_module.py:17-86.  unary [B,cv,H,W,L]; label_context [L] or [L,L];
     edge_weights [D,B,cv,H,W] or None.  Returns (cost_final [B,cv,H,W,L], label_all)."""
@@ -59,6 +77,7 @@ class TRWPFunction(torch.autograd.Function):
         _TRWP.forward(rho, int(n_iter), int(args.enable_min_a_dir), unary, label_context, ew, message,
                       cost_final, message_index, cost_index, _empty_f32(unary.device), label_all)
         ctx.intermediate_results = rho, message_index, cost_index, label_context, ew, enable_edge_weights
+        ctx.norm_index_override = _norm_index_override(args, cost_index, n_disp)
         ctx.mark_non_differentiable(label_all)
         return cost_final, label_all
 
@@ -69,6 +88,8 @@ class TRWPFunction(torch.autograd.Function):
         if message_index.numel() == 0:
             raise RuntimeError("backward needs the indices saved by a training-mode forward "
                                "(args.training was False)")
+        if ctx.norm_index_override is not None:
+            cost_index = ctx.norm_index_override
         dcost_final = dcost_final.contiguous()
         n_iter, n_dir, batch, cv, h, w, n_disp = message_index.size()
         dunary = torch.empty_like(dcost_final)

@@ -13,6 +13,7 @@ import torch.nn as nn
 
 from . import TRWP as _TRWP
 from .MP_module import TRWPFunction as _TRWPFunctionBase
+from .MP_module import _norm_index_override
 from .label_context import create_label_context
 
 
@@ -48,6 +49,7 @@ class TRWPSoftFunction(torch.autograd.Function):
         _TRWP.forward_soft(rho, int(n_iter), unary, label_context, ew, message, message_edge_label,
                            cost_index, cost_final, e0, label_all)
         ctx.intermediate_results = rho, message_edge_label, cost_index, label_context, ew, enable_edge_weights
+        ctx.norm_index_override = _norm_index_override(args, cost_index, n_disp)
         ctx.mark_non_differentiable(label_all, message_edge_label, cost_index)
         return cost_final, label_all, message_edge_label, cost_index
 
@@ -58,6 +60,8 @@ class TRWPSoftFunction(torch.autograd.Function):
         if cost_index.numel() == 0:
             raise RuntimeError("backward needs the edge values saved by a training-mode forward "
                                "(args.training was False)")
+        if ctx.norm_index_override is not None:
+            cost_index = ctx.norm_index_override
         dcost_final = dcost_final.contiguous()
         n_iter, n_dir, batch, cv, h, w = cost_index.size()
         n_disp = dcost_final.size(-1)
@@ -96,9 +100,9 @@ class MPModule(torch.nn.Module):
                                  enable_symmetric=self.args.enable_symmetric)
 
     def forward(self, unary, edge_weights=None, msg_norm_index=None, pairwise_terms=None):
-        if msg_norm_index is not None:
-            raise NotImplementedError("externally supplied msg_norm_index (a debugging hook of the "
-                                      "reference) is not supported")
+        # pytorch/MP_module_hard_soft.py:169-171: indices given here replace the saved
+        # normalisation indices in the backward pass
+        self.args.msg_norm_index = msg_norm_index
         assert self.args.mpnet_mrf_mode == 'TRWP'
         unary = unary.permute(0, 1, 3, 4, 2).contiguous()
         edge_weights = edge_weights.unsqueeze(1).permute(2, 0, 1, 3, 4).contiguous() \

@@ -35,3 +35,22 @@ def labeling_energy(unary, label_context, edge_weights, labels, n_dir):
             ctypes.byref(prob), _lib.ptr(unary), _lib.ptr(label_context), _lib.ptr(edge_weights),
             _lib.ptr(labels), int(labels.size(0)), _lib.ptr(out), _lib.ptr(ws), n, _lib.stream_ptr(dev)))
     return out
+
+
+def save_energy_mat(file_path, unary, label_context, label_all, n_iter, n_dir, rho, p_func, p_weight, trunct,
+                    min_a_dir=False):
+    """Writes the `.mat` file the reference's driver hands to its MATLAB energy script
+    (MPLayers/main.py:322-333): the run's parameters, `unary` [H,W,L], `label_context` [L,L,D] and
+    the per-iteration labellings `seg_all` [H,W,I] (uint8).  unary [B=1,cv=1,H,W,L] or [H,W,L];
+    label_context [D,L,L] or [L,L]; label_all [I,1,1,H,W] or [I,H,W].  Needs scipy."""
+    import numpy as np
+    import scipy.io as scio
+    u = unary.detach().reshape(unary.shape[-3:]).cpu().numpy()
+    ctx = label_context.detach().cpu()
+    ctx = ctx.unsqueeze(0).repeat(int(n_dir), 1, 1) if ctx.dim() == 2 else ctx
+    seg = label_all.detach().reshape(label_all.size(0), *label_all.shape[-2:]).permute(1, 2, 0).cpu().numpy()
+    scio.savemat(file_path, {'n_iter': n_iter, 'n_dir': n_dir, 'rho': rho, 'p_func': p_func,
+                             'n_disp': u.shape[-1], 'p_weight': p_weight, 'trunct': trunct,
+                             'min_a_dir': int(min_a_dir), 'unary': u,
+                             'label_context': ctx.permute(1, 2, 0).numpy(),
+                             'seg_all': seg.astype(np.uint8)})

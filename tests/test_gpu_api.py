@@ -120,3 +120,52 @@ def test_identical_samples_give_identical_results():
         cost = mod(u, e)[0]
     for b in range(1, 12):
         assert torch.equal(cost[b], cost[0])
+
+
+@pytest.mark.parametrize("soft", [False, True])
+def test_supplied_norm_index_replaces_the_saved_one_in_backward(soft):
+    """pytorch/MP_module_hard_soft.py:76,169-171: `msg_norm_index` given to forward() is used by
+    the backward pass instead of the indices the forward pass saved; the forward result does not
+    change."""
+    from mplayers_b200 import MP_module_hard_soft
+    L, D, I = 21, 4, 2
+    unary, ctx, ew, g = _inputs(9, 1, L, 9, 10, D, 2)
+    args = _args("TRWP", I, D, L)
+    args.mpnet_enable_soft = soft
+    mod = MP_module_hard_soft.MPModule(args)
+    mod.set_label_context(torch.from_numpy(ctx).cuda(), None, None)
+    mod.train()
+    rng = np.random.default_rng(1)
+    given = rng.integers(0, L, (I, D, 1, 1, 9, 10)).astype(np.uint8)
+    u = torch.from_numpy(unary).cuda().requires_grad_(True)
+    e = torch.from_numpy(ew).cuda()
+    out_plain = mod(u, e)
+    out = mod(u, e, msg_norm_index=torch.from_numpy(given))
+    assert torch.equal(out[0], out_plain[0])
+    (out[0] * torch.from_numpy(g).cuda()).sum().backward()
+    un, en, gn = _to_ext(unary, ew, g)
+    if soft:
+        fw = oracle.forward_soft(un, ctx, en, D, I)
+        bw = oracle.backward_soft(ctx, en, gn, fw["edge_label"], given)
+    else:
+        fw = oracle.forward("TRWP", un, ctx, en, D, I)
+        bw = oracle.backward("TRWP", ctx, en, gn, fw["min_idx"], given, keep_diag=True)
+    assert rel_err(u.grad.permute(0, 1, 3, 4, 2).cpu().numpy(), bw["dunary"]) < GRAD_RTOL
+    with pytest.raises(RuntimeError, match="msg_norm_index"):
+        mod(u, e, msg_norm_index=torch.zeros(1, D, 1, 1, 9, 10, dtype=torch.uint8))
+    with pytest.raises(RuntimeError, match="n_disp"):
+        mod(u, e, msg_norm_index=torch.full((I, D, 1, 1, 9, 10), 200, dtype=torch.uint8))
+
+
+def test_energy_mat_file(tmp_path):
+    scio = pytest.importorskip("scipy.io")
+    from mplayers_b200 import energy
+    H, W, L, I, D = 6, 7, 5, 3, 4
+    unary = torch.rand(1, 1, H, W, L, device="cuda")
+    ctx = torch.rand(L, L, device="cuda")
+    labels = torch.randint(0, L, (I, 1, 1, H, W), dtype=torch.uint8, device="cuda")
+    path = str(tmp_path / "run.mat")
+    energy.save_energy_mat(path, unary, ctx, labels, I, D, 0.5, "TL", 10, 2)
+    m = scio.loadmat(path)
+    assert m["unary"].shape == (H, W, L) and m["label_context"].shape == (L, L, D) and m["seg_all"].shape == (H, W, I)
+    assert np.array_equal(m["seg_all"][:, :, 1], labels[1, 0, 0].cpu().numpy()) and int(m["n_disp"].item()) == L
