@@ -10,87 +10,160 @@ namespace mpl {
 
 namespace {
 
-constexpr int kDsiTX = 32;        // pixels of one row per block
-constexpr int kDsiThreads = 256;
+constexpr int kDsiTX = 64;        // pixels of one row per block
+constexpr int kDsiThreads = 512;  // 8 per pixel
 
-// c | min(c, left, right) << 8 | max(...) << 16 of one channel of pixel x, the half-sample
-// neighbours being (c + neighbour) / 2 in integers (aux.cpp:57-66).
-__device__ __forceinline__ uint32_t bt_pack(const uint8_t* row, int x, int W, int nB, int b) {
-  const int c = row[x * nB + b];
-  const int l = x == 0 ? c : (c + row[(x - 1) * nB + b]) / 2;
-  const int r = x == W - 1 ? c : (c + row[(x + 1) * nB + b]) / 2;
-  const int lo = min(c, min(l, r)), hi = max(c, max(l, r));
-  return (uint32_t)c | ((uint32_t)lo << 8) | ((uint32_t)hi << 16);
+// Per pixel and pair of colours (two 16-bit halves per word): c, c + 256, lo + 256 and hi, where
+// [lo, hi] spans the pixel's value and its two integer half-sample neighbours (c + neighbour) / 2
+// (aux.cpp:57-66); lo = hi = c when the plain absolute difference is asked for.  With these, the
+// one-sided distances of the Birchfield-Tomasi cost,
+//   max(0, c1 - hi2, lo2 - c1) + 256 = max(256, (c1 + 256) - hi2, (lo2 + 256) - c1),
+// are two 32-bit subtractions (every half stays in [1, 511]: no borrow crosses the halves) and one
+// packed 3-input maximum for two colours at once.
+struct __align__(16) BtWord {
+  uint32_t c, cb, lob, hi;
+};
+
+__device__ __forceinline__ void bt_half(const uint8_t* row, int x, int W, int nB, int b, int birchfield,
+                                        uint32_t& c, uint32_t& lo, uint32_t& hi) {
+  const int v = row[x * nB + b];
+  int l = v, r = v;
+  if (birchfield) {
+    l = x == 0 ? v : (v + row[(x - 1) * nB + b]) / 2;
+    r = x == W - 1 ? v : (v + row[(x + 1) * nB + b]) / 2;
+  }
+  c = v;
+  lo = min(v, min(l, r));
+  hi = max(v, max(l, r));
 }
 
-__device__ __forceinline__ int dsi_value(const uint32_t* s1, const uint32_t* s2, int nc, int birchfield,
-                                         int squared, int maxsum) {
-  int sum = 0;
-#pragma unroll 3
-  for (int b = 0; b < nc; ++b) {
-    const uint32_t p1 = s1[b], p2 = s2[b];
-    const int c1 = p1 & 255, c2 = p2 & 255;
-    int diff;
-    if (birchfield) {
-      const int lo1 = (p1 >> 8) & 255, hi1 = (p1 >> 16) & 255, lo2 = (p2 >> 8) & 255, hi2 = (p2 >> 16) & 255;
-      const int di1 = max(0, max(c1 - hi2, lo2 - c1));
-      const int di2 = max(0, max(c2 - hi1, lo1 - c2));
-      diff = min(di1, di2);
-    } else {
-      diff = abs(c1 - c2);
-    }
-    sum += squared ? diff * diff : diff;
+// Words of pixel x for colours (b0, b0 + 1); a colour beyond nc counts as 0 in both images.
+__device__ __forceinline__ BtWord bt_pack(const uint8_t* row, int x, int W, int nB, int nc, int b0,
+                                          int birchfield) {
+  uint32_t c[2] = {0, 0}, lo[2] = {0, 0}, hi[2] = {0, 0};
+  for (int k = 0; k < 2; ++k)
+    if (b0 + k < nc) bt_half(row, x, W, nB, b0 + k, birchfield, c[k], lo[k], hi[k]);
+  BtWord w;
+  w.c = c[0] | (c[1] << 16);
+  w.cb = w.c + 0x01000100u;
+  w.lob = (lo[0] + 256u) | ((lo[1] + 256u) << 16);
+  w.hi = hi[0] | (hi[1] << 16);
+  return w;
+}
+
+// min(di1, di2) + 256 of two colours, one per 16-bit half.
+__device__ __forceinline__ uint32_t bt_pair(const BtWord& l, const BtWord& r) {
+  const uint32_t k = 0x01000100u;
+  const uint32_t d1 = __vimax3_u16x2(l.cb - r.hi, r.lob - l.c, k);
+  const uint32_t d2 = __vimax3_u16x2(r.cb - l.hi, l.lob - r.c, k);
+  return __vimin3_u16x2(d1, d2, d2);
+}
+
+// Third colour: the same left pixel against TWO neighbouring right pixels at once (one per half).
+__device__ __forceinline__ BtWord bt_pack_third(const uint8_t* row, int x, int W, int nB, int nc, int birchfield) {
+  uint32_t c[2] = {0, 0}, lo[2] = {0, 0}, hi[2] = {0, 0};
+  if (nc > 2) {
+    if (x >= 0) bt_half(row, x, W, nB, 2, birchfield, c[0], lo[0], hi[0]);
+    if (x >= 1) bt_half(row, x - 1, W, nB, 2, birchfield, c[1], lo[1], hi[1]);
+  }
+  BtWord w;
+  w.c = c[0] | (c[1] << 16);
+  w.cb = w.c + 0x01000100u;
+  w.lob = (lo[0] + 256u) | ((lo[1] + 256u) << 16);
+  w.hi = hi[0] | (hi[1] << 16);
+  return w;
+}
+
+// Sum over colours of one label's differences: the two halves of m01 and half `odd` of `third`,
+// each biased by 256.  Not squared: two 2-way dot products with ones do the unpacking and the adds.
+template <bool SQUARED>
+__device__ __forceinline__ int dsi_sum(uint32_t m01, uint32_t third, int odd, int maxsum) {
+  int sum;
+  if (SQUARED) {
+    const int d0 = (int)(m01 & 0xffffu) - 256, d1 = (int)(m01 >> 16) - 256;
+    const int d2 = (int)(odd ? (third >> 16) : (third & 0xffffu)) - 256;
+    sum = d0 * d0 + d1 * d1 + d2 * d2;
+  } else {
+    sum = (int)__dp2a_lo(m01, 0x0101u, __dp2a_lo(third, odd ? 0x0100u : 0x0001u, (unsigned)-768));
   }
   return min(sum, maxsum);
 }
 
-// One block: kDsiTX pixels of one row, all labels.  The tile of the output is contiguous
-// (kDsiTX * L floats), so consecutive threads write consecutive addresses.
-template <bool VEC4>
+// Right pixels of a block live in shared memory de-interleaved by (index mod 4): entry j (pixel
+// x0 - (L - 1) + j) sits at row j & 3, column j >> 2.  Plane 0: colours (0, 1) of the pixel; plane 1:
+// colour 2 of the pixel (low half) and of its left neighbour (high half), so that one packed
+// operation against the left pixel's colour 2 (duplicated in both halves) serves two labels.
+constexpr int kDsiQ = (kDsiTX + 256 - 1 + 3) / 4 + 1;   // columns per row for up to 256 labels
+__device__ __forceinline__ int dsi_slot(int j) { return (j & 3) * kDsiQ + (j >> 2); }
+
+// One block: kDsiTX pixels of one row, all labels; its output tile is one contiguous run of
+// kDsiTX * L floats.  VEC4 (L a multiple of 4): thread = (pixel, one of 8 lanes); a lane computes
+// labels 4*lane .. 4*lane+3, then 32 further on, and stores them as one 16-byte word, so 8 lanes
+// write 128 contiguous bytes.  Consecutive lanes read right pixels 4 apart, which the
+// de-interleaved layout turns into consecutive 16-byte shared-memory words; the left pixel's words
+// stay in registers and the four read pointers only step by a constant.
+template <bool VEC4, bool THREE, bool SQUARED>
 __global__ void __launch_bounds__(kDsiThreads)
 stereo_data_cost_kernel(const uint8_t* __restrict__ left, const uint8_t* __restrict__ right, int H, int W,
-                        int nB, int L, int birchfield, int squared, int maxsum, int badcost,
-                        float* __restrict__ out) {
-  extern __shared__ uint32_t sm[];
+                        int nB, int L, int birchfield, int maxsum, int badcost, float* __restrict__ out) {
+  __shared__ BtWord s1[kDsiTX * 2];        // left pixels: colours (0,1), colour 2
+  __shared__ BtWord s2[2 * 4 * kDsiQ];     // right pixels: plane of colours (0,1), plane of colour 2
   const int nc = min(3, nB);
   const int y = blockIdx.y, x0 = blockIdx.x * kDsiTX;
   const int tx = min(kDsiTX, W - x0);
-  uint32_t* s1 = sm;                     // [kDsiTX][3]
-  uint32_t* s2 = sm + kDsiTX * 3;        // [kDsiTX + L - 1][3], entry j <-> pixel x0 - (L - 1) + j
   const uint8_t* lrow = left + (long long)y * W * nB;
   const uint8_t* rrow = right + (long long)y * W * nB;
-  for (int i = threadIdx.x; i < tx * nc; i += kDsiThreads) {
-    const int px = i / nc, b = i - px * nc;
-    s1[px * 3 + b] = bt_pack(lrow, x0 + px, W, nB, b);
+  for (int i = threadIdx.x; i < tx * 2; i += kDsiThreads) {
+    BtWord w = bt_pack(lrow, x0 + (i >> 1), W, nB, nc, (i & 1) * 2, birchfield);
+    if (i & 1) {   // colour 2 in both halves
+      w.c *= 0x00010001u, w.cb = w.c + 0x01000100u, w.lob = (w.lob & 0xffffu) * 0x00010001u, w.hi *= 0x00010001u;
+    }
+    s1[i] = w;
   }
   const int n2 = tx + L - 1;
-  for (int i = threadIdx.x; i < n2 * nc; i += kDsiThreads) {
-    const int j = i / nc, b = i - j * nc;
-    const int x = x0 - (L - 1) + j;
-    if (x >= 0) s2[j * 3 + b] = bt_pack(rrow, x, W, nB, b);
+  for (int i = threadIdx.x; i < n2 * 2; i += kDsiThreads) {
+    const int j = i >> 1, x = x0 - (L - 1) + j;
+    if (x >= 0)
+      s2[(i & 1) * 4 * kDsiQ + dsi_slot(j)] =
+          (i & 1) ? bt_pack_third(rrow, x, W, nB, nc, birchfield) : bt_pack(rrow, x, W, nB, nc, 0, birchfield);
   }
   __syncthreads();
   float* tile = out + ((long long)y * W + x0) * L;
-  const int n = tx * L;
   if (VEC4) {
-    for (int i = threadIdx.x * 4; i < n; i += kDsiThreads * 4) {
-      const int px = i / L, d0 = i - px * L;
+    const int px = threadIdx.x >> 3, l8 = threadIdx.x & 7;
+    if (px >= tx) return;
+    const BtWord l[2] = {s1[px * 2], s1[px * 2 + 1]};
+    const int xl = x0 + px;                       // labels d <= xl have a right pixel
+    const int j0 = px + L - 1 - 4 * l8;           // entry matched by label 4 * l8
+    const BtWord* r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) r[k] = s2 + dsi_slot(j0 - k);
+    float* o = tile + px * L + 4 * l8;
+    for (int d0 = 4 * l8; d0 < L; d0 += 32) {
       float v[4];
+      uint32_t third[2] = {0x01000100u, 0x01000100u};
+      if (THREE) {   // labels (d0, d0+1) and (d0+2, d0+3): right pixels (j, j-1) and (j-2, j-3)
+        third[0] = bt_pair(l[1], r[0][4 * kDsiQ]);
+        third[1] = bt_pair(l[1], r[2][4 * kDsiQ]);
+      }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int d = d0 + k;
-        v[k] = (x0 + px - d >= 0)
-                   ? (float)dsi_value(s1 + px * 3, s2 + (px - d + L - 1) * 3, nc, birchfield, squared, maxsum)
-                   : (float)badcost;
+        const int c = dsi_sum<SQUARED>(bt_pair(l[0], r[k][0]), third[k >> 1], k & 1, maxsum);
+        v[k] = (float)(d0 + k <= xl ? c : badcost);
+        r[k] -= 8;                                // 32 labels further: 8 columns back
       }
-      *reinterpret_cast<float4*>(tile + i) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+      o += 32;
     }
   } else {
+    const int n = tx * L;
     for (int i = threadIdx.x; i < n; i += kDsiThreads) {
       const int px = i / L, d = i - px * L;
-      tile[i] = (x0 + px - d >= 0)
-                    ? (float)dsi_value(s1 + px * 3, s2 + (px - d + L - 1) * 3, nc, birchfield, squared, maxsum)
-                    : (float)badcost;
+      const BtWord l[2] = {s1[px * 2], s1[px * 2 + 1]};
+      const BtWord* r = s2 + dsi_slot(px - d + L - 1);
+      const uint32_t third = THREE ? bt_pair(l[1], r[4 * kDsiQ]) : 0x01000100u;
+      const int c = dsi_sum<SQUARED>(bt_pair(l[0], r[0]), third, 0, maxsum);
+      tile[i] = (float)(x0 + px - d >= 0 ? c : badcost);
     }
   }
 }
@@ -269,13 +342,14 @@ cudaError_t launch_stereo_data_cost(const uint8_t* left, const uint8_t* right, i
   const int maxsum = squared ? trunc * trunc : nc * abs(trunc);
   const int bad = worst < maxsum ? worst : maxsum;
   dim3 grid((W + kDsiTX - 1) / kDsiTX, H);
-  const size_t smem = (size_t)(kDsiTX * 3 + (kDsiTX + L - 1) * 3) * sizeof(uint32_t);
-  if (L % 4 == 0)
-    stereo_data_cost_kernel<true><<<grid, kDsiThreads, smem, st>>>(left, right, H, W, nB, L, birchfield, squared,
-                                                                  maxsum, bad, out);
-  else
-    stereo_data_cost_kernel<false><<<grid, kDsiThreads, smem, st>>>(left, right, H, W, nB, L, birchfield,
-                                                                   squared, maxsum, bad, out);
+  using Kern = void (*)(const uint8_t*, const uint8_t*, int, int, int, int, int, int, int, float*);
+  static const Kern table[8] = {
+      stereo_data_cost_kernel<false, false, false>, stereo_data_cost_kernel<false, false, true>,
+      stereo_data_cost_kernel<false, true, false>,  stereo_data_cost_kernel<false, true, true>,
+      stereo_data_cost_kernel<true, false, false>,  stereo_data_cost_kernel<true, false, true>,
+      stereo_data_cost_kernel<true, true, false>,   stereo_data_cost_kernel<true, true, true>};
+  const Kern kern = table[(L % 4 == 0 ? 4 : 0) + (nc == 3 ? 2 : 0) + (squared ? 1 : 0)];
+  kern<<<grid, kDsiThreads, 0, st>>>(left, right, H, W, nB, L, birchfield, maxsum, bad, out);
   count_launch();
   return cudaGetLastError();
 }

@@ -1,7 +1,7 @@
 """Generates the golden vectors in this directory from the REFERENCE's own implementation.
 
-Run in a container that has the reference checkout (default /root/reference, or
-$MPL_REFERENCE_DIR):   python tests/golden/make_golden.py
+Run in a container that has the reference checkout (its path in $MPL_REFERENCE_DIR; the default is
+the directory mounted next to this repository):   python tests/golden/make_golden.py
 
 The generator imports the reference's pure-PyTorch autograd implementation
 (pytorch/message_passing.py, MessagePassingModule) in float64, feeds it the seeded inputs of

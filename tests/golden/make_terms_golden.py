@@ -1,6 +1,7 @@
 """Generates terms_golden.npz from the REFERENCE's own input builders.
 
-Run where the reference checkout is present (default /root/reference, or $MPL_REFERENCE_DIR):
+Run where the reference checkout is present (its path in $MPL_REFERENCE_DIR; the default is the
+directory mounted next to this repository):
     python oracle/build.py --ref-terms && python tests/golden/make_terms_golden.py
 
 * stereo cost volume, gradient cues, pairwise tables: the reference's MPLayers/aux/aux.cpp compiled
