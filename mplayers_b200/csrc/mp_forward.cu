@@ -910,6 +910,21 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
   }
 }
 
+constexpr int kWideChains = 4;  // most chains per CTA of fwd_wide_kernel
+// Chains per CTA of fwd_wide_kernel.  Wide windows make a step arithmetic-bound: four chains per
+// CTA (consumers on warps 0..3, producers on 4..7) give each of the SM's four schedulers one
+// consumer however the SM places a CTA's warps (measured on 256 labels, window 16: 0.47 -> 0.35 ms
+// per sweep).  Narrow windows leave the sweep bound by memory latency, where more, smaller CTAs
+// spread over all SMs win; there a CTA holds one chain, padded with an idle third warp so that
+// successive CTAs start on different schedulers (192 labels, window 3: 0.50 -> 0.47 ms).
+__host__ __device__ constexpr int wide_chains_per_cta(int lpt, int rw) { return lpt * rw >= 32 ? kWideChains : 1; }
+// Shared memory of one chain of fwd_wide_kernel (staging ring, two window buffers, edge weights,
+// barriers), rounded so that the next chain's ring starts 128-byte aligned.
+__host__ __device__ inline size_t wide_chain_bytes(int ns, int A, int k, int L, int lpt, int g) {
+  const size_t b = ((size_t)ns * A * k * L + 2 * (32 * lpt + 2 * g) + 2 * k + 2) * sizeof(float) + 2 * ns * 8 + 16;
+  return (b + 127) & ~(size_t)127;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Inference, rank-1 context that saturates inside a window (truncated linear / quadratic, Potts),
 // 32 < L <= 256, L % 4 == 0: one WARP per chain, LPT = ceil(L/32) consecutive labels per lane.
@@ -923,39 +938,47 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
 // beyond R carry the saturated value, which is an exact candidate of the dense evaluation too).
 // ------------------------------------------------------------------------------------------------
 template <int LPT, int RW, int DT>
-__global__ void __launch_bounds__(64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p) {
-  extern __shared__ __align__(128) float smem[];
-  ChainCtx ch;
-  if (!decode_chain(p, blockIdx.x, ch)) return;  // uniform for the CTA
+__global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(128) float smem_all[];
   constexpr int LP = 32 * LPT;                   // padded label count
   constexpr int G = ((RW - 1 + 3) / 4) * 4;      // guard band (floats) on both sides of the window buffer
   constexpr int NWV = (LPT + 2 * G) / 2;         // float2 loads covering a lane's window
   constexpr bool AGG = DT == 2;  // aggregate mode (FwdParams::agg): arrays A, M_dir, M_inv
   const int L = p.L, D = DT ? DT : p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Warps 0..C-1 are the consumers of the CTA's C chains, warps C..2C-1 their producers.
+  constexpr int C = wide_chains_per_cta(LPT, RW);
+  const int sub = warp & (C - 1);
+  const bool producer = warp >= C;
+  float* smem = smem_all + (size_t)sub * (wide_chain_bytes(NS, A, K, L, LPT, G) / sizeof(float));
+  ChainCtx ch;
+  const bool valid = decode_chain(p, blockIdx.x * C + sub, ch);
   const int tile_floats = A * K * L;
   float* tiles = smem;                                   // [NS][A][K][L]
   float* hwin = tiles + NS * tile_floats;                // [2][G + LP + G]
   float* etile = hwin + 2 * (LP + 2 * G);                // [2][K]
   unsigned long long* full = reinterpret_cast<unsigned long long*>(etile + 2 * K + ((2 * K) & 1));
   unsigned long long* empty = full + NS;
-  const int len = ch.len;
+  const int len = valid ? ch.len : 0;
   const int nstages = (len + K - 1) / K;
   const long long ibase = (long long)ch.img * p.H * p.W;
   const int pix0 = ch.h0 * p.W + ch.w0;
   const bool contiguous = (ch.pstep == 1 || ch.pstep == -1);
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < NS; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+  if (!producer) {
+    if (lane == 0) {
+      for (int i = 0; i < NS; ++i) {
+        mbar_init(&full[i], 1);
+        mbar_init(&empty[i], 1);
+      }
+      mbar_fence_init();
     }
-    mbar_fence_init();
+    for (int i = lane; i < 2 * (LP + 2 * G); i += 32) hwin[i] = kInf;  // guards and padding labels
   }
-  for (int i = threadIdx.x; i < 2 * (LP + 2 * G); i += 64) hwin[i] = kInf;  // guards and padding labels
   __syncthreads();
+  if (!valid || warp >= 2 * C) return;  // warps beyond 2C only pad the CTA (see launch_wide_d)
 
-  if (warp == 1) {
+  if (producer) {
     // ---------------------------------- producer ----------------------------------
     const float* U = p.unary + ibase * L;
     const float* Mr = p.msg_read + ibase * L;
@@ -1510,14 +1533,14 @@ cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
   const int A = (p.agg ? 2 : p.D) + 1;
   constexpr int G = ((RW - 1 + 3) / 4) * 4;
   int K = 8, NS = 3;
-  auto bytes = [&](int k, int ns) {
-    return ((size_t)ns * A * k * p.L + 2 * (32 * LPT + 2 * G) + 2 * k + 2) * sizeof(float) + 2 * ns * 8 + 16;
-  };
+  auto bytes = [&](int k, int ns) { return wide_chain_bytes(ns, A, k, p.L, LPT, G); };
   // keep every chain of the launch resident at once where possible (chains are equally long, so a
   // partial second wave would double the time)
-  const int per_sm = (total + 147) / 148;
-  size_t limit = (size_t)220 * 1024 / (per_sm > 0 ? per_sm : 1);
-  if (limit > 100 * 1024) limit = 100 * 1024;
+  constexpr int C = wide_chains_per_cta(LPT, RW);
+  const int ctas = (total + C - 1) / C;
+  const int per_sm = (ctas + 147) / 148;
+  size_t limit = (size_t)220 * 1024 / ((per_sm > 0 ? per_sm : 1) * C);
+  if (limit > 56 * 1024) limit = 56 * 1024;
   if (limit < 12 * 1024) limit = 12 * 1024;
   while (bytes(K, NS) > limit) {
     if (K > 4) {
@@ -1533,11 +1556,15 @@ cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
   if (tma_stage_override()) NS = tma_stage_override();
   p.tma_k = K;
   p.tma_stages = NS;
-  const size_t smem = bytes(K, NS);
+  const size_t smem = bytes(K, NS) * C;
   cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW, DT>, smem);
   if (e != cudaSuccess) return e;
+  // the residency computed above assumes the largest shared-memory carve-out
+  e = cudaFuncSetAttribute(fwd_wide_kernel<LPT, RW, DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                           (int)cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
-  fwd_wide_kernel<LPT, RW, DT><<<total, 64, smem, st>>>(p);
+  fwd_wide_kernel<LPT, RW, DT><<<ctas, C == 1 ? 96 : C * 64, smem, st>>>(p);
   count_launch();
   return cudaGetLastError();
 }
