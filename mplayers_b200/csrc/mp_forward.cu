@@ -1375,6 +1375,35 @@ __global__ void aggregate_kernel(const float* __restrict__ unary, const float* _
   }
 }
 
+// The same with 16-byte accesses (n, slice multiples of 4, pointers 16-byte aligned); every
+// component is summed in the same order as above.
+__global__ void __launch_bounds__(256)
+aggregate_vec4_kernel(const float4* __restrict__ unary, const float4* __restrict__ msg, float4* __restrict__ cost,
+                      long long n4, int D, long long slice4, float factor, int min_a_dir) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 u = unary[i];
+    float4 v = make_float4(u.x * factor, u.y * factor, u.z * factor, u.w * factor);
+    if (min_a_dir) {
+      float4 mm = msg[i];
+      for (int k = 1; k < D; ++k) {
+        const float4 x = msg[k * slice4 + i];
+        if (x.x < mm.x) mm.x = x.x;
+        if (x.y < mm.y) mm.y = x.y;
+        if (x.z < mm.z) mm.z = x.z;
+        if (x.w < mm.w) mm.w = x.w;
+      }
+      v.x += mm.x, v.y += mm.y, v.z += mm.z, v.w += mm.w;
+    } else {
+      for (int k = 0; k < D; ++k) {
+        const float4 x = msg[k * slice4 + i];
+        v.x += x.x, v.y += x.y, v.z += x.z, v.w += x.w;
+      }
+    }
+    cost[i] = v;
+  }
+}
+
 __global__ void label_kernel(const float* __restrict__ cost, uint8_t* __restrict__ label,
                              long long npix, int L) {
   const long long px = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -2023,7 +2052,19 @@ cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, 
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   ProfScope prof(kProfElementwise, st);
-  aggregate_kernel<<<(int)blocks, 256, 0, st>>>(unary, msg, cost, n, D, slice, factor, min_a_dir);
+  const bool vec4 = n % 4 == 0 && slice % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(unary) | reinterpret_cast<uintptr_t>(msg) |
+                      reinterpret_cast<uintptr_t>(cost)) & 15) == 0;
+  if (vec4) {
+    long long b4 = (n / 4 + 255) / 256;
+    if (b4 > 148 * 16) b4 = 148 * 16;
+    aggregate_vec4_kernel<<<(int)b4, 256, 0, st>>>(reinterpret_cast<const float4*>(unary),
+                                                   reinterpret_cast<const float4*>(msg),
+                                                   reinterpret_cast<float4*>(cost), n / 4, D, slice / 4, factor,
+                                                   min_a_dir);
+  } else {
+    aggregate_kernel<<<(int)blocks, 256, 0, st>>>(unary, msg, cost, n, D, slice, factor, min_a_dir);
+  }
   count_launch();
   if (label) {
     label_kernel<<<(int)((npix + 127) / 128), 128, 0, st>>>(cost, label, npix, L);
