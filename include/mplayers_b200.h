@@ -190,7 +190,9 @@ int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t wo
  *                                  saved for the backward (lowest index among equal maxima)
  *   mpl_scores_to_costs_backward   dscores[b,l,p] = -dcosts[b,p,l] + (l == argmax[b,p]) * sum_l dcosts[b,p,:]
  *   mpl_negate_hwl_to_lhw          scores_out[b,l,p] = -cost_final[b,p,l]   (and its backward:)
- *   mpl_negate_lhw_to_hwl          out[b,p,l] = -in[b,l,p] */
+ *   mpl_negate_lhw_to_hwl          out[b,p,l] = -in[b,l,p]
+ *   mpl_permute_lhw_to_hwl / mpl_permute_hwl_to_lhw   the plain layout change of the module call,
+ *                                  unary [B*cv,L,H,W] -> [B*cv,H,W,L] and back (pytorch/MP_module.py:198,232) */
 int mpl_scores_to_costs(const float* scores, float* costs, uint8_t* argmax, int32_t batch,
                         int32_t n_disp, int32_t height, int32_t width, void* stream);
 int mpl_scores_to_costs_backward(const float* dcosts, const uint8_t* argmax, float* dscores,
@@ -200,6 +202,10 @@ int mpl_negate_lhw_to_hwl(const float* in, float* out, int32_t batch, int32_t n_
                           int32_t width, void* stream);
 int mpl_negate_hwl_to_lhw(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
                           int32_t width, void* stream);
+int mpl_permute_lhw_to_hwl(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                           int32_t width, void* stream);
+int mpl_permute_hwl_to_lhw(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                           int32_t width, void* stream);
 
 /* Energy of labellings on the MRF the layers minimise, for energy-versus-iteration curves from the
  * per-iteration labels `label_all` of a forward call.  energy [n_labelings, 2] (f64, device):

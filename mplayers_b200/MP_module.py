@@ -14,6 +14,8 @@ Under the API everything runs in hand-written sm_100a kernels behind a C ABI
 import torch
 import torch.nn as nn
 
+from . import glue as _glue
+
 from . import ISGMR as _ISGMR
 from . import TRWP as _TRWP
 from .label_context import create_label_context
@@ -230,7 +232,7 @@ class MPModule(torch.nn.Module):
 
     def forward(self, unary, edge_weights=None):
         # unary [B,cv,L,H,W]; edge_weights [B,D,H,W]
-        unary = unary.permute(0, 1, 3, 4, 2).contiguous()
+        unary = _glue.labels_last(unary)
         edge_weights = edge_weights.unsqueeze(1).permute(2, 0, 1, 3, 4).contiguous() \
             if (edge_weights is not None) else edge_weights
         if self.args.mpnet_mrf_mode == 'SGM':
@@ -250,6 +252,6 @@ class MPModule(torch.nn.Module):
             cost_final, cost_all = TRWPFunction.apply(unary, label_context, edge_weights, self.args)
         else:
             assert False
-        cost_final = cost_final.permute(0, 1, 4, 2, 3).contiguous()
+        cost_final = _glue.labels_first(cost_final)
         label_context = label_context.unsqueeze(0)
         return cost_final, label_context, cost_all, None, None

@@ -11,6 +11,8 @@ and the normalisation indices (returned as `message_index`), as the reference do
 import torch
 import torch.nn as nn
 
+from . import glue as _glue
+
 from . import TRWP as _TRWP
 from .MP_module import TRWPFunction as _TRWPFunctionBase
 from .MP_module import _norm_index_override
@@ -104,7 +106,7 @@ class MPModule(torch.nn.Module):
         # normalisation indices in the backward pass
         self.args.msg_norm_index = msg_norm_index
         assert self.args.mpnet_mrf_mode == 'TRWP'
-        unary = unary.permute(0, 1, 3, 4, 2).contiguous()
+        unary = _glue.labels_last(unary)
         edge_weights = edge_weights.unsqueeze(1).permute(2, 0, 1, 3, 4).contiguous() \
             if (edge_weights is not None) else edge_weights
         label_context = self.label_context * self.args.mpnet_term_weight
@@ -124,10 +126,10 @@ class MPModule(torch.nn.Module):
         if getattr(self.args, 'mpnet_enable_soft', False):
             cost_final, cost_all, message_vector, message_index = \
                 TRWPSoftFunction.apply(unary, label_context, edge_weights, self.args)
-            cost_final = cost_final.permute(0, 1, 4, 2, 3).contiguous()
+            cost_final = _glue.labels_first(cost_final)
             return cost_final, label_context.unsqueeze(0), cost_all, message_vector, message_index
         cost_final, cost_all = TRWPFunction.apply(unary, label_context, edge_weights, self.args)
-        cost_final = cost_final.permute(0, 1, 4, 2, 3).contiguous()
+        cost_final = _glue.labels_first(cost_final)
         label_context = label_context.unsqueeze(0)
         empty = torch.empty(0, dtype=torch.float32, device=unary.device)
         return cost_final, label_context, cost_all, empty, empty

@@ -70,6 +70,9 @@ def lib():
         L.mpl_negate_lhw_to_hwl.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.mpl_negate_hwl_to_lhw.restype = ctypes.c_int
         L.mpl_negate_hwl_to_lhw.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+        for name in ("mpl_permute_lhw_to_hwl", "mpl_permute_hwl_to_lhw"):
+            getattr(L, name).restype = ctypes.c_int
+            getattr(L, name).argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.mpl_energy_workspace_bytes.restype = sz
         L.mpl_energy_workspace_bytes.argtypes = [pp]
         L.mpl_labeling_energy.restype = ctypes.c_int

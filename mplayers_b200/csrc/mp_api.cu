@@ -656,6 +656,15 @@ int mpl_negate_hwl_to_lhw(const float* in, float* out, int32_t batch, int32_t n_
   return layout_call(2, in, out, nullptr, batch, n_disp, height, width, stream);
 }
 
+int mpl_permute_lhw_to_hwl(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                           int32_t width, void* stream) {
+  return layout_call(4, in, out, nullptr, batch, n_disp, height, width, stream);
+}
+int mpl_permute_hwl_to_lhw(const float* in, float* out, int32_t batch, int32_t n_disp, int32_t height,
+                           int32_t width, void* stream) {
+  return layout_call(5, in, out, nullptr, batch, n_disp, height, width, stream);
+}
+
 // ---- energy of labellings (evaluation of the minimisation, not part of the layer) -----------------
 size_t mpl_energy_workspace_bytes(const mpl_problem* p) {
   Dims d;

@@ -1909,6 +1909,7 @@ cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream
 // shared-memory tile of 32 pixels x L labels, coalesced on both ends.
 //   MODE 0: out = -in            MODE 1: out = max_l(in) - in, argmax saved (lowest index on ties)
 //   MODE 2 (backward of 1, direction hwl -> lhw): out[l] = -in[l] + (l == argmax) * sum_l in[l]
+//   MODE 3: out = in (the plain layout change of pytorch/MP_module.py:198,232)
 // ------------------------------------------------------------------------------------------------
 template <int MODE>
 __global__ void lhw_to_hwl_kernel(const float* __restrict__ in, float* __restrict__ out, uint8_t* __restrict__ amax,
@@ -1938,7 +1939,7 @@ __global__ void lhw_to_hwl_kernel(const float* __restrict__ in, float* __restric
   for (int i = threadIdx.x; i < np * L; i += 256) {
     const int px = i / L, l = i - px * L;
     const float v = tile[l * 33 + px];
-    dst[i] = MODE == 1 ? mx[px] - v : -v;
+    dst[i] = MODE == 1 ? mx[px] - v : (MODE == 3 ? v : -v);
   }
 }
 
@@ -1967,7 +1968,10 @@ __global__ void hwl_to_lhw_kernel(const float* __restrict__ in, float* __restric
   float* dst = out + b * L * HW;
   const int k = (MODE == 2 && tx < np) ? (int)amax[b * HW + p0 + tx] : -1;
   for (int l = ty; l < L; l += 8)
-    if (tx < np) dst[(long long)l * HW + p0 + tx] = -tile[l * 33 + tx] + ((MODE == 2 && l == k) ? sm[tx] : 0.f);
+    if (tx < np) {
+      const float v = tile[l * 33 + tx];
+      dst[(long long)l * HW + p0 + tx] = MODE == 3 ? v : -v + ((MODE == 2 && l == k) ? sm[tx] : 0.f);
+    }
 }
 
 cudaError_t launch_layout(int kind, const float* in, float* out, uint8_t* amax, int B, int L, long long HW,
@@ -1979,6 +1983,8 @@ cudaError_t launch_layout(int kind, const float* in, float* out, uint8_t* amax, 
     case 0: lhw_to_hwl_kernel<0><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
     case 1: lhw_to_hwl_kernel<1><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
     case 2: hwl_to_lhw_kernel<0><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
+    case 4: lhw_to_hwl_kernel<3><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
+    case 5: hwl_to_lhw_kernel<3><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
     default: hwl_to_lhw_kernel<2><<<grid, 256, smem, st>>>(in, out, amax, L, HW); break;
   }
   count_launch();

@@ -81,3 +81,61 @@ def mp_on_scores(layer, scores, edge_weights=None):
     ew = edge_weights.unsqueeze(1).permute(2, 0, 1, 3, 4).contiguous() if edge_weights is not None else None
     cost_final, label_context = layer.forward_native(costs, ew)
     return CostsToScores.apply(cost_final), label_context
+
+
+def _permute(name, x, out_shape, bc, l, h, w):
+    out = torch.empty(out_shape, dtype=torch.float32, device=x.device)
+    if out.numel():
+        with torch.cuda.device(x.device):
+            _lib.check(getattr(_lib.lib(), name)(_lib.ptr(x), _lib.ptr(out), bc, l, h, w, _lib.stream_ptr(x.device)))
+    return out
+
+
+class LabelsLast(torch.autograd.Function):
+    """unary [B,cv,L,H,W] -> [B,cv,H,W,L]: the `permute(0, 1, 3, 4, 2).contiguous()` of the module
+    call (pytorch/MP_module.py:198) as one kernel that is coalesced on both sides; the backward is
+    the inverse change of layout."""
+
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        _lib.require(x, "unary", torch.float32)
+        b, cv, l, h, w = (int(v) for v in x.shape)
+        return _permute("mpl_permute_lhw_to_hwl", x, (b, cv, h, w, l), b * cv, l, h, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        b, cv, h, w, l = (int(v) for v in g.shape)
+        return _permute("mpl_permute_hwl_to_lhw", g, (b, cv, l, h, w), b * cv, l, h, w)
+
+
+class LabelsFirst(torch.autograd.Function):
+    """cost_final [B,cv,H,W,L] -> [B,cv,L,H,W] (pytorch/MP_module.py:232); inverse of LabelsLast."""
+
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        _lib.require(x, "cost_final", torch.float32)
+        b, cv, h, w, l = (int(v) for v in x.shape)
+        return _permute("mpl_permute_hwl_to_lhw", x, (b, cv, l, h, w), b * cv, l, h, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        b, cv, l, h, w = (int(v) for v in g.shape)
+        return _permute("mpl_permute_lhw_to_hwl", g, (b, cv, h, w, l), b * cv, l, h, w)
+
+
+def labels_last(x):
+    """[B,cv,L,H,W] -> contiguous [B,cv,H,W,L] (kernel for float32 tensors within its limits, torch otherwise)."""
+    if x.dtype == torch.float32 and x.is_cuda and x.dim() == 5 and x.size(2) <= 256 and x.size(0) * x.size(1) <= 65535:
+        return LabelsLast.apply(x)
+    return x.permute(0, 1, 3, 4, 2).contiguous()
+
+
+def labels_first(x):
+    """[B,cv,H,W,L] -> contiguous [B,cv,L,H,W]."""
+    if x.dtype == torch.float32 and x.is_cuda and x.dim() == 5 and x.size(4) <= 256 and x.size(0) * x.size(1) <= 65535:
+        return LabelsFirst.apply(x)
+    return x.permute(0, 1, 4, 2, 3).contiguous()

@@ -78,3 +78,26 @@ def test_glue_timing_on_the_segmentation_shape():
         times[fused] = e0.elapsed_time(e1) / 10
     print("\n[glue] scores -> layer -> scores, fwd+bwd, B2 512x512 L21: torch expressions %.3f ms, fused glue %.3f ms"
           % (times[False], times[True]))
+
+
+@pytest.mark.parametrize("shape", [(2, 1, 21, 37, 45), (1, 3, 64, 8, 130), (1, 1, 256, 5, 7), (3, 1, 1, 4, 4)])
+def test_plain_layout_change_equals_torch_permute(shape):
+    """LabelsLast / LabelsFirst (the module call's two permutes) against torch, values and gradients
+    bit for bit (they only move data)."""
+    import torch
+    from mplayers_b200 import glue
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(*shape, generator=g).cuda().requires_grad_(True)
+    y = glue.labels_last(x)
+    assert y.is_contiguous() and torch.equal(y, x.permute(0, 1, 3, 4, 2))
+    w = torch.randn(*y.shape, generator=g).cuda()
+    (y * w).sum().backward()
+    assert torch.equal(x.grad, w.permute(0, 1, 4, 2, 3))
+    z = y.detach().requires_grad_(True)
+    back = glue.labels_first(z)
+    assert back.is_contiguous() and torch.equal(back, x.detach())
+    w2 = torch.randn(*back.shape, generator=g).cuda()
+    (back * w2).sum().backward()
+    assert torch.equal(z.grad, w2.permute(0, 1, 3, 4, 2))
+    xd = x.detach().double()   # other dtypes take the torch path
+    assert torch.equal(glue.labels_last(xd), xd.permute(0, 1, 3, 4, 2))
