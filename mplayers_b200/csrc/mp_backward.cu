@@ -20,6 +20,7 @@
 #include <cstdlib>
 
 #include "mp_common.cuh"
+#include "mp_minplus.cuh"
 
 namespace mpl {
 
@@ -48,64 +49,6 @@ __device__ __forceinline__ void warp_sum2(float& a, float& b) {
     a += __shfl_xor_sync(0xffffffffu, a, o);
     b += __shfl_xor_sync(0xffffffffu, b, o);
   }
-}
-
-__device__ __forceinline__ float eq_flag(float a, float b) {
-  float d;
-  asm("set.eq.f32.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));  // 1.0f if a == b else 0.0f
-  return d;
-}
-
-// q[f] = sum over labels c whose saved argmin is f of t[c], for f = `me`; fixed summation order
-// (interleaved partial sums).  tb / ib: the t values and argmin indices (stored as floats)
-// of all labels of this pixel in shared memory.  One compare-to-flag plus one fused multiply-add
-// per label: compare/select instructions issue at half the rate of multiply-adds.
-template <int LT>
-__device__ __forceinline__ float gather_q(const float* tb, const float* ib, int L, float me) {
-  float q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
-  if constexpr (LT > 0) {
-    constexpr int NV = (LT + 3) / 4;
-    float tv[NV * 4], iv[NV * 4];
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      const float4 a = reinterpret_cast<const float4*>(tb)[v];
-      const float4 b = reinterpret_cast<const float4*>(ib)[v];
-      tv[4 * v] = a.x, tv[4 * v + 1] = a.y, tv[4 * v + 2] = a.z, tv[4 * v + 3] = a.w;
-      iv[4 * v] = b.x, iv[4 * v + 1] = b.y, iv[4 * v + 2] = b.z, iv[4 * v + 3] = b.w;
-    }
-    // two labels per packed fma, two alternating accumulator pairs
-#pragma unroll
-    for (int c = 0; c + 1 < LT; c += 2) {
-      if (c & 2) {
-        ffma2(q2, q3, eq_flag(iv[c], me), eq_flag(iv[c + 1], me), tv[c], tv[c + 1], q2, q3);
-      } else {
-        ffma2(q0, q1, eq_flag(iv[c], me), eq_flag(iv[c + 1], me), tv[c], tv[c + 1], q0, q1);
-      }
-    }
-    if (LT & 1) q0 = fmaf(eq_flag(iv[LT - 1], me), tv[LT - 1], q0);
-  } else {
-    int c = 0;
-    for (; c + 2 < L; c += 3) {
-      q0 = fmaf(eq_flag(ib[c], me), tb[c], q0);
-      q1 = fmaf(eq_flag(ib[c + 1], me), tb[c + 1], q1);
-      q2 = fmaf(eq_flag(ib[c + 2], me), tb[c + 2], q2);
-    }
-    for (; c < L; ++c) q0 = fmaf(eq_flag(ib[c], me), tb[c], q0);
-  }
-  return (q0 + q1) + (q2 + q3);
-}
-
-// Sum of n consecutive floats (n = LT when known at compile time).
-template <int LT>
-__device__ __forceinline__ float row_sum(const float* row, int L) {
-  float s = 0.f;
-  if constexpr (LT > 0) {
-#pragma unroll
-    for (int c = 0; c < LT; ++c) s += row[c];
-  } else {
-    for (int c = 0; c < L; ++c) s += row[c];
-  }
-  return s;
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -18,6 +18,7 @@
 #include <cstdlib>
 
 #include "mp_common.cuh"
+#include "mp_minplus.cuh"
 
 namespace mpl {
 
@@ -51,110 +52,6 @@ __device__ __forceinline__ float uu_from_ring(const float* slot, int rs, int col
   for (int k = 0; k < D; ++k) s += slot[(1 + k) * rs + col];
   s -= slot[(1 + dir) * rs + col];
   return fmaf(s, rho, -slot[(1 + inv) * rs + col]);
-}
-
-__device__ __forceinline__ float min3f(float a, float b, float c) {
-  float d;
-  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));  // 3-input min (sm_100)
-  return d;
-}
-
-// Minimum of N registers with 3-input min instructions: depth ceil(log3 N) instead of the
-// reference's serial scan.
-template <int N>
-__device__ __forceinline__ float min_tree(const float (&v)[N]) {
-  if constexpr (N == 1) {
-    return v[0];
-  } else if constexpr (N == 2) {
-    return fminf(v[0], v[1]);
-  } else if constexpr (N == 3) {
-    return min3f(v[0], v[1], v[2]);
-  } else {
-    constexpr int M = (N + 2) / 3;
-    float t[M];
-#pragma unroll
-    for (int i = 0; i < M; ++i) {
-      if (3 * i + 2 < N) {
-        t[i] = min3f(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
-      } else if (3 * i + 1 < N) {
-        t[i] = fminf(v[3 * i], v[3 * i + 1]);
-      } else {
-        t[i] = v[3 * i];
-      }
-    }
-    return min_tree<M>(t);
-  }
-}
-
-__device__ __forceinline__ float eq_flag(float a, float b) {
-  float d;
-  asm("set.eq.f32.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));  // 1.0f if a == b else 0.0f
-  return d;
-}
-
-__device__ __forceinline__ constexpr float pow2f(int k) {
-  float r = 1.f;
-  for (int i = 0; i < k; ++i) r *= 2.f;
-  return r;
-}
-
-// Candidates val[f] = e*ctx(c,f) + h[f] for the label c of this thread, their minimum and -- when
-// TRAIN -- the HIGHEST f attaining it (what the reference's high-to-low strict-< scan returns,
-// MPLayers/TRWP/TRWP_forward.cu:126-152).
-//
-// Compare / select / min instructions run at half the rate of fused multiply-adds, so the index is
-// not tracked with a compare-and-select chain.  The exact minimum is taken first (3-input min
-// tree); then every candidate contributes (val[f] == min) * 2^f to a float accumulator with one
-// set + one fma (groups of 24 labels per accumulator, exact in a 24-bit mantissa), and the wanted
-// index is the exponent of the accumulator.
-// CN / OFF: `cr` has CN entries of which LMAX starting at OFF are used (hb points at candidate OFF).
-template <int LMAX, bool TRAIN, int CN = LMAX, int OFF = 0>
-__device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr)[CN], float e,
-                                               float& best, int& bi) {
-  constexpr int NV = (LMAX + 3) / 4;
-  float hv[NV * 4];
-#pragma unroll
-  for (int q = 0; q < NV; ++q) {
-    const float4 t = reinterpret_cast<const float4*>(hb)[q];
-    hv[4 * q] = t.x;
-    hv[4 * q + 1] = t.y;
-    hv[4 * q + 2] = t.z;
-    hv[4 * q + 3] = t.w;
-  }
-  float val[LMAX];
-#pragma unroll
-  for (int f = 0; f + 1 < LMAX; f += 2) ffma2(val[f], val[f + 1], e, e, cr[OFF + f], cr[OFF + f + 1], hv[f], hv[f + 1]);
-  if (LMAX & 1) val[LMAX - 1] = fmaf(e, cr[OFF + LMAX - 1], hv[LMAX - 1]);
-  best = min_tree<LMAX>(val);
-  bi = 0;
-  if (TRAIN) {
-    // Sums of distinct powers of two are exact in any order, so each group of 24 labels is
-    // accumulated in four interleaved partial sums (short dependency chains), two per packed fma.
-    constexpr int NA = (LMAX + 23) / 24;
-    float acc[NA][4];
-#pragma unroll
-    for (int a = 0; a < NA; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
-#pragma unroll
-    for (int f = 0; f + 1 < LMAX; f += 2) {  // 24 is even: a pair never straddles two groups
-      const int a = f / 24, j = f & 2;
-      ffma2(acc[a][j], acc[a][j + 1], eq_flag(val[f], best), eq_flag(val[f + 1], best), pow2f(f % 24),
-            pow2f((f + 1) % 24), acc[a][j], acc[a][j + 1]);
-    }
-    if (LMAX & 1) {
-      constexpr int f = LMAX - 1;
-      acc[f / 24][0] = fmaf(eq_flag(val[f], best), pow2f(f % 24), acc[f / 24][0]);
-    }
-#pragma unroll
-    for (int a = 0; a < NA; ++a) {
-      const float sum = (acc[a][0] + acc[a][1]) + (acc[a][2] + acc[a][3]);
-      const int ex = ((__float_as_int(sum) >> 23) & 0xff) - 127 + 24 * a;
-      if (a == 0) {
-        bi = ex;
-      } else {
-        bi = sum != 0.f ? ex : bi;
-      }
-    }
-  }
 }
 
 // Sum of 32 values in the order of a shuffle-down tree over a warp (x[i] += x[i + 16], then 8, 4,

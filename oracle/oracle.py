@@ -83,6 +83,35 @@ def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=Tr
     return dict(cost=cost, msg=msg, min_idx=mi, norm_idx=ni, label_all=lab)
 
 
+def audit_ties(mode, unary, ctx, edge_weights, n_dir, n_iter, alt_min_idx, rho=None, n_threads=None):
+    """Tie audit of another implementation's saved argmin indices (layout of min_idx).  Runs the
+    forward pass and, wherever `alt_min_idx` differs from the index computed here, compares the value
+    of that candidate with the minimum bit for bit.  Returns (differing entries, differing entries
+    that are NOT exact ties); the second number must be 0."""
+    unary = np.ascontiguousarray(unary, np.float32)
+    ctx = np.ascontiguousarray(ctx, np.float32)
+    b, cv, h, w, l = unary.shape
+    if edge_weights is None:
+        edge_weights = np.ones((n_dir, b, cv, h, w), np.float32)
+    edge_weights = np.ascontiguousarray(edge_weights, np.float32)
+    alt = np.ascontiguousarray(alt_min_idx, np.uint8)
+    assert alt.shape == (n_iter, n_dir, b, cv, h, w, l)
+    prob = _problem(mode, unary, n_dir, n_iter, ctx, rho, 0, 0, 0, n_threads)
+    msg = np.zeros((n_dir, b, cv, h, w, l), np.float32)
+    cost = np.zeros_like(unary)
+    mi = np.zeros(alt.shape, np.uint8)
+    ni = np.zeros(alt.shape[:-1], np.uint8)
+    out = (ctypes.c_longlong * 2)()
+    lib().mpo_forward_audit.restype = ctypes.c_int
+    rc = lib().mpo_forward_audit(ctypes.byref(prob), _p(unary, ctypes.c_float), _p(ctx, ctypes.c_float),
+                                 _p(edge_weights, ctypes.c_float), _p(msg, ctypes.c_float),
+                                 _p(cost, ctypes.c_float), _p(mi, ctypes.c_uint8), _p(ni, ctypes.c_uint8),
+                                 _p(alt, ctypes.c_uint8), out)
+    if rc:
+        raise RuntimeError("mpo_forward_audit failed with code %d" % rc)
+    return int(out[0]), int(out[1])
+
+
 def backward(mode, ctx, edge_weights, dcost, min_idx, norm_idx, rho=None, enable_sgm=False,
              keep_diag=False, n_threads=None):
     """Returns dict(dunary, dctx, dew)."""

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import cases
-from helpers import COST_RTOL, GRAD_RTOL, rel_err
+from helpers import COST_RTOL, GRAD_RTOL, assert_grad_close, audit_index_ties, rel_err
 from oracle import oracle
 
 pytestmark = pytest.mark.gpu
@@ -24,10 +24,10 @@ def _check_backward(mode, ctx, ew, dcost, fwd, **kw):
     for keep_diag in (False, True):
         want = oracle.backward(mode, ctx, ew, dcost, fwd["min_idx"], fwd["norm_idx"], keep_diag=keep_diag, **kw)
         got = g.backward(mode, ctx, ew, dcost, fwd["min_idx"], fwd["norm_idx"], keep_diag=keep_diag, **kw)
-        assert rel_err(got["dunary"], want["dunary"]) < GRAD_RTOL
-        assert rel_err(got["dctx"], want["dctx"]) < GRAD_RTOL
+        assert_grad_close(got["dunary"], want["dunary"], "dunary")
+        assert_grad_close(got["dctx"], want["dctx"], "dctx")   # entry by entry as well as in max-norm
         if ew is not None:
-            assert rel_err(got["dew"], want["dew"]) < GRAD_RTOL
+            assert_grad_close(got["dew"], want["dew"], "dew")
     return got
 
 
@@ -131,7 +131,9 @@ def test_forward_backward_vs_oracle(shape):
     windowed = kind in ("tl1d", "tq1d") and L > 32 and ewk != "neg"
     if windowed:
         # the windowed evaluation may pick another index only among candidates of EQUAL value
-        # (then the values above still agree bit for bit); such ties are rare
+        # (MPLayers/TRWP/TRWP_forward.cu:126-152 fixes the index up to exact ties): every differing
+        # entry is audited by recomputing both candidates in the oracle and comparing their bits
+        audit_index_ties(mode, unary, ctx, ew, D, I, got["min_idx"], want["min_idx"])
         assert mism.mean() < 2e-3
     else:
         assert not mism.any()

@@ -54,3 +54,25 @@ def test_oracle_matches_reference_golden(name):
             else:
                 want[0] = gold["dctx_diag"][0]
         assert rel_err(bwd["dctx"], want) < GRAD_RTOL
+
+
+def test_tie_audit_counts_only_non_ties():
+    """oracle.audit_ties: an index that differs from the oracle's is accepted only when its
+    candidate has exactly the minimum's value.  Integer-valued inputs make exact ties frequent."""
+    rng = np.random.default_rng(0)
+    L = 8
+    unary = rng.integers(0, 3, size=(1, 1, 6, 7, L)).astype(np.float32)
+    ctx = np.minimum(np.arange(L), 2).astype(np.float32)
+    fwd = oracle.forward("TRWP", unary, ctx, None, 4, 2)
+    assert oracle.audit_ties("TRWP", unary, ctx, None, 4, 2, fwd["min_idx"]) == (0, 0)
+    # an arbitrary other index is counted, and reported as a non-tie unless its value happens to tie
+    wrong = fwd["min_idx"].copy()
+    wrong[0, 0, 0, 0, 2, 3, 1] = (wrong[0, 0, 0, 0, 2, 3, 1] + 1) % L
+    seen, bad = oracle.audit_ties("TRWP", unary, ctx, None, 4, 2, wrong)
+    assert seen == 1 and bad in (0, 1)
+    # a constant unary makes every candidate of the first step equal: any index is a tie there
+    flat = np.zeros((1, 1, 3, 4, 4), np.float32)
+    f2 = oracle.forward("ISGMR", flat, np.zeros(4, np.float32), None, 4, 1)
+    alt = np.zeros_like(f2["min_idx"])          # lowest index everywhere
+    seen, bad = oracle.audit_ties("ISGMR", flat, np.zeros(4, np.float32), None, 4, 1, alt)
+    assert bad == 0 and seen == int((alt != f2["min_idx"]).sum()) and seen > 0
