@@ -53,7 +53,24 @@ typedef struct mpl_problem {
                                MPLayers/TRWP_hard_soft does), 0 = skip it (TRWP / ISGMR libs,
                                MPLayers/TRWP/TRWP_backward.cu:111-112) */
   float rho;                /* 0.5 for TRWP, 1 for ISGMR (pytorch/MP_module.py:172) */
+  int32_t context_window;   /* inference with a rank-1 context and more than 32 labels only; else ignored.
+                               0: unknown -- the forward call analyses context and edge weights on the
+                                  device and reads the verdict back, i.e. it waits for `stream` once;
+                                  while `stream` is being captured it does not wait and evaluates all
+                                  L candidates per label instead;
+                               R > 0: the caller states that context[k] is non-decreasing for k < R,
+                                  equal to context[L-1] for k >= R, and that no edge weight is negative
+                                  (what mpl_analyze_context reports) -- no read-back, fully
+                                  asynchronous; a wrong statement gives wrong results;
+                               -1: evaluate all L candidates per label. */
 } mpl_problem;
+
+/* Analyses a rank-1 context (and the edge weights, may be NULL) for mpl_problem::context_window:
+ * *window receives R > 0 if min over the 2R-1 nearest labels plus one global term is exact (see
+ * above), else -1.  Synchronous (waits for `stream`); call it once per context, not per step.
+ * The reference evaluates all L candidates always (MPLayers/TRWP/TRWP_forward.cu:126-152). */
+int mpl_analyze_context(const mpl_problem* p, const float* context, const float* edge_weights,
+                        int32_t* window, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Bytes of device scratch the forward / backward entry points need for `p` (never 0). */
 size_t mpl_forward_workspace_bytes(const mpl_problem* p);
@@ -61,7 +78,10 @@ size_t mpl_backward_workspace_bytes(const mpl_problem* p);
 
 /* TRWP forward.  Replaces TRWP.forward of the reference extension
  * (MPLayers/TRWP/TRWP.cpp:245-283,323-326 -> ForwardCUDA, MPLayers/TRWP/TRWP_forward.cu:378-564).
- *   msg            in/out: must be zero on entry, holds the final messages on exit
+ *   msg            in/out: the messages the first iteration starts from -- zero as the reference
+ *                  allocates them (pytorch/MP_module.py:26), or those of an earlier call (pixels
+ *                  without a predecessor must hold 0: no sweep writes them); holds the final
+ *                  messages on exit
  *   edge_weights   NULL = every weight is 1
  *   msg_min_index, msg_norm_index   both NULL = inference (nothing saved); both non-NULL = training
  *   label_all      NULL = do not save per-iteration labels
@@ -85,9 +105,12 @@ int mpl_trwp_backward(const mpl_problem* p, const float* context, const float* e
                       void* stream);
 
 /* ISGMR (and SGM) forward.  Replaces ISGMR.forward (MPLayers/ISGMR/ISGMR.cpp:300-342,399-404 ->
- * ForwardCUDA, MPLayers/ISGMR/ISGMR_forward.cu:433-665).  msg and msg_update must both be zero on
- * entry; the two buffers are used alternately (no per-iteration copy) and on exit `msg` holds the
- * final messages, `msg_update` those of the iteration before. */
+ * ForwardCUDA, MPLayers/ISGMR/ISGMR_forward.cu:433-665).  The iterations start from the messages in
+ * `msg` (zero as the reference allocates them, or those of an earlier call), whatever the label and
+ * direction counts; msg_update must hold 0 at the pixels without a predecessor (zero it once).  The
+ * two buffers are used alternately instead of being copied every iteration (an odd n_iter costs one
+ * copy at the start); on exit `msg` holds the final messages, `msg_update` those of the iteration
+ * before. */
 int mpl_isgmr_forward(const mpl_problem* p, const float* unary, const float* context,
                       const float* edge_weights, float* msg, float* msg_update, float* cost_final,
                       uint8_t* msg_min_index, uint8_t* msg_norm_index, uint8_t* label_all,
@@ -242,11 +265,28 @@ int mpl_trwp_backward_static(const mpl_problem* p, const float* context, const f
                              const uint8_t* msg_norm_index, float* dunary, float* dcontext,
                              float* dedge_weights, float* dmsg, void* stream);
 
-/* Reads back (synchronously) the device status word of a forward workspace after the forward
- * call that used it: 0 = every kernel ran to completion, otherwise the code of a bounded wait
- * that gave up (101 / 102: staging pipeline of the bulk-copy kernel).  No counterpart in the
- * reference, whose kernels never wait on anything. */
+/* Device status word.  The bulk-copy staged kernels wait on mbarriers; every such wait is bounded
+ * (about a second) and, when it gives up, records a code in the status word of the call's
+ * workspace and lets its warp return, so that the context stays usable.  The word sits at byte
+ * mpl_workspace_status_offset() (= 64) of every workspace, forward or backward; every call clears
+ * it first.  mpl_workspace_status reads it back (synchronously: it waits for the device) after the
+ * call that used the workspace: 0 = every kernel ran to completion, otherwise the code of the wait
+ * that gave up -- forward staging 101 / 102 (labels <= 32), 111 / 112 and 121 / 122 (one CTA per
+ * chain, many labels per lane), 131 / 132 (two labels per lane); backward staging 201 / 202
+ * (labels <= 32), 141 (two labels per lane), 151 (soft TRWP); 901 the self-test below -- and the
+ * call's outputs must be discarded.  mpl_static_scratch_status
+ * does the same for the built-in scratch of mpl_trwp_backward_static on the current device.
+ * mpl_forward_status is the older name of mpl_workspace_status.  No counterpart in the reference,
+ * whose kernels never wait on anything.
+ *
+ * mpl_selftest_bounded_wait launches one warp that waits, with a limit of `limit_cycles` clocks, on
+ * an mbarrier nothing ever arrives at, so that the give-up path (status code 901) can be exercised
+ * without a fault, a trap or an unbounded spin. */
+int mpl_workspace_status(const void* workspace, int32_t* status);
 int mpl_forward_status(const void* workspace, int32_t* status);
+int mpl_static_scratch_status(int32_t* status);
+size_t mpl_workspace_status_offset(void);
+int mpl_selftest_bounded_wait(void* workspace, size_t workspace_bytes, int64_t limit_cycles, void* stream);
 
 /* Stand-alone soft-weighted message ops of the reference's TRWP_hard_soft extension
  * (`soft_weighted_message`, `soft_weighted_message_back`: MPLayers/TRWP_hard_soft/TRWP.cpp:382-419,

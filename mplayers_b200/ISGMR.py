@@ -14,7 +14,7 @@ from .TRWP import _problem
 
 
 def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, cost_final,
-            msg_min_index, msg_norm_index, unary_update, msg_update, label_all):
+            msg_min_index, msg_norm_index, unary_update, msg_update, label_all, context_window=0):
     dev = unary.device
     for t, n in ((unary, "unary"), (context, "context"), (edge_weights, "edge_weights"), (msg, "msg"),
                  (cost_final, "cost_final"), (msg_update, "msg_update")):
@@ -24,7 +24,8 @@ def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weig
         _lib.require(t, n, torch.uint8, dev)
     if msg.dim() != 6 or tuple(unary.shape) != tuple(msg.shape[1:]) or msg.shape != msg_update.shape:
         raise RuntimeError("msg and msg_update must be [D,B,cv,H,W,L] matching unary [B,cv,H,W,L]")
-    prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir, enable_sgm)
+    prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir, enable_sgm,
+                    context_window=context_window)
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_forward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)
@@ -33,7 +34,7 @@ def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weig
             _lib.ptr(msg), _lib.ptr(msg_update), _lib.ptr(cost_final), _lib.ptr(msg_min_index),
             _lib.ptr(msg_norm_index), _lib.ptr(label_all), _lib.ptr(ws), nbytes,
             _lib.stream_ptr(dev)))
-        _lib.check_status(ws)
+        _lib.check_status(ws, "ISGMR.forward")
 
 
 def backward(enable_sgm, rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,
@@ -57,3 +58,4 @@ def backward(enable_sgm, rho, context, edge_weights, dcost_final, msg_min_index,
             _lib.ptr(msg_min_index), _lib.ptr(msg_norm_index), _lib.ptr(dunary), _lib.ptr(dcontext),
             _lib.ptr(dedge_weights), _lib.ptr(dmsg), _lib.ptr(dmsg_update), _lib.ptr(ws), nbytes,
             _lib.stream_ptr(dev)))
+        _lib.check_status(ws, "ISGMR.backward")

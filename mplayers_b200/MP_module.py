@@ -77,7 +77,8 @@ class TRWPFunction(torch.autograd.Function):
         enable_edge_weights = edge_weights is not None
         ew = edge_weights.contiguous() if enable_edge_weights else _empty_f32(unary.device)
         _TRWP.forward(rho, int(n_iter), int(args.enable_min_a_dir), unary, label_context, ew, message,
-                      cost_final, message_index, cost_index, _empty_f32(unary.device), label_all)
+                      cost_final, message_index, cost_index, _empty_f32(unary.device), label_all,
+                      context_window=int(getattr(args, "context_window", 0) or 0))
         ctx.intermediate_results = rho, message_index, cost_index, label_context, ew, enable_edge_weights
         ctx.norm_index_override = _norm_index_override(args, cost_index, n_disp)
         ctx.mark_non_differentiable(label_all)
@@ -122,7 +123,8 @@ class ISGMRFunction(torch.autograd.Function):
         ew = edge_weights.contiguous() if enable_edge_weights else _empty_f32(unary.device)
         _ISGMR.forward(int(args.enable_sgm), rho, int(n_iter), int(args.enable_min_a_dir), unary,
                        label_context, ew, message, cost_final, message_index, cost_index,
-                       _empty_f32(unary.device), message_tmp, label_all)
+                       _empty_f32(unary.device), message_tmp, label_all,
+                       context_window=int(getattr(args, "context_window", 0) or 0))
         ctx.intermediate_results = args.enable_sgm, rho, message_index, cost_index, label_context, ew, \
             enable_edge_weights
         ctx.mark_non_differentiable(label_all)
@@ -218,12 +220,31 @@ class MPModule(torch.nn.Module):
             label_context[self.label_context_diag_loc] = self.args.mpnet_diag_value
         return label_context
 
+    def _context_window(self, label_context, edge_weights):
+        """Inference with a rank-1 context and more than 32 labels: the kernels' windowed evaluation
+        needs to know where the context saturates.  The library can find out per call, but then the
+        call waits for the stream; here the answer is computed once per state of the context
+        parameter (its version counter tells when an optimiser step or an assignment changed it) and
+        handed down as a statement (mpl_problem::context_window).  Only without edge weights: those
+        are new tensors every call, and the statement covers them too."""
+        if self.training or label_context.dim() != 1 or label_context.numel() <= 32 or edge_weights is not None:
+            return 0
+        src = self.label_context
+        key = (id(src), src._version, src.data_ptr(), getattr(self.args, 'mpnet_smoothness_train', None),
+               getattr(self.args, 'mpnet_term_weight', None), getattr(self.args, 'mpnet_diag_value', None))
+        if getattr(self, "_window_key", None) != key:
+            from . import _lib
+            self._window_value = _lib.analyze_context(label_context)
+            self._window_key = key
+        return self._window_value
+
     def forward_native(self, unary, edge_weights=None):
         """The layer in the extension's own layouts, without the two permutes of forward():
         unary [B,cv,H,W,L], edge_weights [D,B,cv,H,W] or None -> (cost_final [B,cv,H,W,L],
         label_context).  Used by glue.mp_on_scores."""
         label_context = self._transformed_label_context()
         self.args.training = self.training
+        self.args.context_window = self._context_window(label_context, edge_weights)
         if self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'}:
             cost_final, _ = ISGMRFunction.apply(unary, label_context, edge_weights, self.args)
         else:
@@ -241,6 +262,7 @@ class MPModule(torch.nn.Module):
         if edge_weights is not None:
             assert unary.size()[-3:-1] == edge_weights.size()[-2:]
         self.args.training = self.training
+        self.args.context_window = self._context_window(label_context, edge_weights)
         if self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'} and self.direction_comm is not None:
             from .direction_sharding import isgmr_direction_sharded
             cost_final = isgmr_direction_sharded(unary, label_context, edge_weights, self.args,

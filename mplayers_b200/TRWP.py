@@ -16,15 +16,19 @@ from . import _lib
 keep_diag = False  # TRWP_hard_soft accumulates dcontext on the diagonal, the TRWP lib does not
 
 
-def _problem(n_iter, msg_shape, context, rho, enable_min_a_dir=0, enable_sgm=0, keep_diag_=0):
+def _problem(n_iter, msg_shape, context, rho, enable_min_a_dir=0, enable_sgm=0, keep_diag_=0,
+             context_window=0):
     n_dir, batch, n_cv, h, w, n_disp = msg_shape
     return _lib.Problem(int(n_iter), n_dir, batch, n_cv, h, w, n_disp,
                         _lib.context_rank(context, n_disp), int(enable_min_a_dir), int(enable_sgm),
-                        int(keep_diag_), float(rho))
+                        int(keep_diag_), float(rho), int(context_window))
 
 
 def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, cost_final,
-            msg_min_index, msg_norm_index, unary_update, label_all):
+            msg_min_index, msg_norm_index, unary_update, label_all, context_window=0):
+    """`context_window` (keyword, not in the reference's signature): see mpl_problem::context_window;
+    0 lets the library find out by itself, which makes an inference call with a rank-1 context and
+    more than 32 labels wait for the stream once."""
     dev = unary.device
     for t, n in ((unary, "unary"), (context, "context"), (edge_weights, "edge_weights"), (msg, "msg"),
                  (cost_final, "cost_final")):
@@ -34,7 +38,7 @@ def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, co
         _lib.require(t, n, torch.uint8, dev)
     if msg.dim() != 6 or tuple(unary.shape) != tuple(msg.shape[1:]):
         raise RuntimeError("msg must be [D,B,cv,H,W,L] matching unary [B,cv,H,W,L]")
-    prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir)
+    prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir, context_window=context_window)
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_forward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)
@@ -42,7 +46,7 @@ def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, co
             ctypes.byref(prob), _lib.ptr(unary), _lib.ptr(context), _lib.ptr(edge_weights),
             _lib.ptr(msg), _lib.ptr(cost_final), _lib.ptr(msg_min_index), _lib.ptr(msg_norm_index),
             _lib.ptr(label_all), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
-        _lib.check_status(ws)
+        _lib.check_status(ws, "TRWP.forward")
 
 
 def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index, dunary,
@@ -66,6 +70,7 @@ def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_in
             ctypes.byref(prob), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(dcost_final),
             _lib.ptr(msg_min_index), _lib.ptr(msg_norm_index), _lib.ptr(dunary), _lib.ptr(dcontext),
             _lib.ptr(dedge_weights), _lib.ptr(dmsg), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+        _lib.check_status(ws, "TRWP.backward")
 
 
 def forward_soft(rho, n_iter, unary, context, edge_weights, msg, msg_edge_label, msg_norm_index,
@@ -89,6 +94,7 @@ def forward_soft(rho, n_iter, unary, context, edge_weights, msg, msg_edge_label,
             ctypes.byref(prob), _lib.ptr(unary), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(msg),
             _lib.ptr(cost_final), _lib.ptr(msg_edge_label), _lib.ptr(msg_norm_index), _lib.ptr(label_all),
             _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+        _lib.check_status(ws, "TRWP.forward_soft")
 
 
 def backward_soft(rho, dcost_final, context, edge_weights, msg_edge_label, msg_norm_index, dunary,
@@ -113,6 +119,7 @@ def backward_soft(rho, dcost_final, context, edge_weights, msg_edge_label, msg_n
             ctypes.byref(prob), _lib.ptr(context), _lib.ptr(edge_weights), _lib.ptr(dcost_final),
             _lib.ptr(msg_edge_label), _lib.ptr(msg_norm_index), _lib.ptr(dunary), _lib.ptr(dcontext),
             _lib.ptr(dedge_weights), _lib.ptr(dmsg), _lib.ptr(ws), nbytes, _lib.stream_ptr(dev)))
+        _lib.check_status(ws, "TRWP.backward_soft")
 
 
 def soft_weighted_message(message, message_soft_sum_norm, message_soft_sum_min_ind):

@@ -6,6 +6,7 @@ machine without a CUDA device.
 """
 import ctypes
 import os
+import threading
 
 import torch
 
@@ -19,7 +20,8 @@ class Problem(ctypes.Structure):
     """struct mpl_problem of include/mplayers_b200.h"""
     _fields_ = [(n, ctypes.c_int32) for n in
                 ("n_iter", "n_dir", "batch", "n_cv", "height", "width", "n_disp", "context_rank",
-                 "enable_min_a_dir", "enable_sgm", "keep_diag")] + [("rho", ctypes.c_float)]
+                 "enable_min_a_dir", "enable_sgm", "keep_diag")] + [("rho", ctypes.c_float),
+                                                                   ("context_window", ctypes.c_int32)]
 
 
 _lib = None
@@ -39,6 +41,8 @@ def lib():
         L.mpl_forward_workspace_bytes.argtypes = [pp]
         L.mpl_backward_workspace_bytes.restype = sz
         L.mpl_backward_workspace_bytes.argtypes = [pp]
+        L.mpl_analyze_context.restype = ctypes.c_int
+        L.mpl_analyze_context.argtypes = [pp, vp, vp, ctypes.POINTER(ctypes.c_int32), vp, sz, vp]
         L.mpl_trwp_forward.restype = ctypes.c_int
         L.mpl_trwp_forward.argtypes = [pp] + [vp] * 9 + [sz, vp]
         L.mpl_trwp_backward.restype = ctypes.c_int
@@ -99,6 +103,13 @@ def lib():
         L.mpl_static_scratch_bytes.restype = sz
         L.mpl_forward_status.restype = ctypes.c_int
         L.mpl_forward_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32)]
+        L.mpl_workspace_status.restype = ctypes.c_int
+        L.mpl_workspace_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32)]
+        L.mpl_static_scratch_status.restype = ctypes.c_int
+        L.mpl_static_scratch_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
+        L.mpl_workspace_status_offset.restype = sz
+        L.mpl_selftest_bounded_wait.restype = ctypes.c_int
+        L.mpl_selftest_bounded_wait.argtypes = [vp, sz, ctypes.c_int64, vp]
         L.mpl_last_error.restype = ctypes.c_char_p
         L.mpl_kernel_launches.restype = ctypes.c_int64
         L.mpl_version.restype = ctypes.c_int32
@@ -115,16 +126,98 @@ def check(rc):
         raise RuntimeError("mplayers_b200: " + lib().mpl_last_error().decode())
 
 
-def check_status(ws):
-    """With MPL_CHECK_STATUS=1 in the environment: wait for the forward call that used workspace
-    `ws` and raise if a kernel recorded that one of its bounded waits gave up.  Off by default
-    because it synchronises."""
-    if os.environ.get("MPL_CHECK_STATUS") != "1":
+class DeviceStatusError(RuntimeError):
+    """A kernel recorded that one of its bounded waits gave up; the outputs of that call are invalid."""
+
+
+_STATUS_WHAT = {101: "forward staging", 102: "forward staging", 111: "forward staging", 112: "forward staging",
+                121: "forward staging", 122: "forward staging", 131: "forward staging", 132: "forward staging",
+                141: "backward staging", 151: "backward staging", 201: "backward staging", 202: "backward staging",
+                901: "self-test wait"}
+
+
+def _raise_status(code, what):
+    raise DeviceStatusError("mplayers_b200: device status %d after %s (%s: a bounded wait timed out; the "
+                            "outputs of that call are invalid)" % (code, what, _STATUS_WHAT.get(code, "unknown")))
+
+
+class _StatusWatch:
+    """Deferred check of the device status words.  After every call the word is copied to pinned
+    host memory on the call's stream, without waiting; the copies that have completed are inspected
+    at the next library call (and by `poll_status`), so a wait that gave up surfaces as an exception
+    one call later instead of passing silently, and no call synchronises for it."""
+    SLOTS = 64
+
+    def __init__(self):
+        self.host = None
+        self.pending = []   # (slot, event, what)
+        self.free = list(range(self.SLOTS))
+        self.lock = threading.Lock()   # ranks may be threads of one process
+
+    def watch(self, ws, what):
+        with self.lock:
+            self._watch(ws, what)
+
+    def poll(self, wait=False, wait_oldest=False):
+        with self.lock:
+            self._poll(wait, wait_oldest)
+
+    def _watch(self, ws, what):
+        if self.host is None:
+            self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self._poll()
+        if not self.free:           # every slot in flight: wait for the oldest
+            self._poll(wait_oldest=True)
+        slot = self.free.pop()
+        off = int(lib().mpl_workspace_status_offset())
+        self.host[slot:slot + 1].copy_(ws[off:off + 4].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(ws.device))
+        self.pending.append((slot, ev, what))
+
+    def _poll(self, wait=False, wait_oldest=False):
+        keep, bad = [], None
+        for i, (slot, ev, what) in enumerate(self.pending):
+            if wait or (wait_oldest and i == 0):
+                ev.synchronize()
+            if ev.query():
+                code = int(self.host[slot])
+                self.free.append(slot)
+                if code != 0 and bad is None:
+                    bad = (code, what)
+            else:
+                keep.append((slot, ev, what))
+        self.pending = keep
+        if bad is not None:
+            _raise_status(*bad)
+
+
+_watch = _StatusWatch()
+
+
+def poll_status(wait=False):
+    """Raises DeviceStatusError if an earlier call's kernels recorded a wait that gave up.  With
+    wait=True it first waits for every call watched so far (a natural place: where the training
+    loop synchronises anyway, e.g. when it reads the loss)."""
+    _watch.poll(wait=wait)
+
+
+def check_status(ws, what="a forward call"):
+    """Status word of the call that just used workspace `ws`.  MPL_CHECK_STATUS=1: wait for the call
+    and raise at once if a bounded wait gave up (synchronises; what the tests run with).
+    MPL_CHECK_STATUS=0: no check.  Default: deferred check, see _StatusWatch."""
+    mode = os.environ.get("MPL_CHECK_STATUS", "")
+    if mode == "0":
         return
-    st = ctypes.c_int32(0)
-    check(lib().mpl_forward_status(ctypes.c_void_p(ws.data_ptr()), ctypes.byref(st)))
-    if st.value != 0:
-        raise RuntimeError("mplayers_b200: device status %d (a staging wait timed out)" % st.value)
+    if mode == "1":
+        st = ctypes.c_int32(0)
+        check(lib().mpl_workspace_status(ctypes.c_void_p(ws.data_ptr()), ctypes.byref(st)))
+        if st.value != 0:
+            _raise_status(st.value, what)
+        return
+    if torch.cuda.is_current_stream_capturing():
+        return  # a captured call cannot be watched from the host; read the word after the replay
+    _watch.watch(ws, what)
 
 
 def ptr(t):
@@ -169,6 +262,27 @@ def context_rank(context, n_disp):
     if context.numel() < need or context.size(-1) != n_disp:
         raise RuntimeError("context shape %s does not match n_disp=%d" % (tuple(context.shape), n_disp))
     return rank
+
+
+def analyze_context(context, edge_weights=None, n_pixels=0, n_dir=2):
+    """mpl_problem::context_window for a rank-1 context [L] (and, optionally, edge weights
+    [D,B,cv,H,W]): R > 0 if the windowed evaluation is exact, else -1.  Waits for the device."""
+    if context.dim() != 1:
+        return -1
+    dev = context.device
+    L = context.numel()
+    if edge_weights is not None and edge_weights.numel():
+        n_dir, b, cv, h, w = edge_weights.shape
+    else:
+        edge_weights, b, cv, h, w = None, 1, 1, 1, max(int(n_pixels), 1)
+    prob = Problem(1, int(n_dir), b, cv, h, w, L, 1, 0, 0, 0, 1.0, 0)
+    out = ctypes.c_int32(-1)
+    with torch.cuda.device(dev):
+        n = lib().mpl_forward_workspace_bytes(ctypes.byref(prob))
+        ws = workspace(n, dev)
+        check(lib().mpl_analyze_context(ctypes.byref(prob), ptr(context.contiguous()), ptr(edge_weights),
+                                        ctypes.byref(out), ptr(ws), n, stream_ptr(dev)))
+    return int(out.value)
 
 
 def workspace(nbytes, device):

@@ -167,7 +167,7 @@ void fill_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, const
   fp.ctx = ctx;
   fp.ew = ew;
   fp.info = static_cast<const mpl::CtxInfo*>(workspace);
-  fp.status = reinterpret_cast<int*>(static_cast<char*>(workspace) + 64);
+  fp.status = reinterpret_cast<int*>(static_cast<char*>(workspace) + 64);  // kStatusOffset
   fp.H = p->height;
   fp.W = p->width;
   fp.L = p->n_disp;
@@ -187,6 +187,17 @@ void set_dirs(mpl::FwdParams& fp, int dir0, int ndirs) {
     fp.chain_off[i + 1] = fp.chain_off[i] + mpl::make_geom(dir0 + i, fp.H, fp.W).n_chains * fp.nimg;
 }
 
+// Verdict of the device-side analysis (launch_analyze, in `workspace`): *window = R > 0 if the
+// windowed evaluation is exact, else -1.  Waits for the stream.
+int read_window(const void* workspace, bool has_weights, int* window, cudaStream_t st) {
+  mpl::CtxInfo hi;
+  MPL_CUDA(cudaMemcpyAsync(&hi, workspace, sizeof(hi), cudaMemcpyDeviceToHost, st));
+  MPL_CUDA(cudaStreamSynchronize(st));
+  const bool ew_ok = !has_weights || hi.ew_min_bits >= 0;  // order bits: negative <=> negative float
+  *window = (hi.windowed && ew_ok && hi.R > 0) ? hi.R : -1;
+  return MPL_OK;
+}
+
 // Fills the sweep parameters, clears the status word and runs the context / edge-weight analysis
 // (and, for inference with a rank-1 context, reads its verdict back: one small synchronising copy).
 int prepare_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, const float* unary,
@@ -198,14 +209,24 @@ int prepare_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, con
   MPL_CUDA(mpl::launch_analyze(context, L, p->context_rank, edge_weights, d.npix * D,
                                static_cast<mpl::CtxInfo*>(workspace), st));
   if (p->context_rank == 1 && L > 32 && !train) {
-    // Inference with a rank-1 context: the choice of the wide windowed kernel is made on the host,
-    // which costs one small device-to-host copy (the call synchronises with its stream here).
-    mpl::CtxInfo hi;
-    MPL_CUDA(cudaMemcpyAsync(&hi, workspace, sizeof(hi), cudaMemcpyDeviceToHost, st));
-    MPL_CUDA(cudaStreamSynchronize(st));
-    const float ew_min = hi.ew_min_bits >= 0 ? 1.f : -1.f;  // order bits: negative <=> negative float
-    fp.host_windowed = hi.windowed && (edge_weights == nullptr || ew_min >= 0.f);
-    fp.host_R = hi.R;
+    // Inference with a rank-1 context: the wide windowed kernel is chosen on the host.  With a
+    // statement from the caller (mpl_problem::context_window) nothing is read back; without one the
+    // verdict of the device-side analysis is copied to the host, which waits for the stream --
+    // unless the stream is being captured, where waiting is not allowed: then all candidates are
+    // evaluated.
+    if (p->context_window > 0) {
+      fp.host_windowed = 1;
+      fp.host_R = p->context_window;
+    } else if (p->context_window == 0) {
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      MPL_CUDA(cudaStreamIsCapturing(st, &cap));
+      if (cap == cudaStreamCaptureStatusNone) {
+        int w = -1;
+        if (int rc = read_window(workspace, edge_weights != nullptr, &w, st)) return rc;
+        fp.host_windowed = w > 0;
+        fp.host_R = w > 0 ? w : 0;
+      }
+    }
   }
   return MPL_OK;
 }
@@ -239,6 +260,10 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
     const bool last_writes_msg_when_first_writes_msg = (p->n_iter % 2) == 1;
     wr = last_writes_msg_when_first_writes_msg ? msg : msg_update;
     rd = wr == msg ? msg_update : msg;
+    // The iterations start from the messages in `msg`, as in the reference.  With an odd iteration
+    // count the first sweep writes `msg`, so its input moves to `msg_update` first.
+    if (rd != msg && p->n_iter > 0)
+      MPL_CUDA(cudaMemcpyAsync(msg_update, msg, (size_t)D * d.slice * sizeof(float), cudaMemcpyDeviceToDevice, st));
   }
   for (int it = 0; it < p->n_iter; ++it) {
     fp.min_idx = train ? msg_min_index + (long long)it * D * d.slice : nullptr;
@@ -248,14 +273,15 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
     if (isgmr) {
       // Every direction reads the previous iteration's messages.  Their sum with the unaries is
       // formed once (in `cost_final`, which is otherwise unused until the end) so that a sweep
-      // stages three arrays instead of D+1; in the first iteration the messages are zero.
+      // stages three arrays instead of D+1.  The first iteration forms it too: the messages the
+      // caller passes in count, as they do in the reference and in the other path.
       // With few labels and directions the sweep sums U + sum_k M_k itself faster than a separate
       // pass over all messages does (measured 5.13 -> 4.99 ms on 2x512x512, L = 21, D = 4); with
       // 256 labels the extra staged rows cost more than the pass (28.4 -> 29.2 ms).
       const bool use_agg = !(L <= 32 && D <= 4);
       fp.agg = use_agg ? 1 : 0;
       fp.unary = unary;
-      if (it > 0 && use_agg) {
+      if (use_agg) {
         MPL_CUDA(mpl::launch_aggregate(unary, rd, cost_final, nullptr, d.npix, L, D, d.slice, 1.f, 0, st));
         fp.unary = cost_final;
       }
@@ -283,6 +309,12 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
                                  p->enable_min_a_dir, st));
   return MPL_OK;
 }
+
+// Layout of every workspace (forward, backward, the built-in scratch): bytes [0, 64) context
+// analysis, [64, 68) the device status word, [256, ...) the backward's partial label-context tables.
+constexpr size_t kStatusOffset = 64, kTablesOffset = 256;
+inline float* ws_tables(void* workspace) { return reinterpret_cast<float*>(static_cast<char*>(workspace) + kTablesOffset); }
+inline int* ws_status(void* workspace) { return reinterpret_cast<int*>(static_cast<char*>(workspace) + kStatusOffset); }
 
 void fill_backward(mpl::BwdParams& bp, const mpl_problem* p, const Dims& d, const float* context,
                    const float* edge_weights, float* dunary, float* part, int n_slots, int cp, int* status) {
@@ -324,7 +356,7 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int D = p->n_dir, L = p->n_disp;
   const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg);
-  float* part = static_cast<float*>(workspace);
+  float* part = ws_tables(workspace);
   MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
 
   const float factor = (isgmr && p->enable_sgm) ? (float)D : 1.f;
@@ -338,7 +370,7 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced
   float* Y = isgmr ? dmsg : dmsg;         // gradients of the messages the sweeps read
   MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp == 1, st));
-  int* status = reinterpret_cast<int*>(part + (size_t)n_slots * d.ctx_elems);
+  int* status = ws_status(workspace);
   MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
 
   mpl::BwdParams bp{};
@@ -375,6 +407,25 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
 
 extern "C" {
 
+int mpl_analyze_context(const mpl_problem* p, const float* context, const float* edge_weights,
+                        int32_t* window, void* workspace, size_t workspace_bytes, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (!context || !window) return fail(MPL_ERR_INVALID, "NULL pointer");
+  if (!workspace || workspace_bytes < mpl_forward_workspace_bytes(p))
+    return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
+                mpl_forward_workspace_bytes(p));
+  *window = -1;
+  if (p->context_rank != 1 || p->n_disp <= 32) return MPL_OK;  // only those sweeps have a windowed form
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MPL_CUDA(mpl::launch_analyze(context, p->n_disp, 1, edge_weights, d.npix * p->n_dir,
+                               static_cast<mpl::CtxInfo*>(workspace), st));
+  int w = -1;
+  if (int rc = read_window(workspace, edge_weights != nullptr, &w, st)) return rc;
+  *window = w;
+  return MPL_OK;
+}
+
 size_t mpl_forward_workspace_bytes(const mpl_problem* p) {
   (void)p;
   return 256;
@@ -384,8 +435,7 @@ size_t mpl_backward_workspace_bytes(const mpl_problem* p) {
   Dims d;
   if (validate(p, &d) != MPL_OK) return 256;
   const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
-  const size_t b = (size_t)n_slots * d.ctx_elems * sizeof(float) + 64;  // tables + status word
-  return b < 256 ? 256 : b;
+  return kTablesOffset + (size_t)n_slots * d.ctx_elems * sizeof(float);  // header + tables
 }
 
 int mpl_trwp_forward(const mpl_problem* p, const float* unary, const float* context,
@@ -496,8 +546,8 @@ int mpl_isgmr_backward_directions(const mpl_problem* p, int32_t dir_first, int32
                 mpl_backward_workspace_bytes(p));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
-  float* part = static_cast<float*>(workspace);
-  int* status = reinterpret_cast<int*>(part + (size_t)n_slots * d.ctx_elems);
+  float* part = ws_tables(workspace);
+  int* status = ws_status(workspace);
   if (clear_workspace) {
     MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
     MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
@@ -538,7 +588,7 @@ int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t wo
     return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
                 mpl_backward_workspace_bytes(p));
   const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
-  MPL_CUDA(mpl::launch_dctx_reduce(static_cast<float*>(workspace), n_slots, p->n_disp, p->context_rank,
+  MPL_CUDA(mpl::launch_dctx_reduce(ws_tables(workspace), n_slots, p->n_disp, p->context_rank,
                                    p->keep_diag, dcontext, static_cast<cudaStream_t>(stream)));
   return MPL_OK;
 }
@@ -602,8 +652,8 @@ int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const flo
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int D = p->n_dir, L = p->n_disp;
   const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg);
-  float* part = static_cast<float*>(workspace);
-  int* status = reinterpret_cast<int*>(part + (size_t)n_slots * d.ctx_elems);
+  float* part = ws_tables(workspace);
+  int* status = ws_status(workspace);
   MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
   MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
   // C + P bookkeeping (BwdParams::cp_scheme == 1): C in dunary, P_k in dmsg
@@ -795,9 +845,46 @@ int mpl_edge_weights(int32_t mode, const float* image, int32_t batch, int32_t ch
   return MPL_OK;
 }
 
-int mpl_forward_status(const void* workspace, int32_t* status) {
+int mpl_workspace_status(const void* workspace, int32_t* status) {
   if (!workspace || !status) return fail(MPL_ERR_INVALID, "NULL pointer");
-  MPL_CUDA(cudaMemcpy(status, static_cast<const char*>(workspace) + 64, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  MPL_CUDA(cudaMemcpy(status, static_cast<const char*>(workspace) + kStatusOffset, sizeof(int32_t),
+                      cudaMemcpyDeviceToHost));
+  return MPL_OK;
+}
+
+int mpl_forward_status(const void* workspace, int32_t* status) { return mpl_workspace_status(workspace, status); }
+
+size_t mpl_workspace_status_offset(void) { return kStatusOffset; }
+
+}  // extern "C"
+
+namespace {
+// One warp waits on an mbarrier that nothing ever arrives at, with a limit of `limit_cycles`
+// clocks: the wait must give up, record its code and let the kernel return.
+__global__ void selftest_wait_kernel(int* status, long long limit_cycles) {
+  __shared__ unsigned long long bar;
+  if (threadIdx.x == 0) {
+    mpl::mbar_init(&bar, 1);
+    mpl::mbar_fence_init();
+  }
+  __syncwarp();
+  if (!mpl::mbar_wait(&bar, 0, limit_cycles)) {
+    if (threadIdx.x == 0) atomicExch(status, 901);
+  }
+}
+}  // namespace
+
+extern "C" {
+
+int mpl_selftest_bounded_wait(void* workspace, size_t workspace_bytes, int64_t limit_cycles, void* stream) {
+  if (!workspace || workspace_bytes < 256) return fail(MPL_ERR_INVALID, "workspace of at least 256 bytes needed");
+  if (limit_cycles < 1 || limit_cycles > 2000000000ll)
+    return fail(MPL_ERR_INVALID, "limit_cycles=%lld outside 1..2e9", (long long)limit_cycles);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MPL_CUDA(cudaMemsetAsync(ws_status(workspace), 0, sizeof(int), st));
+  selftest_wait_kernel<<<1, 32, 0, st>>>(ws_status(workspace), (long long)limit_cycles);
+  mpl::count_launch();
+  MPL_CUDA(cudaGetLastError());
   return MPL_OK;
 }
 
@@ -841,6 +928,13 @@ int mpl_trwp_backward_static(const mpl_problem* p, const float* context, const f
   // backward_common clears the part of the scratch it uses (partial tables and status word)
   return backward_common(false, p, context, edge_weights, dcost_final, msg_min_index, msg_norm_index, dunary,
                          dcontext, dedge_weights, dmsg, nullptr, scratch, MPL_STATIC_SCRATCH_BYTES, stream);
+}
+
+int mpl_static_scratch_status(int32_t* status) {
+  if (!status) return fail(MPL_ERR_INVALID, "NULL pointer");
+  void* ptr = nullptr;
+  MPL_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+  return mpl_workspace_status(ptr, status);
 }
 
 const char* mpl_last_error(void) { return g_err.c_str(); }

@@ -213,8 +213,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, u
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-// Waits for the phase with the given parity; gives up after about a second and returns false.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+// Waits for the phase with the given parity; gives up after `limit` clocks (default: about a second)
+// and returns false.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
+                                          long long limit = 2000000000ll) {
   const unsigned a = smem_u32(bar);
   const long long t0 = clock64();
   for (;;) {
@@ -227,7 +229,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
         : "r"(a), "r"(parity)
         : "memory");
     if (ok) return true;
-    if (clock64() - t0 > 2000000000ll) return false;
+    if (clock64() - t0 > limit) return false;
   }
 }
 // Tensor maps of the vertical-direction kernels (2-D tiled TMA: one copy brings kTK image rows of

@@ -33,14 +33,12 @@ __device__ __forceinline__ ColumnStats column_stats(const float* __restrict__ co
 
 __global__ void soft_weighted_message_kernel(const float* __restrict__ msg, int L, float* __restrict__ norm,
                                              uint8_t* __restrict__ min_ind) {
-  __shared__ float soft_s[256];
   __shared__ float best_v[8];
   __shared__ int best_i[8];
   const long long t = blockIdx.x;
   const int c = threadIdx.x;
   float soft = INFINITY;
   if (c < L) soft = column_stats(msg + t * L * L + c, L).soft;
-  soft_s[c] = soft;
   // argmin over c, highest index among equal values
   float v = soft;
   int idx = c < L ? c : -1;

@@ -81,7 +81,7 @@ class CudaBackend:
                 ctypes.byref(prob), d0, dc, _lib.ptr(aggregate), _lib.ptr(context), _lib.ptr(ew),
                 _lib.ptr(msg_read), _lib.ptr(msg_write), _lib.ptr(min_idx), _lib.ptr(norm_idx),
                 _lib.ptr(ws), n, _lib.stream_ptr(dev)))
-            _lib.check_status(ws)
+            _lib.check_status(ws, "ISGMR forward (direction-sharded)")
 
     def sum_directions(self, prob, d0, dc, base, factor, fields, out):
         dev = out.device
@@ -102,6 +102,7 @@ class CudaBackend:
                 ctypes.byref(prob), d0, dc, _lib.ptr(context), _lib.ptr(ew), _lib.ptr(dmsg_update),
                 _lib.ptr(min_idx), _lib.ptr(norm_idx), _lib.ptr(scatter), _lib.ptr(dew), _lib.ptr(ws),
                 ws.numel(), int(clear), _lib.stream_ptr(dev)))
+            _lib.check_status(ws, "ISGMR backward (direction-sharded)")
 
     def combine(self, prob, d0, dc, scatter_total, scatter, dmsg_update, dunary):
         dev = scatter_total.device

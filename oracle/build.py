@@ -26,7 +26,9 @@ REF_OUT = os.path.join(HERE, "_ref")
 
 
 def reference_dir():
-    return os.environ.get("MPL_REFERENCE_DIR", "/root/reference")
+    """The reference checkout: $MPL_REFERENCE_DIR, else a directory `reference` next to this repository."""
+    default = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return os.environ.get("MPL_REFERENCE_DIR", default)
 
 
 def _cpu_has_fma():

@@ -59,8 +59,9 @@ def _problem(mode, unary, n_dir, n_iter, ctx, rho, enable_sgm, enable_min_a_dir,
 
 
 def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=True,
-            save_labels=False, enable_sgm=False, enable_min_a_dir=False, n_threads=None):
-    """Returns dict(cost, msg, min_idx, norm_idx, label_all)."""
+            save_labels=False, enable_sgm=False, enable_min_a_dir=False, n_threads=None, msg_init=None):
+    """Returns dict(cost, msg, min_idx, norm_idx, label_all).  msg_init: messages to start from
+    (default zeros, as the reference allocates them)."""
     unary = np.ascontiguousarray(unary, np.float32)
     ctx = np.ascontiguousarray(ctx, np.float32)
     b, cv, h, w, l = unary.shape
@@ -70,6 +71,8 @@ def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=Tr
     assert edge_weights.shape == (n_dir, b, cv, h, w)
     prob = _problem(mode, unary, n_dir, n_iter, ctx, rho, enable_sgm, enable_min_a_dir, 0, n_threads)
     msg = np.zeros((n_dir, b, cv, h, w, l), np.float32)
+    if msg_init is not None:
+        msg[...] = msg_init
     cost = np.zeros_like(unary)
     mi = np.zeros((n_iter, n_dir, b, cv, h, w, l), np.uint8) if training else None
     ni = np.zeros((n_iter, n_dir, b, cv, h, w), np.uint8) if training else None

@@ -23,7 +23,9 @@ sys.path.insert(0, ROOT)
 import terms_cases  # noqa: E402
 from oracle import ref_terms  # noqa: E402
 
-REF = os.environ.get("MPL_REFERENCE_DIR", "/root/reference")
+# the reference checkout: $MPL_REFERENCE_DIR, else a directory `reference` next to this repository
+REF = os.environ.get("MPL_REFERENCE_DIR",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"))
 
 
 def main():

@@ -11,7 +11,7 @@ def _dev(a, dtype=torch.float32):
 
 
 def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=True,
-            save_labels=False, enable_sgm=False, enable_min_a_dir=False):
+            save_labels=False, enable_sgm=False, enable_min_a_dir=False, msg_init=None, context_window=0):
     if rho is None:
         rho = 0.5 if mode == "TRWP" else 1.0
     u = _dev(unary)
@@ -20,17 +20,18 @@ def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=Tr
     e0 = torch.empty(0, device="cuda")
     e8 = torch.empty(0, dtype=torch.uint8, device="cuda")
     ew = _dev(edge_weights) if edge_weights is not None else e0
-    msg = torch.zeros(n_dir, b, cv, h, w, l, device="cuda")
+    msg = torch.zeros(n_dir, b, cv, h, w, l, device="cuda") if msg_init is None else _dev(msg_init)
     cost = torch.full((b, cv, h, w, l), float("nan"), device="cuda")
     mi = torch.zeros(n_iter, n_dir, b, cv, h, w, l, dtype=torch.uint8, device="cuda") if training else e8
     ni = torch.zeros(n_iter, n_dir, b, cv, h, w, dtype=torch.uint8, device="cuda") if training else e8
     lab = torch.zeros(n_iter, b, cv, h, w, dtype=torch.uint8, device="cuda") if save_labels else e8
     if mode == "TRWP":
-        TRWP.forward(rho, n_iter, int(enable_min_a_dir), u, c, ew, msg, cost, mi, ni, e0, lab)
+        TRWP.forward(rho, n_iter, int(enable_min_a_dir), u, c, ew, msg, cost, mi, ni, e0, lab,
+                     context_window=context_window)
     else:
         mu = torch.zeros_like(msg)
         ISGMR.forward(int(enable_sgm), rho, n_iter, int(enable_min_a_dir), u, c, ew, msg, cost, mi, ni,
-                      e0, mu, lab)
+                      e0, mu, lab, context_window=context_window)
     torch.cuda.synchronize()
     return dict(cost=cost.cpu().numpy(), msg=msg.cpu().numpy(),
                 min_idx=mi.cpu().numpy() if training else None,

@@ -30,7 +30,7 @@ def test_exports_every_declared_symbol():
 
 def _prob(**kw):
     d = dict(n_iter=2, n_dir=4, batch=1, n_cv=1, height=8, width=9, n_disp=21, context_rank=2,
-             enable_min_a_dir=0, enable_sgm=0, keep_diag=0, rho=0.5)
+             enable_min_a_dir=0, enable_sgm=0, keep_diag=0, rho=0.5, context_window=0)
     d.update(kw)
     return _lib.Problem(*[d[n] for n, _ in _lib.Problem._fields_])
 
@@ -68,9 +68,10 @@ def test_workspace_sizes():
     lib = _lib.lib()
     p = _prob(batch=2, height=512, width=512)
     assert lib.mpl_forward_workspace_bytes(ctypes.byref(p)) >= 16
-    # one partial 21x21 table per chain of all four directions (4 x 2 images x 512 rows; an ISGMR
-    # launch covers every direction at once) + the status word
-    assert lib.mpl_backward_workspace_bytes(ctypes.byref(p)) == 4096 * 441 * 4 + 64
+    # a 256-byte header (context analysis, status word at byte 64) + one partial 21x21 table per chain
+    # of all four directions (4 x 2 images x 512 rows; an ISGMR launch covers every direction at once)
+    assert lib.mpl_backward_workspace_bytes(ctypes.byref(p)) == 256 + 4096 * 441 * 4
+    assert lib.mpl_workspace_status_offset() == 64
 
 
 @pytest.mark.parametrize("hw", [(1, 1), (1, 7), (5, 1), (2, 3), (6, 7), (13, 4)])
@@ -128,7 +129,8 @@ def test_label_context_builder_matches_reference_when_present(n, mode, trunc, lo
     from mplayers_b200.label_context import create_label_context
     lc, where, diag = create_label_context(_args(n, mode, None, trunc, loc), enable_symmetric=sym)
     assert lc.shape == ((n, n) if n == 21 else (n,))
-    ref_dir = os.environ.get("MPL_REFERENCE_DIR", "/root/reference")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref_dir = os.environ.get("MPL_REFERENCE_DIR", os.path.join(os.path.dirname(repo), "reference"))
     path = os.path.join(ref_dir, "utils", "label_context.py")
     if not os.path.exists(path):
         pytest.skip("reference checkout not present")

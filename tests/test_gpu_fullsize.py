@@ -27,7 +27,7 @@ def _run(cfg, edge=True, train=True):
 
 
 def test_segmentation_config_properties():
-    """BASELINE config 4 per GPU: TRWP fwd+bwd, 2 x 512 x 512, 21 labels, 4 directions, 5 iterations."""
+    """configuration 4 per GPU: TRWP fwd+bwd, 2 x 512 x 512, 21 labels, 4 directions, 5 iterations."""
     from mplayers_b200 import TRWP, synthetic
     cfg = synthetic.config4_segmentation()
     cfg["unary"][1] = cfg["unary"][0]                 # two identical samples ...
@@ -67,7 +67,7 @@ def test_segmentation_config_properties():
 
 
 def test_stereo_config_windowed_equals_dense():
-    """BASELINE config 2 shapes (192 labels, truncated linear): the windowed multi-label kernel and
+    """configuration 2 shapes (192 labels, truncated linear): the windowed multi-label kernel and
     the dense evaluation (same function given as a symmetric 192 x 192 matrix) must agree bit for
     bit; checked on a crop, plus full-size sanity of the windowed path."""
     from mplayers_b200 import TRWP, synthetic

@@ -73,3 +73,40 @@ def test_forward_backward_step_replays_from_a_cuda_graph(mode, shape, monkeypatc
     for k in want:
         assert torch.equal(got[k], t[k]), k
     assert not torch.equal(got["cost"], want["cost"])   # the replay really used the new inputs
+
+
+@pytest.mark.parametrize("window", [0, 2])
+def test_rank1_inference_is_capturable(window, monkeypatch):
+    """Inference with a rank-1 context and more than 32 labels.  Outside a capture the library may read
+    its context analysis back (it waits for the stream); inside one it must not: with
+    context_window = 0 it evaluates all candidates instead, with the caller's statement
+    (context_window = R) it runs the windowed kernels.  Either way the captured call replays to the
+    eager result."""
+    from mplayers_b200 import TRWP
+    monkeypatch.setenv("MPL_CHECK_STATUS", "0")
+    L, D, I, H, W = 96, 4, 2, 12, 16
+    g = torch.Generator().manual_seed(5)
+    unary = torch.randn(1, 1, H, W, L, generator=g).cuda()
+    ctx = torch.clamp(torch.arange(L, dtype=torch.float32), max=2.0).cuda()
+    none, lab = torch.empty(0, device="cuda"), torch.empty(0, dtype=torch.uint8, device="cuda")
+    msg, cost = torch.zeros(D, 1, 1, H, W, L, device="cuda"), torch.zeros(1, 1, H, W, L, device="cuda")
+
+    def run():
+        msg.zero_()
+        TRWP.forward(0.5, I, 0, unary, ctx, none, msg, cost, lab, lab, none, lab, context_window=window)
+
+    run()
+    torch.cuda.synchronize()
+    want = cost.clone()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run()
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        run()
+    cost.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(cost, want)

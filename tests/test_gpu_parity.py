@@ -228,3 +228,45 @@ def test_wide_inference_kernel(mode, D, H, W, L, kind, ewk):
     assert np.array_equal(got["cost"], want["cost"])
     assert np.array_equal(got["msg"], want["msg"])
     assert np.array_equal(got["label_all"], want["label_all"])
+
+
+@pytest.mark.parametrize("mode,D,L,I", [
+    ("ISGMR", 8, 64, 2), ("ISGMR", 8, 64, 3),   # aggregate path (many labels / directions), even and odd iteration counts
+    ("ISGMR", 4, 21, 2), ("ISGMR", 4, 21, 3),   # every slice staged
+    ("TRWP", 4, 21, 2), ("TRWP", 8, 40, 1),
+])
+def test_warm_start_from_given_messages(mode, D, L, I):
+    """The iterations start from the messages the caller passes in `msg` (MPLayers/TRWP/TRWP_forward.cu:
+    440-518 and MPLayers/ISGMR/ISGMR_forward.cu:506-622 read them as they are), on every kernel path
+    and for both parities of the iteration count."""
+    g = _gpu()
+    unary, ctx, ew, dcost = _rand_case(77 + L + I, mode, D, 1, 1, 12, 16, L, I, "sym2d")
+    first = oracle.forward(mode, unary, ctx, ew, D, 2)
+    want = oracle.forward(mode, unary, ctx, ew, D, I, msg_init=first["msg"])
+    got = g.forward(mode, unary, ctx, ew, D, I, msg_init=first["msg"])
+    for k in ("cost", "msg", "min_idx", "norm_idx"):
+        assert np.array_equal(got[k], want[k]), k
+    # and it equals running the iterations in one go (ISGMR and TRWP are stationary iterations)
+    whole = oracle.forward(mode, unary, ctx, ew, D, 2 + I)
+    assert np.array_equal(got["msg"], whole["msg"])
+
+
+def test_context_window_statement_and_analysis():
+    """Inference with a rank-1 context and more than 32 labels: the caller's statement about the
+    context (mpl_problem::context_window) selects the same kernels as the library's own analysis, and
+    -1 the evaluation of all candidates; all three give the oracle's bits."""
+    import torch
+    from mplayers_b200 import _lib
+    g = _gpu()
+    rng = np.random.default_rng(4)
+    L, D = 96, 4
+    unary = rng.standard_normal((1, 1, 10, 12, L)).astype(np.float32)
+    ctx = cases.make_context("tl1d", L, rng)
+    want = oracle.forward("TRWP", unary, ctx, None, D, 2, training=False)
+    assert _lib.analyze_context(torch.from_numpy(ctx).cuda()) == 2
+    assert _lib.analyze_context(torch.from_numpy(rng.uniform(0, 1, L).astype(np.float32)).cuda()) == -1
+    neg = torch.full((D, 1, 1, 10, 12), -0.5, device="cuda")
+    assert _lib.analyze_context(torch.from_numpy(ctx).cuda(), neg) == -1
+    for window in (0, 2, -1):
+        got = g.forward("TRWP", unary, ctx, None, D, 2, training=False, context_window=window)
+        assert np.array_equal(got["cost"], want["cost"]), window

@@ -57,6 +57,15 @@ def _rank_main(rank, world, port, out):
     # a second path: explicit call on a tensor
     t = torch.from_numpy(bw["dctx"].copy())
     parallel.allreduce_label_context_grad(t)
+    # a rank whose parameter received no gradient still takes part: its zeros are reduced and it
+    # ends up with the other rank's gradient
+    idle = torch.nn.Parameter(torch.zeros(3))
+    if rank == 0:
+        idle.grad = torch.tensor([1.0, 2.0, 3.0])
+    parallel.allreduce_label_context_grad(idle)
+    assert torch.equal(idle.grad, torch.tensor([1.0, 2.0, 3.0]))
+    with pytest.raises(RuntimeError, match="every rank"):
+        parallel.allreduce_label_context_grad(None)
     if rank == 0:
         np.save(out, np.stack([param.grad.numpy(), t.numpy()]))
     dist.barrier()

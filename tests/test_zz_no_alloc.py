@@ -42,15 +42,38 @@ def _run_both(seed, B, H, W, L, D, I):
     du_b, dc_b, de_b = torch.empty_like(dcost), torch.zeros_like(ctx), torch.zeros_like(ew)
     dmsg_b = torch.empty(D, B, 1, H, W, L, device="cuda")
     prob = _problem(_lib, I, D, B, H, W, L, 2)
-    torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated()
     vp = lambda t: ctypes.c_void_p(t.data_ptr())
-    rc = lib.mpl_trwp_backward_static(ctypes.byref(prob), vp(ctx), vp(ew), vp(dcost), vp(mi), vp(ni), vp(du_b),
-                                      vp(dc_b), vp(de_b), vp(dmsg_b),
-                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-    assert rc == 0, lib.mpl_last_error().decode()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(du, dc, de, dm):
+        rc = lib.mpl_trwp_backward_static(ctypes.byref(prob), vp(ctx), vp(ew), vp(dcost), vp(mi), vp(ni), vp(du),
+                                          vp(dc), vp(de), vp(dm), stream)
+        assert rc == 0, lib.mpl_last_error().decode()
+
+    # Warm-up call: loads the kernels' code and looks the scratch array's address up.  What follows
+    # must not change the device's free memory as the DRIVER counts it (torch's own counter would
+    # not see an allocation made inside the library).
+    call(torch.empty_like(dcost), torch.zeros_like(ctx), torch.zeros_like(ew), torch.empty_like(dmsg))
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
+    free_before = torch.cuda.mem_get_info()[0]
+    torch_before = torch.cuda.memory_allocated()
+    launches_before = lib.mpl_kernel_launches()
+    call(du_b, dc_b, de_b, dmsg_b)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_allocated() == torch_before
+    assert lib.mpl_kernel_launches() > launches_before      # kernels ran: not a silent no-op
+    st = ctypes.c_int32(-1)
+    assert lib.mpl_static_scratch_status(ctypes.byref(st)) == 0 and st.value == 0
+
+    # ... and against the CPU oracle directly, not only against the regular entry point
+    from oracle import oracle
+    want = oracle.backward("TRWP", ctx.cpu().numpy(), ew.cpu().numpy(), dcost.cpu().numpy(), mi.cpu().numpy(),
+                           ni.cpu().numpy())
+    from helpers import assert_grad_close
+    assert_grad_close(du_b.cpu().numpy(), want["dunary"], "dunary (static scratch)")
+    assert_grad_close(dc_b.cpu().numpy(), want["dctx"], "dctx (static scratch)")
+    assert_grad_close(de_b.cpu().numpy(), want["dew"], "dew (static scratch)")
     return (du_a, dc_a, de_a), (du_b, dc_b, de_b)
 
 
