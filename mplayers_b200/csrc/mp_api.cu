@@ -355,7 +355,7 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
                 mpl_backward_workspace_bytes(p));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int D = p->n_dir, L = p->n_disp;
-  const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg);
+  const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg, p->context_rank);
   float* part = ws_tables(workspace);
   MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));
 
@@ -434,7 +434,7 @@ size_t mpl_forward_workspace_bytes(const mpl_problem* p) {
 size_t mpl_backward_workspace_bytes(const mpl_problem* p) {
   Dims d;
   if (validate(p, &d) != MPL_OK) return 256;
-  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
+  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg, p->context_rank);
   return kTablesOffset + (size_t)n_slots * d.ctx_elems * sizeof(float);  // header + tables
 }
 
@@ -545,7 +545,7 @@ int mpl_isgmr_backward_directions(const mpl_problem* p, int32_t dir_first, int32
     return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
                 mpl_backward_workspace_bytes(p));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
+  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg, p->context_rank);
   float* part = ws_tables(workspace);
   int* status = ws_status(workspace);
   if (clear_workspace) {
@@ -587,7 +587,7 @@ int mpl_backward_context_finish(const mpl_problem* p, void* workspace, size_t wo
   if (!workspace || workspace_bytes < mpl_backward_workspace_bytes(p))
     return fail(MPL_ERR_INVALID, "workspace too small: %zu < %zu", workspace_bytes,
                 mpl_backward_workspace_bytes(p));
-  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg);
+  const int n_slots = mpl::backward_slots(p->height, p->width, p->n_disp, p->n_dir, (int)d.nimg, p->context_rank);
   MPL_CUDA(mpl::launch_dctx_reduce(ws_tables(workspace), n_slots, p->n_disp, p->context_rank,
                                    p->keep_diag, dcontext, static_cast<cudaStream_t>(stream)));
   return MPL_OK;
@@ -651,7 +651,7 @@ int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const flo
                 mpl_backward_workspace_bytes(p));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int D = p->n_dir, L = p->n_disp;
-  const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg);
+  const int n_slots = mpl::backward_slots(p->height, p->width, L, D, (int)d.nimg, p->context_rank);
   float* part = ws_tables(workspace);
   int* status = ws_status(workspace);
   MPL_CUDA(cudaMemsetAsync(part, 0, (size_t)n_slots * d.ctx_elems * sizeof(float), st));

@@ -1374,18 +1374,23 @@ cudaError_t launch_sum_fields(const float* base, float factor, const float* fiel
   return cudaGetLastError();
 }
 
-int backward_slots(int H, int W, int L, int D, int nimg) {
-  // one partial table per chain of a launch where that stays modest (deterministic sums); a launch
-  // covers one direction (TRWP) or all of them (ISGMR), the larger count is provisioned
+int backward_slots(int H, int W, int L, int D, int nimg, int rank) {
+  // One partial table per chain of a launch, so that every table has a single writer per launch and
+  // the sums are run-to-run identical.  A launch covers one direction (TRWP) or all of them (ISGMR);
+  // the call does not know which, so the larger count is provisioned while the tables stay within
+  // 256 MB, else the largest direction's count, else 4096 slots shared through atomic adds (then
+  // the order of the additions, and with it the last bits of the gradient, can vary between runs).
   long long mx = 1, sum = 0;
   for (int d = 0; d < D; ++d) {
     const long long n = (long long)make_geom(d, H, W).n_chains * nimg;
     if (n > mx) mx = n;
     sum += n;
   }
-  if (sum <= 4096) mx = sum;
-  if (mx > 4096) mx = 4096;
-  return (int)mx;
+  const long long table = (long long)(rank == 2 ? L * L : L) * (long long)sizeof(float);
+  const long long budget = 256ll << 20;
+  if (sum * table <= budget || sum <= 4096) return (int)sum;
+  if (mx * table <= budget || mx <= 4096) return (int)mx;
+  return 4096;
 }
 
 cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,

@@ -315,7 +315,7 @@ cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long 
                                  cudaStream_t st);
 cudaError_t launch_dctx_reduce(float* part, int n_slots, int L, int rank, int keep_diag,
                                float* dctx, cudaStream_t st);
-int backward_slots(int H, int W, int L, int D, int nimg);
+int backward_slots(int H, int W, int L, int D, int nimg, int rank);
 int tma_stage_override();  // MPL_TMA_STAGES environment variable (tuning knob), 0 = not set
 void count_launch(int n = 1);
 
