@@ -215,6 +215,7 @@ NCU_TRAFFIC = {
     ("seg_trwp_train", "bwd"): 149.3e6 + 80.9e6,
     ("seg_trwp_train", "fwd"): 222.4e6 + 33.9e6,
     ("stereo_trwp_infer", "fwd"): 1788.5e6 + 338.6e6,
+    ("denoise_isgmr_infer", "fwd"): 728.4e6 + 245.6e6,
     # captured on the 384 x 384 copy of the workload (a full-size launch is too large to replay under
     # the profiler); traffic is proportional to the pixel count, so the full-size figures are those
     # times (1024 / 384)^2
@@ -575,12 +576,16 @@ def run_ours(a):
         if extras:
             line["workloads"] = extras
         if not a.no_cpu_baseline and world == 1:
-            line["cpu_baseline"] = cpu_baseline(a.workload, target_s=10.0)
-            for name in extras:
-                extras[name]["cpu_baseline"] = cpu_baseline(name, target_s=5.0)
+            # The reference's CUDA build is loaded BEFORE its CPU build: both extensions export the
+            # same C symbols (MPLayers/TRWP/TRWP.h:23-25), and where the loader resolves them
+            # process-wide the first one loaded serves both -- the CUDA build contains the CPU path
+            # too, the CPU build has no device path.
             rc = reference_cuda(a.workload)
             if rc is not None:
                 line["reference_cuda"] = rc
+            line["cpu_baseline"] = cpu_baseline(a.workload, target_s=10.0)
+            for name in extras:
+                extras[name]["cpu_baseline"] = cpu_baseline(name, target_s=5.0)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -706,8 +711,8 @@ def reference_cuda(workload):
     try:
         import torch
         from oracle import ref_cuda
-        cfg = _CFG_CACHE.get(workload)
-        if cfg is None or cfg.get("soft") or not ref_cuda.available(cfg["mode"]):
+        cfg = _cpu_sample(workload, 32)[0]   # the generated configuration (cached)
+        if cfg.get("soft") or not ref_cuda.available(cfg["mode"]):
             return None
         u = cfg["unary"].permute(0, 1, 3, 4, 2).contiguous().cuda()
         b, cv, h, w, l = u.shape

@@ -96,6 +96,7 @@ struct FwdParams {
   int ctx_rank;
   int tma_stages;         // bulk-copy kernels: ring depth
   int tma_k;              // bulk-copy CTA kernel: chain pixels per stage
+  int tma_box;            // wide kernel: vertical chains are staged with 2-D tiled TMA boxes
   // agg != 0 (ISGMR): `unary` holds the per-iteration aggregate A = U + sum_k M_k of the messages
   // being read (computed once per iteration in the reference order of the additions), so a sweep
   // stages A, M_dir and M_inv only: UU = (A - M_dir) * rho - M_inv, bit-identical to the

@@ -835,7 +835,8 @@ __host__ __device__ inline size_t wide_chain_bytes(int ns, int A, int k, int L, 
 // beyond R carry the saturated value, which is an exact candidate of the dense evaluation too).
 // ------------------------------------------------------------------------------------------------
 template <int LPT, int RW, int DT>
-__global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p,
+                                                                       const __grid_constant__ TmaMaps maps) {
   extern __shared__ __align__(128) float smem_all[];
   constexpr int LP = 32 * LPT;                   // padded label count
   constexpr int G = ((RW - 1 + 3) / 4) * 4;      // guard band (floats) on both sides of the window buffer
@@ -861,6 +862,9 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
   const long long ibase = (long long)ch.img * p.H * p.W;
   const int pix0 = ch.h0 * p.W + ch.w0;
   const bool contiguous = (ch.pstep == 1 || ch.pstep == -1);
+  // vertical chains (directions 2 / 3) with tensor maps from the launcher: one 2-D tiled TMA box
+  // (L labels x K image rows of the chain's column) per array and stage instead of K row copies
+  const bool boxed = p.tma_box != 0 && (ch.dir == 2 || ch.dir == 3);
 
   if (!producer) {
     if (lane == 0) {
@@ -887,6 +891,21 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
       }
       const int np = len - s * K < K ? len - s * K : K;
       float* T = tiles + slot * tile_floats;
+      if (boxed) {
+        // The whole box is always transferred; rows outside the tensor read as zero, rows of a
+        // neighbouring image are never used.  An upward walk (direction 3) gets its rows in
+        // ascending order: the consumer reads the box from its last row.
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full[slot], (unsigned)(K * A * L) * 4u);
+          const int y0 = ch.img * p.H + (ch.dir == 2 ? s * K : p.H - (s + 1) * K);
+          tma_load_2d(T, &maps.a, ch.w0 * L, y0, &full[slot]);
+          for (int a = 1; a < A; ++a) {
+            const int sid = AGG ? (a == 1 ? ch.dir : ch.inv) : a - 1;
+            tma_load_2d(T + a * K * L, &maps.b, ch.w0 * L, sid * p.nimg * p.H + y0, &full[slot]);
+          }
+        }
+        continue;
+      }
       if (lane == 0) mbar_arrive_expect_tx(&full[slot], (unsigned)(np * A * L) * 4u);
       __syncwarp();
       if (contiguous) {
@@ -940,8 +959,9 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
     const int np = len - s * K < K ? len - s * K : K;
     const float* T = tiles + slot * tile_floats;
     const float* et = etile + (s & 1) * K;
-    const int kbase = (contiguous && ch.pstep == -1) ? np - 1 : 0;
-    const int kstep = (contiguous && ch.pstep == -1) ? -1 : 1;
+    const bool up = boxed && ch.dir == 3;
+    const int kbase = (contiguous && ch.pstep == -1) ? np - 1 : (up ? K - 1 : 0);
+    const int kstep = ((contiguous && ch.pstep == -1) || up) ? -1 : 1;
     __syncwarp();
     for (int k = 0; k < np; ++k) {
       const float* t = T + (kbase + k * kstep) * L + c0;
@@ -1482,6 +1502,16 @@ cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
   if (tma_stage_override()) NS = tma_stage_override();
   p.tma_k = K;
   p.tma_stages = NS;
+  // tensor maps for the vertical chains (box = one pixel's labels x K image rows); the box must
+  // land 128-byte aligned in the staging ring
+  TmaMaps maps{};
+  p.tma_box = 0;
+  if (p.dir0 <= 3 && p.dir0 + p.ndirs > 2 && ((size_t)K * p.L * sizeof(float)) % 128 == 0 && p.L <= 256) {
+    const unsigned long long inner = (unsigned long long)p.W * p.L, rows = (unsigned long long)p.nimg * p.H;
+    if (encode_tmap_2d(&maps.a, p.unary, inner, rows, p.L, K) &&
+        encode_tmap_2d(&maps.b, p.msg_read, inner, rows * p.D, p.L, K))
+      p.tma_box = 1;
+  }
   const size_t smem = bytes(K, NS) * C;
   cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW, DT>, smem);
   if (e != cudaSuccess) return e;
@@ -1490,7 +1520,7 @@ cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
                            (int)cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
-  fwd_wide_kernel<LPT, RW, DT><<<ctas, C == 1 ? 96 : C * 64, smem, st>>>(p);
+  fwd_wide_kernel<LPT, RW, DT><<<ctas, C == 1 ? 96 : C * 64, smem, st>>>(p, maps);
   count_launch();
   return cudaGetLastError();
 }
