@@ -63,6 +63,14 @@ typedef struct mpl_problem {
                                   (what mpl_analyze_context reports) -- no read-back, fully
                                   asynchronous; a wrong statement gives wrong results;
                                -1: evaluate all L candidates per label. */
+  int32_t chain_part;       /* iteration-level ISGMR entry points only (mpl_isgmr_forward_directions, */
+  int32_t chain_parts;      /* mpl_isgmr_backward_directions): the call runs part chain_part of
+                               chain_parts of the chains of each of its directions (chains of the even
+                               direction of a pair in the order of mpl_chain_geometry, images outermost;
+                               the odd direction walks the same lines from their other end, so that a
+                               part holds both messages of every line it owns); chain_parts <= 1: all chains.
+                               Lets more ranks than direction pairs share one image: pixels a call
+                               does not visit are left untouched in every output. */
 } mpl_problem;
 
 /* Analyses a rank-1 context (and the edge weights, may be NULL) for mpl_problem::context_window:
@@ -176,6 +184,12 @@ int mpl_isgmr_forward_directions(const mpl_problem* p, int32_t dir_first, int32_
  * (fields [D,B,cv,H,W,L]; base may be NULL: plain sum; any dir_first / dir_count inside 0..D). */
 int mpl_sum_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_count, const float* base,
                        float base_factor, const float* fields, float* out, void* stream);
+/* The same for elements [first_element, first_element + n_elements) of the field only (the same
+ * pointers as above): lets a caller form the sum chunk by chunk and hand each chunk to a
+ * collective while the next one is being summed. */
+int mpl_sum_directions_range(const mpl_problem* p, int32_t dir_first, int32_t dir_count, const float* base,
+                             float base_factor, const float* fields, float* out, int64_t first_element,
+                             int64_t n_elements, void* stream);
 
 /* Backward sweeps of one iteration: replays the given directions' chains from this iteration's
  * saved indices.

@@ -21,7 +21,9 @@ class Problem(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
                 ("n_iter", "n_dir", "batch", "n_cv", "height", "width", "n_disp", "context_rank",
                  "enable_min_a_dir", "enable_sgm", "keep_diag")] + [("rho", ctypes.c_float),
-                                                                   ("context_window", ctypes.c_int32)]
+                                                                   ("context_window", ctypes.c_int32),
+                                                                   ("chain_part", ctypes.c_int32),
+                                                                   ("chain_parts", ctypes.c_int32)]
 
 
 _lib = None
@@ -56,6 +58,9 @@ def lib():
         L.mpl_isgmr_forward_directions.argtypes = [pp, i32, i32] + [vp] * 8 + [sz, vp]
         L.mpl_sum_directions.restype = ctypes.c_int
         L.mpl_sum_directions.argtypes = [pp, i32, i32, vp, ctypes.c_float, vp, vp, vp]
+        L.mpl_sum_directions_range.restype = ctypes.c_int
+        L.mpl_sum_directions_range.argtypes = [pp, i32, i32, vp, ctypes.c_float, vp, vp, ctypes.c_int64,
+                                               ctypes.c_int64, vp]
         L.mpl_isgmr_backward_directions.restype = ctypes.c_int
         L.mpl_isgmr_backward_directions.argtypes = [pp, i32, i32] + [vp] * 8 + [sz, i32, vp]
         L.mpl_isgmr_backward_combine.restype = ctypes.c_int

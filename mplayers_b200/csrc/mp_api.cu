@@ -150,6 +150,8 @@ int validate(const mpl_problem* p, Dims* d) {
   if (d->nimg * 4096ll >= (1ll << 31) || d->npix >= (1ll << 40))
     return fail(MPL_ERR_UNSUPPORTED, "batch*n_cv=%lld too large", d->nimg);
   d->ctx_elems = p->context_rank == 2 ? p->n_disp * p->n_disp : p->n_disp;
+  if (p->chain_parts > 1 && (p->chain_part < 0 || p->chain_part >= p->chain_parts))
+    return fail(MPL_ERR_INVALID, "chain_part=%d outside 0..%d", p->chain_part, p->chain_parts - 1);
   return MPL_OK;
 }
 
@@ -183,8 +185,12 @@ void set_dirs(mpl::FwdParams& fp, int dir0, int ndirs) {
   fp.dir0 = dir0;
   fp.ndirs = ndirs;
   fp.chain_off[0] = 0;
-  for (int i = 0; i < ndirs; ++i)
-    fp.chain_off[i + 1] = fp.chain_off[i] + mpl::make_geom(dir0 + i, fp.H, fp.W).n_chains * fp.nimg;
+  for (int i = 0; i < ndirs; ++i) {
+    int begin, count;
+    mpl::chain_part((long long)mpl::make_geom(dir0 + i, fp.H, fp.W).n_chains * fp.nimg, fp.part, fp.parts, begin, count);
+    fp.chain_begin[i] = begin;
+    fp.chain_off[i + 1] = fp.chain_off[i] + count;
+  }
 }
 
 // Verdict of the device-side analysis (launch_analyze, in `workspace`): *window = R > 0 if the
@@ -511,6 +517,8 @@ int mpl_isgmr_forward_directions(const mpl_problem* p, int32_t dir_first, int32_
   fp.norm_idx = msg_norm_index;
   fp.msg_read = msg_read;
   fp.msg_write = msg_write;
+  fp.part = p->chain_part;
+  fp.parts = p->chain_parts;
   set_dirs(fp, dir_first, dir_count);
   MPL_CUDA(mpl::launch_forward_sweep(fp, train, st));
   return MPL_OK;
@@ -524,7 +532,26 @@ int mpl_sum_directions(const mpl_problem* p, int32_t dir_first, int32_t dir_coun
     return fail(MPL_ERR_INVALID, "directions [%d, %d) of %d", dir_first, dir_first + dir_count, p->n_dir);
   if (!out || (dir_count > 0 && !fields)) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
   MPL_CUDA(mpl::launch_sum_fields(base, base_factor, fields ? fields + (long long)dir_first * d.slice : nullptr,
-                                  dir_count, d.slice, out, static_cast<cudaStream_t>(stream)));
+                                  dir_count, d.slice, d.slice, out, static_cast<cudaStream_t>(stream)));
+  return MPL_OK;
+}
+
+int mpl_sum_directions_range(const mpl_problem* p, int32_t dir_first, int32_t dir_count, const float* base,
+                             float base_factor, const float* fields, float* out, int64_t first_element,
+                             int64_t n_elements, void* stream) {
+  Dims d;
+  if (int rc = validate(p, &d)) return rc;
+  if (dir_first < 0 || dir_count < 0 || dir_first + dir_count > p->n_dir)
+    return fail(MPL_ERR_INVALID, "directions [%d, %d) of %d", dir_first, dir_first + dir_count, p->n_dir);
+  if (!out || (dir_count > 0 && !fields)) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
+  if (first_element < 0 || n_elements < 0 || first_element + n_elements > d.slice)
+    return fail(MPL_ERR_INVALID, "elements [%lld, %lld) outside the field of %lld",
+                (long long)first_element, (long long)(first_element + n_elements), d.slice);
+  if (n_elements == 0) return MPL_OK;
+  MPL_CUDA(mpl::launch_sum_fields(base ? base + first_element : nullptr, base_factor,
+                                  fields ? fields + (long long)dir_first * d.slice + first_element : nullptr,
+                                  dir_count, n_elements, d.slice, out + first_element,
+                                  static_cast<cudaStream_t>(stream)));
   return MPL_OK;
 }
 
@@ -560,6 +587,8 @@ int mpl_isgmr_backward_directions(const mpl_problem* p, int32_t dir_first, int32
   bp.dew = (edge_weights && dedge_weights) ? dedge_weights : nullptr;
   bp.dir = dir_first;
   bp.ndirs = dir_count;
+  bp.part = p->chain_part;
+  bp.parts = p->chain_parts;
   bp.dm_read = dmsg_update;
   bp.dm_acc = scatter;
   MPL_CUDA(mpl::launch_backward_sweep(bp, st));

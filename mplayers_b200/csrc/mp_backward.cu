@@ -35,10 +35,18 @@ __device__ __forceinline__ bool decode_bchain(const BwdParams& p, int g, BChain&
   int di = 0;
   while (g >= p.chain_off[di + 1]) ++di;
   c.dir = p.dir + di;
-  const DirGeom geo = make_geom(c.dir, p.H, p.W);
-  const int local = g - p.chain_off[di];
+  // partial launches: the odd direction of a pair covers the even one's lines (see decode_chain)
+  const bool mirrored = p.parts > 1 && (c.dir & 1);
+  DirGeom geo = make_geom(mirrored ? (c.dir ^ 1) : c.dir, p.H, p.W);
+  const int local = g - p.chain_off[di] + p.chain_begin[di];
   c.img = local / geo.n_chains;
   chain_start(geo, p.H, p.W, local - c.img * geo.n_chains, c.h0, c.w0, c.len);
+  if (mirrored) {
+    c.h0 += (c.len - 1) * geo.hs;
+    c.w0 += (c.len - 1) * geo.ws;
+    geo.hs = -geo.hs;
+    geo.ws = -geo.ws;
+  }
   c.pstep = geo.hs * p.W + geo.ws;
   return true;
 }
@@ -1242,11 +1250,11 @@ __global__ void isgmr_combine_total_kernel(const float* __restrict__ Qt, const f
 
 // out = base * factor + sum of nf consecutive fields (base may be null: plain sum), ascending order
 __global__ void sum_fields_kernel(const float* __restrict__ base, float factor, const float* __restrict__ f,
-                                  int nf, long long n, float* __restrict__ out) {
+                                  int nf, long long n, long long stride, float* __restrict__ out) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
     float v = base ? base[i] * factor : 0.f;
-    for (int k = 0; k < nf; ++k) v += f[k * n + i];
+    for (int k = 0; k < nf; ++k) v += f[k * stride + i];
     out[i] = v;
   }
 }
@@ -1364,12 +1372,12 @@ cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, flo
   return cudaGetLastError();
 }
 
-cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n, float* out,
-                              cudaStream_t st) {
+cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n,
+                              long long stride, float* out, cudaStream_t st) {
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   ProfScope prof(kProfElementwise, st);
-  sum_fields_kernel<<<(int)blocks, 256, 0, st>>>(base, factor, fields, nf, n, out);
+  sum_fields_kernel<<<(int)blocks, 256, 0, st>>>(base, factor, fields, nf, n, stride, out);
   count_launch();
   return cudaGetLastError();
 }
@@ -1406,7 +1414,8 @@ cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, l
 cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
   BwdParams p = p0;
   if (p.ndirs < 1) p.ndirs = 1;
-  if (p.cp_scheme == 2 && p.L <= 32 && p.ndirs > 1 && (long long)p.nimg * (p.H < p.W ? p.H : p.W) >= 256) {
+  if (p.cp_scheme == 2 && p.L <= 32 && p.ndirs > 1 && p.parts <= 1 &&
+      (long long)p.nimg * (p.H < p.W ? p.H : p.W) >= 256) {
     // ISGMR, L <= 32: the axis directions whose rows are 16-byte aligned go to the bulk-copy kernel
     // one by one (the sweeps are independent), the rest to one launch of the generic kernel.
     // Small problems (few chains per direction) stay with one launch over all directions.
@@ -1425,13 +1434,17 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
     p.dir = d;
   }
   p.chain_off[0] = 0;
-  for (int i = 0; i < p.ndirs; ++i)
-    p.chain_off[i + 1] = p.chain_off[i] + make_geom(p.dir + i, p.H, p.W).n_chains * p.nimg;
+  for (int i = 0; i < p.ndirs; ++i) {
+    int begin, count;
+    chain_part((long long)make_geom(p.dir + i, p.H, p.W).n_chains * p.nimg, p.part, p.parts, begin, count);
+    p.chain_begin[i] = begin;
+    p.chain_off[i + 1] = p.chain_off[i] + count;
+  }
   const int total = p.chain_off[p.ndirs];
   if (total == 0) return cudaSuccess;
   const int L = p.L, LS = L | 1;
   ProfScope prof(kProfBwdSweep, st);
-  if (L <= 32 && bwd_tma_eligible(p)) {
+  if (L <= 32 && p.parts <= 1 && bwd_tma_eligible(p)) {
     p.tma_stages = tma_stage_override() ? tma_stage_override() : 4;
     cudaError_t e = L == 21 ? launch_bwd_tma<21>(p, st) : launch_bwd_tma<0>(p, st);
     if (e != cudaSuccess) return e;
@@ -1493,6 +1506,8 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
 cudaError_t launch_backward_soft_sweep(const BwdParams& p0, cudaStream_t st) {
   BwdParams p = p0;
   p.ndirs = 1;
+  p.parts = 0;
+  p.chain_begin[0] = 0;
   p.chain_off[0] = 0;
   p.chain_off[1] = make_geom(p.dir, p.H, p.W).n_chains * p.nimg;
   const int total = p.chain_off[1];

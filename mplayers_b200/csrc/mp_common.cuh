@@ -69,6 +69,17 @@ __host__ __device__ inline void chain_start(const DirGeom& g, int H, int W, int 
   len = 1 + (nh < nw ? nh : nw);
 }
 
+// Chains [begin, begin + count) of `total` that part `part` of `parts` covers (parts <= 1: all).
+__host__ __device__ inline void chain_part(long long total, int part, int parts, int& begin, int& count) {
+  if (parts <= 1) {
+    begin = 0;
+    count = (int)total;
+    return;
+  }
+  begin = (int)(total * part / parts);
+  count = (int)(total * (part + 1) / parts) - begin;
+}
+
 // What the device learned about a rank-1 context and the edge weights (written by
 // analyze kernels, read by the sweep kernels; lives in the caller's workspace).
 struct CtxInfo {
@@ -105,7 +116,9 @@ struct FwdParams {
   int host_windowed;      // host copy of the context analysis (rank-1, L > 32): windowed path is exact
   int host_R;             //   ... and its window half-width
   int dir0, ndirs;        // this launch covers directions dir0 .. dir0+ndirs-1
-  int chain_off[17];      // prefix sums of nimg*n_chains over those directions
+  int chain_off[17];      // prefix sums of the chain counts of those directions in this launch
+  int chain_begin[16];    // first chain (of nimg*n_chains) of each of those directions in this launch
+  int part, parts;        // the launch covers part `part` of `parts` of every direction's chains (parts <= 1: all)
 };
 
 struct BwdParams {
@@ -127,7 +140,9 @@ struct BwdParams {
   int ctx_rank, keep_diag;
   int dir;                // first direction of this launch
   int ndirs;              // directions covered (more than one only with cp_scheme == 2)
-  int chain_off[17];      // prefix sums of nimg*n_chains over those directions
+  int chain_off[17];      // prefix sums of the chain counts of those directions in this launch
+  int chain_begin[16];    // first chain (of nimg*n_chains) of each of those directions in this launch
+  int part, parts;        // part `part` of `parts` of every direction's chains (parts <= 1: all)
   int table_in_smem;      // CTA kernel: 1 = [L][L|1] table in shared memory
   // Gradient bookkeeping.  cp_scheme == 0: `dunary` and the D slices of `dm_acc` are updated with
   // one reduction each per pixel (the reference's UpdateUnaryKernelBack).  cp_scheme == 1 (TRWP,
@@ -310,8 +325,8 @@ cudaError_t launch_layout(int kind, const float* in, float* out, uint8_t* amax, 
 cudaError_t launch_energy(const float* unary, const float* ctx, const float* ew, const uint8_t* label,
                           long long npix, int H, int W, int L, int D, int rank, double* part, double* out,
                           cudaStream_t st);
-cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n, float* out,
-                              cudaStream_t st);
+cudaError_t launch_sum_fields(const float* base, float factor, const float* fields, int nf, long long n,
+                              long long stride, float* out, cudaStream_t st);
 cudaError_t launch_isgmr_combine(const float* q, float* dm, float* dunary, long long n, int D, float rho,
                                  cudaStream_t st);
 cudaError_t launch_dctx_reduce(float* part, int n_slots, int L, int rank, int keep_diag,

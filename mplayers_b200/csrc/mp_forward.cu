@@ -36,10 +36,20 @@ __device__ __forceinline__ bool decode_chain(const FwdParams& p, int g, ChainCtx
   while (g >= p.chain_off[di + 1]) ++di;
   c.dir = p.dir0 + di;
   c.inv = c.dir ^ 1;
-  const DirGeom geo = make_geom(c.dir, p.H, p.W);
-  const int local = g - p.chain_off[di];
+  // When a launch covers only a part of the chains, both directions of a pair must cover the same
+  // lines (each reads the other's messages): the odd direction then enumerates the even one's
+  // chains and walks each from its far end.
+  const bool mirrored = p.parts > 1 && (c.dir & 1);
+  DirGeom geo = make_geom(mirrored ? c.inv : c.dir, p.H, p.W);
+  const int local = g - p.chain_off[di] + p.chain_begin[di];
   c.img = local / geo.n_chains;
   chain_start(geo, p.H, p.W, local - c.img * geo.n_chains, c.h0, c.w0, c.len);
+  if (mirrored) {
+    c.h0 += (c.len - 1) * geo.hs;
+    c.w0 += (c.len - 1) * geo.ws;
+    geo.hs = -geo.hs;
+    geo.ws = -geo.ws;
+  }
   c.pstep = geo.hs * p.W + geo.ws;
   return c.len >= 2;
 }
@@ -1784,7 +1794,7 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
     int first_generic = p.dir0;
     // several independent directions (ISGMR) of a small problem: one launch of the generic kernel
     // over all of them beats one small launch per direction
-    const bool few_chains = p.ndirs > 1 && (long long)p.nimg * (p.H < p.W ? p.H : p.W) < 256;
+    const bool few_chains = (p.ndirs > 1 && (long long)p.nimg * (p.H < p.W ? p.H : p.W) < 256) || p.parts > 1;
     for (int d = p.dir0; d < p.dir0 + p.ndirs && !few_chains; ++d) {
       int stages = 0;
       if (d != first_generic || !tma_eligible(p, d, &stages)) break;
@@ -1799,6 +1809,7 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
     rest.dir0 = first_generic;
     rest.ndirs = nrest;
     for (int i = 0; i <= nrest; ++i) rest.chain_off[i] = p.chain_off[first_generic - p.dir0 + i] - base;
+    for (int i = 0; i < nrest; ++i) rest.chain_begin[i] = p.chain_begin[first_generic - p.dir0 + i];
     if (p.L == 21) return train ? launch_warp<21, true>(rest, st) : launch_warp<21, false>(rest, st);
     return train ? launch_warp<32, true>(rest, st) : launch_warp<32, false>(rest, st);
   }

@@ -31,6 +31,24 @@ def test_direction_shards_keep_pairs_together_and_cover_all():
         ds.direction_shards(3, 2)
 
 
+def test_shard_plan_splits_chains_when_ranks_outnumber_pairs():
+    assert ds.shard_plan(8, 4) == [(0, 2, 0, 1), (2, 2, 0, 1), (4, 2, 0, 1), (6, 2, 0, 1)]
+    plan = ds.shard_plan(8, 8)
+    assert plan == [(2 * (r // 2), 2, r % 2, 2) for r in range(8)]
+    plan = ds.shard_plan(4, 7)                       # 2 pairs, 3 ranks each, one rank left over
+    assert plan[:6] == [(0, 2, 0, 3), (0, 2, 1, 3), (0, 2, 2, 3), (2, 2, 0, 3), (2, 2, 1, 3), (2, 2, 2, 3)]
+    assert plan[6][1] == 0                           # owns nothing, still joins the collectives
+    for n_dir, world in ((8, 16), (16, 8), (2, 5)):
+        owned = {}
+        for first, count, part, parts in ds.shard_plan(n_dir, world):
+            for d in range(first, first + count):
+                owned.setdefault(d, []).append((part, parts))
+        assert sorted(owned) == list(range(n_dir))
+        for d, lst in owned.items():                 # every part of every direction exactly once
+            parts = lst[0][1]
+            assert sorted(p for p, _ in lst) == list(range(parts)) and all(q == parts for _, q in lst)
+
+
 def _inputs():
     rng = np.random.default_rng(11)
     B, H, W, L, D, I = 1, 5, 6, 4, 8, 2
@@ -63,15 +81,16 @@ def _rank_main(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_ranks_reproduce_the_monolithic_layer(tmp_path):
+@pytest.mark.parametrize("world", [2, 8])   # whole pairs per rank; two ranks per pair (chains split)
+def test_gloo_ranks_reproduce_the_monolithic_layer(tmp_path, world):
     from oracle import oracle
     out = str(tmp_path / "rank%d.npz")
-    port = 29500 + (os.getpid() + 7) % 2000
-    mp.spawn(_rank_main, args=(2, port, out), nprocs=2, join=True)
+    port = 29500 + (os.getpid() + 7 + world) % 2000
+    mp.spawn(_rank_main, args=(world, port, out), nprocs=world, join=True)
     unary, ctx, ew, g, D, I = _inputs()
     fw = oracle.forward("ISGMR", unary, ctx, ew, D, I)
     bw = oracle.backward("ISGMR", ctx, ew, g, fw["min_idx"], fw["norm_idx"])
-    r0, r1 = np.load(out % 0), np.load(out % 1)
+    r0, r1 = np.load(out % 0), np.load(out % (world - 1))
     for k in ("cost", "dunary", "dctx", "dew"):
         assert np.array_equal(r0[k], r1[k]) or rel_err(r0[k], r1[k]) < 1e-6, k   # every rank ends with the whole result
     assert rel_err(r0["cost"], fw["cost"]) < COST_RTOL

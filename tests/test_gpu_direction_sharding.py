@@ -142,6 +142,9 @@ def _check(results, want, exact=False):
     (3, (1, 18, 22, 64, 8, 2, True)),     # uneven split; two-labels-per-lane kernels
     (2, (1, 16, 19, 40, 4, 3, False)),    # 1-D context
     (8, (1, 9, 11, 12, 16, 2, True)),     # one pair per rank, 16 directions
+    (8, (1, 20, 17, 21, 8, 2, True)),     # two ranks per pair: each walks half of the pair's lines
+    (6, (2, 18, 22, 64, 4, 2, True)),     # three ranks per pair, two images, two-labels-per-lane kernels
+    (5, (1, 14, 15, 40, 8, 2, False)),    # more ranks than pairs but not twice as many: one rank owns nothing
 ])
 def test_thread_ranks_match_the_monolithic_layer(world, shape):
     B, H, W, L, D, I, rank2 = shape
@@ -151,7 +154,7 @@ def test_thread_ranks_match_the_monolithic_layer(world, shape):
     _check(_sharded_threads(world, unary, ctx, ew, dcost, args), want)
 
 
-@pytest.mark.parametrize("world,L", [(2, 21), (4, 64)])
+@pytest.mark.parametrize("world,L", [(2, 21), (4, 64), (8, 64), (16, 21)])
 def test_thread_ranks_bit_identical_on_exact_inputs(world, L):
     unary, ctx, ew, dcost = _dyadic_case(5, 1, 20, 24, L, 8)
     args = _args(8, 3)
