@@ -26,34 +26,6 @@ namespace {
 
 constexpr int kPF = 8;  // pixels staged ahead per chain (power of two)
 
-struct ChainCtx {
-  int dir, inv, img, h0, w0, len, pstep;
-};
-
-__device__ __forceinline__ bool decode_chain(const FwdParams& p, int g, ChainCtx& c) {
-  if (g >= p.chain_off[p.ndirs]) return false;
-  int di = 0;
-  while (g >= p.chain_off[di + 1]) ++di;
-  c.dir = p.dir0 + di;
-  c.inv = c.dir ^ 1;
-  // When a launch covers only a part of the chains, both directions of a pair must cover the same
-  // lines (each reads the other's messages): the odd direction then enumerates the even one's
-  // chains and walks each from its far end.
-  const bool mirrored = p.parts > 1 && (c.dir & 1);
-  DirGeom geo = make_geom(mirrored ? c.inv : c.dir, p.H, p.W);
-  const int local = g - p.chain_off[di] + p.chain_begin[di];
-  c.img = local / geo.n_chains;
-  chain_start(geo, p.H, p.W, local - c.img * geo.n_chains, c.h0, c.w0, c.len);
-  if (mirrored) {
-    c.h0 += (c.len - 1) * geo.hs;
-    c.w0 += (c.len - 1) * geo.ws;
-    geo.hs = -geo.hs;
-    geo.ws = -geo.ws;
-  }
-  c.pstep = geo.hs * p.W + geo.ws;
-  return c.len >= 2;
-}
-
 // UU of one pixel from its ring slot (rows: 0 = U, 1+k = M_k), column `col`, row stride `rs`.
 __device__ __forceinline__ float uu_from_ring(const float* slot, int rs, int col, int D, int dir,
                                               int inv, float rho, int agg = 0) {
@@ -817,278 +789,6 @@ __global__ void __launch_bounds__(288) fwd_cta_tma_kernel(const __grid_constant_
   }
 }
 
-constexpr int kWideChains = 4;  // most chains per CTA of fwd_wide_kernel
-// Chains per CTA of fwd_wide_kernel.  Wide windows make a step arithmetic-bound: four chains per
-// CTA (consumers on warps 0..3, producers on 4..7) give each of the SM's four schedulers one
-// consumer however the SM places a CTA's warps (measured on 256 labels, window 16: 0.47 -> 0.35 ms
-// per sweep).  Narrow windows leave the sweep bound by memory latency, where more, smaller CTAs
-// spread over all SMs win; there a CTA holds one chain, padded with an idle third warp so that
-// successive CTAs start on different schedulers (192 labels, window 3: 0.50 -> 0.47 ms).
-__host__ __device__ constexpr int wide_chains_per_cta(int lpt, int rw) { return lpt * rw >= 32 ? kWideChains : 1; }
-// Shared memory of one chain of fwd_wide_kernel (staging ring, two window buffers, edge weights,
-// barriers), rounded so that the next chain's ring starts 128-byte aligned.
-__host__ __device__ inline size_t wide_chain_bytes(int ns, int A, int k, int L, int lpt, int g) {
-  const size_t b = ((size_t)ns * A * k * L + 2 * (32 * lpt + 2 * g) + 2 * k + 2) * sizeof(float) + 2 * ns * 8 + 16;
-  return (b + 127) & ~(size_t)127;
-}
-
-// ------------------------------------------------------------------------------------------------
-// Inference, rank-1 context that saturates inside a window (truncated linear / quadratic, Potts),
-// 32 < L <= 256, L % 4 == 0: one WARP per chain, LPT = ceil(L/32) consecutive labels per lane.
-//
-// With several labels per lane the whole label vector of a chain lives in one warp's registers:
-// no block barrier per step (the CTA-per-chain kernel needs two), the window around a lane's
-// labels is fetched with a few 16-byte shared loads, and every candidate costs one fma and a
-// share of a 3-input min.  Inputs are staged by a producer warp with cp.async.bulk copies
-// (one per array for horizontal chains, one label row per pixel otherwise) on an mbarrier ring.
-// RW = compile-time window half-width (candidates |c-f| < RW; RW >= R of the context: offsets
-// beyond R carry the saturated value, which is an exact candidate of the dense evaluation too).
-// ------------------------------------------------------------------------------------------------
-template <int LPT, int RW, int DT>
-__global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p,
-                                                                       const __grid_constant__ TmaMaps maps) {
-  extern __shared__ __align__(128) float smem_all[];
-  constexpr int LP = 32 * LPT;                   // padded label count
-  constexpr int G = ((RW - 1 + 3) / 4) * 4;      // guard band (floats) on both sides of the window buffer
-  constexpr int NWV = (LPT + 2 * G) / 2;         // float2 loads covering a lane's window
-  constexpr bool AGG = DT == 2;  // aggregate mode (FwdParams::agg): arrays A, M_dir, M_inv
-  const int L = p.L, D = DT ? DT : p.D, A = D + 1, K = p.tma_k, NS = p.tma_stages;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Warps 0..C-1 are the consumers of the CTA's C chains, warps C..2C-1 their producers.
-  constexpr int C = wide_chains_per_cta(LPT, RW);
-  const int sub = warp & (C - 1);
-  const bool producer = warp >= C;
-  float* smem = smem_all + (size_t)sub * (wide_chain_bytes(NS, A, K, L, LPT, G) / sizeof(float));
-  ChainCtx ch;
-  const bool valid = decode_chain(p, blockIdx.x * C + sub, ch);
-  const int tile_floats = A * K * L;
-  float* tiles = smem;                                   // [NS][A][K][L]
-  float* hwin = tiles + NS * tile_floats;                // [2][G + LP + G]
-  float* etile = hwin + 2 * (LP + 2 * G);                // [2][K]
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(etile + 2 * K + ((2 * K) & 1));
-  unsigned long long* empty = full + NS;
-  const int len = valid ? ch.len : 0;
-  const int nstages = (len + K - 1) / K;
-  const long long ibase = (long long)ch.img * p.H * p.W;
-  const int pix0 = ch.h0 * p.W + ch.w0;
-  const bool contiguous = (ch.pstep == 1 || ch.pstep == -1);
-  // vertical chains (directions 2 / 3) with tensor maps from the launcher: one 2-D tiled TMA box
-  // (L labels x K image rows of the chain's column) per array and stage instead of K row copies
-  const bool boxed = p.tma_box != 0 && (ch.dir == 2 || ch.dir == 3);
-
-  if (!producer) {
-    if (lane == 0) {
-      for (int i = 0; i < NS; ++i) {
-        mbar_init(&full[i], 1);
-        mbar_init(&empty[i], 1);
-      }
-      mbar_fence_init();
-    }
-    for (int i = lane; i < 2 * (LP + 2 * G); i += 32) hwin[i] = kInf;  // guards and padding labels
-  }
-  __syncthreads();
-  if (!valid || warp >= 2 * C) return;  // warps beyond 2C only pad the CTA (see launch_wide_d)
-
-  if (producer) {
-    // ---------------------------------- producer ----------------------------------
-    const float* U = p.unary + ibase * L;
-    const float* Mr = p.msg_read + ibase * L;
-    for (int s = 0; s < nstages; ++s) {
-      const int slot = s % NS;
-      if (s >= NS && !mbar_wait(&empty[slot], ((s / NS) - 1) & 1)) {
-        if (lane == 0) atomicExch(p.status, 121);
-        break;
-      }
-      const int np = len - s * K < K ? len - s * K : K;
-      float* T = tiles + slot * tile_floats;
-      if (boxed) {
-        // The whole box is always transferred; rows outside the tensor read as zero, rows of a
-        // neighbouring image are never used.  An upward walk (direction 3) gets its rows in
-        // ascending order: the consumer reads the box from its last row.
-        if (lane == 0) {
-          mbar_arrive_expect_tx(&full[slot], (unsigned)(K * A * L) * 4u);
-          const int y0 = ch.img * p.H + (ch.dir == 2 ? s * K : p.H - (s + 1) * K);
-          tma_load_2d(T, &maps.a, ch.w0 * L, y0, &full[slot]);
-          for (int a = 1; a < A; ++a) {
-            const int sid = AGG ? (a == 1 ? ch.dir : ch.inv) : a - 1;
-            tma_load_2d(T + a * K * L, &maps.b, ch.w0 * L, sid * p.nimg * p.H + y0, &full[slot]);
-          }
-        }
-        continue;
-      }
-      if (lane == 0) mbar_arrive_expect_tx(&full[slot], (unsigned)(np * A * L) * 4u);
-      __syncwarp();
-      if (contiguous) {
-        const int first = ch.pstep == 1 ? pix0 + s * K : pix0 - (s * K + np - 1);
-        if (lane < A) {
-          const int sid = AGG ? (lane == 1 ? ch.dir : ch.inv) : lane - 1;
-          const float* src = (lane == 0 ? U : Mr + (long long)sid * p.slice) + (long long)first * L;
-          bulk_g2s(T + lane * K * L, src, (unsigned)(np * L) * 4u, &full[slot]);
-        }
-      } else {
-        for (int q = lane; q < np * A; q += 32) {
-          const int k = q / A, a = q - k * A;
-          const int px = pix0 + (s * K + k) * ch.pstep;
-          const int sid = AGG ? (a == 1 ? ch.dir : ch.inv) : a - 1;
-          const float* src = (a == 0 ? U : Mr + (long long)sid * p.slice) + (long long)px * L;
-          bulk_g2s(T + (a * K + k) * L, src, (unsigned)L * 4u, &full[slot]);
-        }
-      }
-    }
-    return;
-  }
-
-  // ---------------------------------- consumer warp ----------------------------------
-  const CtxInfo inf = *p.info;
-  const float cmax = inf.cmax;
-  float cw[RW];  // context at offsets 0 .. RW-1 (saturated value beyond the table)
-#pragma unroll
-  for (int k = 0; k < RW; ++k) cw[k] = k < L ? __ldg(p.ctx + k) : cmax;
-  float* Mw = p.msg_write + (long long)ch.dir * p.slice + ibase * L;
-  const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
-  const int c0 = lane * LPT;                    // first label of this lane
-  const int nl = L - c0 < 0 ? 0 : (L - c0 < LPT ? L - c0 : LPT);  // labels of this lane that exist
-  const int dir_off = (AGG ? 1 : 1 + ch.dir) * K * L, inv_off = (AGG ? 2 : 1 + ch.inv) * K * L;
-  const float rho = p.rho;
-  auto load_e = [&](int s) -> float {  // lane k < K: weight of chain pixel s*K + k
-    const int j = s * K + lane;
-    return (E && lane < K && j < len && j >= 1) ? E[pix0 + j * ch.pstep] : 1.f;
-  };
-  if (lane < K) etile[lane] = load_e(0);
-  float e_next = load_e(1);
-  float uu[LPT], r[LPT];
-#pragma unroll
-  for (int i = 0; i < LPT; ++i) uu[i] = 0.f, r[i] = 0.f;
-
-  for (int s = 0; s < nstages; ++s) {
-    const int slot = s % NS;
-    if (!mbar_wait(&full[slot], (s / NS) & 1)) {
-      if (lane == 0) atomicExch(p.status, 122);
-      return;
-    }
-    const int np = len - s * K < K ? len - s * K : K;
-    const float* T = tiles + slot * tile_floats;
-    const float* et = etile + (s & 1) * K;
-    const bool up = boxed && ch.dir == 3;
-    const int kbase = (contiguous && ch.pstep == -1) ? np - 1 : (up ? K - 1 : 0);
-    const int kstep = ((contiguous && ch.pstep == -1) || up) ? -1 : 1;
-    __syncwarp();
-    for (int k = 0; k < np; ++k) {
-      const float* t = T + (kbase + k * kstep) * L + c0;
-      // inputs of this pixel -> UU (reference order of the additions), LPT labels per lane
-      float un[LPT];
-      if (nl == LPT) {
-        float v[LPT], md[LPT], mi[LPT];
-#pragma unroll
-        for (int q = 0; q < LPT / 2; ++q) {
-          const float2 x = reinterpret_cast<const float2*>(t)[q];
-          v[2 * q] = x.x, v[2 * q + 1] = x.y;
-          const float2 y = reinterpret_cast<const float2*>(t + dir_off)[q];
-          md[2 * q] = y.x, md[2 * q + 1] = y.y;
-          const float2 z = reinterpret_cast<const float2*>(t + inv_off)[q];
-          mi[2 * q] = z.x, mi[2 * q + 1] = z.y;
-        }
-#pragma unroll
-        for (int a = 1; a <= (DT ? DT : 16); ++a) {
-          if (a <= D && !AGG) {
-#pragma unroll
-            for (int q = 0; q < LPT / 2; ++q) {
-              const float2 x = reinterpret_cast<const float2*>(t + a * K * L)[q];
-              v[2 * q] += x.x, v[2 * q + 1] += x.y;
-            }
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < LPT; ++i) un[i] = fmaf(v[i] - md[i], rho, -mi[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < LPT; ++i) {
-          un[i] = 0.f;
-          if (i < nl) {
-            float sum = t[i];
-            if (!AGG)
-              for (int a = 1; a <= D; ++a) sum += t[a * K * L + i];
-            sum -= t[dir_off + i];
-            un[i] = fmaf(sum, rho, -t[inv_off + i]);
-          }
-        }
-      }
-      if (s + k > 0) {
-        const float e = et[k];
-        float* hw = hwin + ((s * K + k) & 1) * (LP + 2 * G);
-        float hl = kInf;
-        if (nl == LPT) {
-          float hv[LPT];
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) {
-            hv[i] = fmaf(rho, r[i], uu[i]);
-            hl = fminf(hl, hv[i]);
-          }
-#pragma unroll
-          for (int q = 0; q < LPT / 2; ++q)
-            reinterpret_cast<float2*>(hw + G + c0)[q] = make_float2(hv[2 * q], hv[2 * q + 1]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) {
-            const float h = fmaf(rho, r[i], uu[i]);
-            if (i < nl) {
-              hw[G + c0 + i] = h;
-              hl = fminf(hl, h);
-            }
-          }
-        }
-        const float gv = fmaf(e, cmax, warp_min(hl));  // candidate through the saturated value
-        __syncwarp();
-        // window of this lane: labels c0 - G .. c0 + LPT + G - 1 (guards read +inf)
-        float win[NWV * 2];
-        if constexpr (LPT % 4 == 0) {
-#pragma unroll
-          for (int q = 0; q < NWV / 2; ++q) {
-            const float4 x = reinterpret_cast<const float4*>(hw + c0)[q];
-            win[4 * q] = x.x, win[4 * q + 1] = x.y, win[4 * q + 2] = x.z, win[4 * q + 3] = x.w;
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < NWV; ++q) {
-            const float2 x = reinterpret_cast<const float2*>(hw + c0)[q];
-            win[2 * q] = x.x, win[2 * q + 1] = x.y;
-          }
-        }
-        float best[LPT];
-        float bl = kInf;
-#pragma unroll
-        for (int i = 0; i < LPT; ++i) {
-          float cand[2 * RW];
-          cand[0] = gv;
-#pragma unroll
-          for (int kk = -(RW - 1); kk <= RW - 1; ++kk)
-            cand[kk + RW] = fmaf(e, cw[kk < 0 ? -kk : kk], win[G + i + kk]);
-          best[i] = min_tree<2 * RW>(cand);
-          if (i < nl) bl = fminf(bl, best[i]);
-        }
-        const float m = warp_min(bl);
-        float* out = Mw + (long long)(pix0 + (s * K + k) * ch.pstep) * L + c0;
-#pragma unroll
-        for (int i = 0; i < LPT; ++i) r[i] = best[i] - m;
-        if (nl == LPT) {
-#pragma unroll
-          for (int q = 0; q < LPT / 2; ++q) reinterpret_cast<float2*>(out)[q] = make_float2(r[2 * q], r[2 * q + 1]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < LPT; ++i)
-            if (i < nl) out[i] = r[i];
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < LPT; ++i) uu[i] = un[i];
-    }
-    if (lane < K) etile[((s + 1) & 1) * K + lane] = e_next;
-    e_next = load_e(s + 2);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[slot]);
-  }
-}
-
 // ------------------------------------------------------------------------------------------------
 // 32 < L <= 64, rank-2 (dense) context, L % 4 == 0: one WARP per chain, TWO labels per lane, both
 // context rows of the lane in registers.  No block barrier (the CTA-per-chain kernel needs two per
@@ -1483,75 +1183,6 @@ cudaError_t launch_cta_tma(FwdParams p, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-template <int LPT, int RW, int DT>
-cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
-  const int total = p.chain_off[p.ndirs];
-  const int A = (p.agg ? 2 : p.D) + 1;
-  constexpr int G = ((RW - 1 + 3) / 4) * 4;
-  int K = 8, NS = 3;
-  auto bytes = [&](int k, int ns) { return wide_chain_bytes(ns, A, k, p.L, LPT, G); };
-  // keep every chain of the launch resident at once where possible (chains are equally long, so a
-  // partial second wave would double the time)
-  constexpr int C = wide_chains_per_cta(LPT, RW);
-  const int ctas = (total + C - 1) / C;
-  const int per_sm = (ctas + 147) / 148;
-  size_t limit = (size_t)220 * 1024 / ((per_sm > 0 ? per_sm : 1) * C);
-  if (limit > 56 * 1024) limit = 56 * 1024;
-  if (limit < 12 * 1024) limit = 12 * 1024;
-  while (bytes(K, NS) > limit) {
-    if (K > 4) {
-      K >>= 1;
-    } else if (NS > 2) {
-      NS = 2;
-    } else if (K > 1) {
-      K >>= 1;
-    } else {
-      break;
-    }
-  }
-  if (tma_stage_override()) NS = tma_stage_override();
-  p.tma_k = K;
-  p.tma_stages = NS;
-  // tensor maps for the vertical chains (box = one pixel's labels x K image rows); the box must
-  // land 128-byte aligned in the staging ring
-  TmaMaps maps{};
-  p.tma_box = 0;
-  if (p.dir0 <= 3 && p.dir0 + p.ndirs > 2 && ((size_t)K * p.L * sizeof(float)) % 128 == 0 && p.L <= 256) {
-    const unsigned long long inner = (unsigned long long)p.W * p.L, rows = (unsigned long long)p.nimg * p.H;
-    if (encode_tmap_2d(&maps.a, p.unary, inner, rows, p.L, K) &&
-        encode_tmap_2d(&maps.b, p.msg_read, inner, rows * p.D, p.L, K))
-      p.tma_box = 1;
-  }
-  const size_t smem = bytes(K, NS) * C;
-  cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW, DT>, smem);
-  if (e != cudaSuccess) return e;
-  // the residency computed above assumes the largest shared-memory carve-out
-  e = cudaFuncSetAttribute(fwd_wide_kernel<LPT, RW, DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                           (int)cudaSharedmemCarveoutMaxShared);
-  if (e != cudaSuccess) return e;
-  ProfScope prof(kProfFwdSweep, st);
-  fwd_wide_kernel<LPT, RW, DT><<<ctas, C == 1 ? 96 : C * 64, smem, st>>>(p, maps);
-  count_launch();
-  return cudaGetLastError();
-}
-
-template <int LPT, int RW>
-cudaError_t launch_wide(const FwdParams& p, cudaStream_t st) {
-  if (p.agg) return launch_wide_d<LPT, RW, 2>(p, st);
-  if (p.D == 2) return cudaErrorNotSupported;  // DT == 2 is reserved for the aggregate mode
-  if (p.D == 4) return launch_wide_d<LPT, RW, 4>(p, st);
-  if (p.D == 8) return launch_wide_d<LPT, RW, 8>(p, st);
-  return launch_wide_d<LPT, RW, 0>(p, st);
-}
-
-template <int LPT>
-cudaError_t launch_wide_r(const FwdParams& p, int R, cudaStream_t st) {
-  if (R <= 2) return launch_wide<LPT, 2>(p, st);
-  if (R <= 4) return launch_wide<LPT, 4>(p, st);
-  if (R <= 8) return launch_wide<LPT, 8>(p, st);
-  return launch_wide<LPT, 16>(p, st);
-}
-
 // Variant with the context rows in shared memory (one [64][68] table per CTA; row stride 68 makes
 // the per-lane 16-byte row reads conflict-free): 164 registers instead of 255, so three chains
 // per SM sub-partition instead of two.  Lane l owns labels l and l + 32.  It is bound by shared
@@ -1815,13 +1446,7 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
   }
   if (p.ctx_rank == 1 && !train && p.host_windowed && p.host_R <= 16 && p.L <= 256 && cta_tma_eligible(p) &&
       (p.agg || p.D != 2)) {
-    const int lpt = 2 * ((p.L + 63) / 64);
-    switch (lpt) {
-      case 2: return launch_wide_r<2>(p, p.host_R, st);
-      case 4: return launch_wide_r<4>(p, p.host_R, st);
-      case 6: return launch_wide_r<6>(p, p.host_R, st);
-      default: return launch_wide_r<8>(p, p.host_R, st);
-    }
+    return launch_forward_wide(p, st);
   }
   if (p.L <= 64 && cta_tma_eligible(p) && !pair_kernels_disabled())
     return train ? launch_pair<true>(p, st) : launch_pair<false>(p, st);

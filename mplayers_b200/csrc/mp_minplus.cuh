@@ -5,6 +5,35 @@
 
 namespace mpl {
 
+// A chain of a forward launch: direction, image, start pixel, length and pixel step.
+struct ChainCtx {
+  int dir, inv, img, h0, w0, len, pstep;
+};
+
+__device__ __forceinline__ bool decode_chain(const FwdParams& p, int g, ChainCtx& c) {
+  if (g >= p.chain_off[p.ndirs]) return false;
+  int di = 0;
+  while (g >= p.chain_off[di + 1]) ++di;
+  c.dir = p.dir0 + di;
+  c.inv = c.dir ^ 1;
+  // When a launch covers only a part of the chains, both directions of a pair must cover the same
+  // lines (each reads the other's messages): the odd direction then enumerates the even one's
+  // chains and walks each from its far end.
+  const bool mirrored = p.parts > 1 && (c.dir & 1);
+  DirGeom geo = make_geom(mirrored ? c.inv : c.dir, p.H, p.W);
+  const int local = g - p.chain_off[di] + p.chain_begin[di];
+  c.img = local / geo.n_chains;
+  chain_start(geo, p.H, p.W, local - c.img * geo.n_chains, c.h0, c.w0, c.len);
+  if (mirrored) {
+    c.h0 += (c.len - 1) * geo.hs;
+    c.w0 += (c.len - 1) * geo.ws;
+    geo.hs = -geo.hs;
+    geo.ws = -geo.ws;
+  }
+  c.pstep = geo.hs * p.W + geo.ws;
+  return c.len >= 2;
+}
+
 __device__ __forceinline__ float min3f(float a, float b, float c) {
   float d;
   asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));  // 3-input min (sm_100)
