@@ -141,7 +141,8 @@ int mpl_isgmr_backward(const mpl_problem* p, const float* context, const float* 
  *   msg_edge_label [I,D,B,cv,H,W,L,L] f32: the edge values of every visited pixel, entry [f][c]
  *                  (front label f, label c) for even directions and [c][f] for odd ones, as the
  *                  reference stores them; msg_norm_index [I,D,B,cv,H,W] u8.  Both NULL = inference.
- *   n_disp <= 32 (MPL_ERR_UNSUPPORTED beyond: L*L values are saved per pixel, direction, iteration).
+ *   n_disp <= 64 (MPL_ERR_UNSUPPORTED beyond: L*L values are saved per pixel, direction, iteration;
+ *   up to 32 labels one warp per chain, 33..64 one CTA of 64 threads per chain).
  * Forward values agree with the reference kernels bit for bit (same intrinsics, same reduction
  * order); the backward accumulates dcontext on the diagonal too, as the reference does
  * (TRWP_backward_soft.cu:114-126).  dmsg is scratch [D,B,cv,H,W,L]. */

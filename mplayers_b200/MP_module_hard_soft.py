@@ -6,7 +6,7 @@ not skip c == f), (iii) returns two extra values.  With `args.mpnet_enable_soft`
 (expected-value) branch runs: the message is the expectation of the edge values under softmin
 weights; in training it saves the edge values [I,D,B,cv,H,W,L,L] (returned as `message_vector`)
 and the normalisation indices (returned as `message_index`), as the reference does
-(pytorch/MP_module_hard_soft.py:37-48,92-97); it is built for n_classes <= 32.
+(pytorch/MP_module_hard_soft.py:37-48,92-97); it is built for n_classes <= 64.
 """
 import torch
 import torch.nn as nn

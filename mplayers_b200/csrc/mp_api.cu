@@ -630,8 +630,8 @@ int mpl_trwp_soft_forward(const mpl_problem* p, const float* unary, const float*
   Dims d;
   if (int rc = validate(p, &d)) return rc;
   if (int rc = check_chain_count(p, d)) return rc;
-  if (p->n_disp > 32)
-    return fail(MPL_ERR_UNSUPPORTED, "soft TRWP is built for n_disp <= 32 (got %d): it saves n_disp^2 values per "
+  if (p->n_disp > 64)
+    return fail(MPL_ERR_UNSUPPORTED, "soft TRWP is built for n_disp <= 64 (got %d): it saves n_disp^2 values per "
                                      "pixel, direction and iteration", p->n_disp);
   if (!unary || !context || !msg || !cost_final) return fail(MPL_ERR_INVALID, "NULL tensor pointer");
   if ((msg_edge_label == nullptr) != (msg_norm_index == nullptr))
@@ -670,7 +670,7 @@ int mpl_trwp_soft_backward(const mpl_problem* p, const float* context, const flo
   Dims d;
   if (int rc = validate(p, &d)) return rc;
   if (int rc = check_chain_count(p, d)) return rc;
-  if (p->n_disp > 32) return fail(MPL_ERR_UNSUPPORTED, "soft TRWP is built for n_disp <= 32 (got %d)", p->n_disp);
+  if (p->n_disp > 64) return fail(MPL_ERR_UNSUPPORTED, "soft TRWP is built for n_disp <= 64 (got %d)", p->n_disp);
   if (!context || !dcost_final || !msg_edge_label || !msg_norm_index || !dunary || !dcontext || !dmsg)
     return fail(MPL_ERR_INVALID, "NULL tensor pointer");
   if (edge_weights && !dedge_weights)

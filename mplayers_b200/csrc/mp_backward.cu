@@ -26,31 +26,6 @@ namespace mpl {
 
 namespace {
 
-struct BChain {
-  int dir, img, h0, w0, len, pstep;
-};
-
-__device__ __forceinline__ bool decode_bchain(const BwdParams& p, int g, BChain& c) {
-  if (g >= p.chain_off[p.ndirs]) return false;
-  int di = 0;
-  while (g >= p.chain_off[di + 1]) ++di;
-  c.dir = p.dir + di;
-  // partial launches: the odd direction of a pair covers the even one's lines (see decode_chain)
-  const bool mirrored = p.parts > 1 && (c.dir & 1);
-  DirGeom geo = make_geom(mirrored ? (c.dir ^ 1) : c.dir, p.H, p.W);
-  const int local = g - p.chain_off[di] + p.chain_begin[di];
-  c.img = local / geo.n_chains;
-  chain_start(geo, p.H, p.W, local - c.img * geo.n_chains, c.h0, c.w0, c.len);
-  if (mirrored) {
-    c.h0 += (c.len - 1) * geo.hs;
-    c.w0 += (c.len - 1) * geo.ws;
-    geo.hs = -geo.hs;
-    geo.ws = -geo.ws;
-  }
-  c.pstep = geo.hs * p.W + geo.ws;
-  return true;
-}
-
 __device__ __forceinline__ void warp_sum2(float& a, float& b) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -1512,7 +1487,8 @@ cudaError_t launch_backward_soft_sweep(const BwdParams& p0, cudaStream_t st) {
   p.chain_off[1] = make_geom(p.dir, p.H, p.W).n_chains * p.nimg;
   const int total = p.chain_off[1];
   if (total == 0) return cudaSuccess;
-  if (p.L > 32 || p.cp_scheme != 1) return cudaErrorNotSupported;
+  if (p.cp_scheme != 1) return cudaErrorNotSupported;
+  if (p.L > 32) return launch_backward_soft_cta(p, total, st);  // one CTA per chain, up to 64 labels
   const int wpb = 4;
   const size_t smem = (size_t)wpb * ((bwd_soft_warp_floats(p.L) + 3) & ~3) * sizeof(float);
   auto go = [&](auto kernel) -> cudaError_t {

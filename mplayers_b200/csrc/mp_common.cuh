@@ -307,6 +307,9 @@ cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, flo
                                        int dir0, int ndirs, float rho, cudaStream_t st);
 cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st);
 cudaError_t launch_backward_soft_sweep(const BwdParams& p, cudaStream_t st);
+// Soft TRWP for 32 < L <= 64 (mp_soft_cta.cu).
+cudaError_t launch_forward_soft_cta(const FwdParams& p, bool train, cudaStream_t st);
+cudaError_t launch_backward_soft_cta(const BwdParams& p, int total, cudaStream_t st);
 // Stand-alone soft-weighted message ops (mp_swbp.cu).
 cudaError_t launch_soft_weighted_message(const float* msg, long long n_tables, int L, float* norm,
                                          uint8_t* min_ind, cudaStream_t st);

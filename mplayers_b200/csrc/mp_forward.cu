@@ -1458,7 +1458,7 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
 // Soft TRWP sweep of the directions described by p (L <= 32 only: one warp per chain).
 cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st) {
   if (p.chain_off[p.ndirs] == 0) return cudaSuccess;
-  if (p.L > 32) return cudaErrorNotSupported;
+  if (p.L > 32) return launch_forward_soft_cta(p, train, st);  // one CTA per chain, up to 64 labels
   if (p.L == 21) return train ? launch_warp_soft<21, true, true>(p, st) : launch_warp_soft<21, false, true>(p, st);
   if (p.L < 21) return train ? launch_warp_soft<21, true, false>(p, st) : launch_warp_soft<21, false, false>(p, st);
   return train ? launch_warp_soft<32, true, false>(p, st) : launch_warp_soft<32, false, false>(p, st);

@@ -34,6 +34,32 @@ __device__ __forceinline__ bool decode_chain(const FwdParams& p, int g, ChainCtx
   return c.len >= 2;
 }
 
+// A chain of a backward launch.
+struct BChain {
+  int dir, img, h0, w0, len, pstep;
+};
+
+__device__ __forceinline__ bool decode_bchain(const BwdParams& p, int g, BChain& c) {
+  if (g >= p.chain_off[p.ndirs]) return false;
+  int di = 0;
+  while (g >= p.chain_off[di + 1]) ++di;
+  c.dir = p.dir + di;
+  // partial launches: the odd direction of a pair covers the even one's lines (see decode_chain)
+  const bool mirrored = p.parts > 1 && (c.dir & 1);
+  DirGeom geo = make_geom(mirrored ? (c.dir ^ 1) : c.dir, p.H, p.W);
+  const int local = g - p.chain_off[di] + p.chain_begin[di];
+  c.img = local / geo.n_chains;
+  chain_start(geo, p.H, p.W, local - c.img * geo.n_chains, c.h0, c.w0, c.len);
+  if (mirrored) {
+    c.h0 += (c.len - 1) * geo.hs;
+    c.w0 += (c.len - 1) * geo.ws;
+    geo.hs = -geo.hs;
+    geo.ws = -geo.ws;
+  }
+  c.pstep = geo.hs * p.W + geo.ws;
+  return true;
+}
+
 __device__ __forceinline__ float min3f(float a, float b, float c) {
   float d;
   asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));  // 3-input min (sm_100)

@@ -64,6 +64,9 @@ SHAPES = [
     (8, 1, 1, 12, 11, 32, 2, "sym2d"),  # full warp
     (8, 1, 1, 10, 9, 17, 1, "tl1d"),    # rank-1 context
     (4, 1, 1, 40, 37, 21, 1, "sym2d"),  # chains longer than the staging ring
+    (4, 1, 1, 9, 11, 33, 2, "sym2d"),   # first label count of the CTA-per-chain kernels
+    (8, 2, 1, 10, 12, 64, 1, "sym2d"),  # their largest, diagonals, two images
+    (4, 1, 2, 7, 9, 48, 2, "tl1d"),     # rank-1 context, cv axis
 ]
 
 
@@ -112,9 +115,9 @@ def test_soft_module_autograd_and_limits():
     assert rel_err(u.grad.permute(0, 1, 3, 4, 2).cpu().numpy(), bw["dunary"]) < GRAD_RTOL
     assert rel_err(ctx.grad.cpu().numpy(), bw["dctx"]) < GRAD_RTOL
     assert rel_err(e.grad.unsqueeze(1).permute(2, 0, 1, 3, 4).cpu().numpy(), bw["dew"]) < GRAD_RTOL
-    # more than 32 labels: refused with a message, nothing computed on the CPU
-    args.n_classes = 40
+    # more than 64 labels: refused with a message, nothing computed on the CPU
+    args.n_classes = 70
     big = MPModule(args).cuda()
-    big.set_label_context(torch.zeros(40, 40, device="cuda"), None, None)
-    with pytest.raises(RuntimeError, match="n_disp <= 32"):
-        big(torch.zeros(1, 1, 40, 4, 4, device="cuda"))
+    big.set_label_context(torch.zeros(70, 70, device="cuda"), None, None)
+    with pytest.raises(RuntimeError, match="n_disp <= 64"):
+        big(torch.zeros(1, 1, 70, 4, 4, device="cuda"))
