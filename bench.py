@@ -34,6 +34,8 @@ WORKLOADS = {
     # name: (generator, kwargs, fwd+bwd?)
     "seg_trwp_train": ("config4_segmentation", {}, True),
     "stereo_trwp_infer": ("config2_stereo", {}, False),
+    # the same inputs as a training step (learning the truncated-linear function): indices saved, fwd+bwd
+    "stereo_trwp_train": ("config2_stereo", {"training": True}, True),
     "denoise_isgmr_infer": ("config3_denoise", {}, False),
     "large_isgmr_train": ("config5_large", {}, True),
     "config1_trwp_train": ("config1", {"mode": "TRWP"}, True),
@@ -202,7 +204,7 @@ def dominant_kernel(cfg, kind):
         return "bwd_pair_kernel" if pair else "bwd_cta_kernel"
     if L <= 32:
         return "fwd_tma_kernel"
-    if not cfg["training"] and cfg["label_context"].dim() == 1 and L % 4 == 0:
+    if (not cfg["training"] or L > 64) and cfg["label_context"].dim() == 1 and L % 4 == 0:
         return "fwd_wide_kernel"
     if pair:
         return "fwd_pair_smem_kernel"
@@ -440,29 +442,36 @@ def measure(r, steps, warmup, min_seconds, sampler, sync_all, with_e2e=True):
 def roofline_of(r, workload, m, steps, peak, peak_src):
     """Per-kind launch times against the byte model, the dominant kernel, and the whole step."""
     cfg, batch, prof = r.cfg, r.batch, m["prof"]
+    # direction sharding: a rank's sweep launch covers its own directions (or its part of a direction
+    # pair's chains) only, and the step's bytes are spread over all ranks
+    share = 1.0
+    if r.by_dir and r.world > 1:
+        _, count, _, parts = r.dsh.shard_plan(cfg["n_dir"], r.world)[r.rank]
+        share = count / float(parts * cfg["n_dir"])
     kinds = {}
     for k in ("fwd", "bwd", "elementwise"):
         if prof[k][1]:
             kinds[k] = {"launches": prof[k][1], "avg_launch_ms": round(prof[k][0] / prof[k][1], 5)}
             if k in ("fwd", "bwd"):
-                b = algorithmic_bytes(cfg, batch, k)
+                b = int(algorithmic_bytes(cfg, batch, k) * share)
                 gbs = b / (prof[k][0] / prof[k][1] * 1e-3) / 1e9
                 kinds[k].update({"kernel": dominant_kernel(cfg, k), "algorithmic_bytes_per_launch": b,
                                  "algorithmic_GBps": round(gbs, 1), "frac": round(gbs / peak, 4)})
                 tr = NCU_TRAFFIC.get((workload, k))
                 if tr is not None:
+                    tr = tr * share
                     kinds[k]["dram_bytes_per_launch"] = tr
                     kinds[k]["dram_frac"] = round(tr / (prof[k][0] / prof[k][1] * 1e-3) / 1e9 / peak, 4)
     fb, bb = step_bytes(cfg, batch, r.train)
     ms_step = m["ms"] / steps
-    step_frac = (fb + bb) / (ms_step * 1e-3) / 1e9 / peak
+    step_frac = (fb + bb) / (ms_step * 1e-3) / 1e9 / peak / (r.world if r.by_dir else 1)
     dom = "bwd" if (r.train and prof["bwd"][0] >= prof["fwd"][0]) else "fwd"
     roof = None
     if dom in kinds:
         d = kinds[dom]
         roof = {"bound": "hbm", "kernel": d["kernel"], "achieved": d["algorithmic_GBps"], "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": d["frac"],
-                "traffic": NCU_TRAFFIC.get((workload, dom)), "avg_launch_ms": d["avg_launch_ms"],
+                "traffic": d.get("dram_bytes_per_launch"), "avg_launch_ms": d["avg_launch_ms"],
                 "algorithmic_bytes_per_launch": d["algorithmic_bytes_per_launch"],
                 "fwd_frac": kinds.get("fwd", {}).get("frac"), "bwd_frac": kinds.get("bwd", {}).get("frac"),
                 "step_frac": round(step_frac, 4), "step_algorithmic_bytes": fb + bb,

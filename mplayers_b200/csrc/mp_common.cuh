@@ -296,7 +296,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned by
 cudaError_t launch_analyze(const float* ctx, int L, int rank, const float* ew, long long n_ew,
                            CtxInfo* info, cudaStream_t st);
 cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st);
-cudaError_t launch_forward_wide(const FwdParams& p, cudaStream_t st);  // mp_wide.cu
+cudaError_t launch_forward_wide(const FwdParams& p, bool train, cudaStream_t st);  // mp_wide.cu
 cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, uint8_t* label,
                              long long npix, int L, int D, long long slice, float factor,
                              int min_a_dir, cudaStream_t st);

@@ -1444,9 +1444,10 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
     if (p.L == 21) return train ? launch_warp<21, true>(rest, st) : launch_warp<21, false>(rest, st);
     return train ? launch_warp<32, true>(rest, st) : launch_warp<32, false>(rest, st);
   }
-  if (p.ctx_rank == 1 && !train && p.host_windowed && p.host_R <= 16 && p.L <= 256 && cta_tma_eligible(p) &&
-      (p.agg || p.D != 2)) {
-    return launch_forward_wide(p, st);
+  // windowed rank-1 context: warp-per-chain kernel (training keeps the pair kernel up to 64 labels)
+  if (p.ctx_rank == 1 && (!train || p.L > 64) && p.host_windowed && p.host_R <= 16 && p.L <= 256 &&
+      cta_tma_eligible(p) && (p.agg || p.D != 2)) {
+    return launch_forward_wide(p, train, st);
   }
   if (p.L <= 64 && cta_tma_eligible(p) && !pair_kernels_disabled())
     return train ? launch_pair<true>(p, st) : launch_pair<false>(p, st);

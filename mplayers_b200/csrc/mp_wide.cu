@@ -1,6 +1,6 @@
-// Forward sweep for inference with a rank-1 context that saturates inside a window (truncated
-// linear / quadratic, Potts), 32 < L <= 256, L % 4 == 0: several labels per lane, one or several
-// warps per chain.  Replaces, for those problems, the reference's chain kernels
+// Forward sweep (inference, and training with saved indices) with a rank-1 context that saturates
+// inside a window (truncated linear / quadratic, Potts), 32 < L <= 256, L % 4 == 0: one warp per
+// chain, several labels per lane.  Replaces, for those problems, the reference's chain kernels
 // (MPLayers/TRWP/TRWP_forward.cu:82-376) with their one thread per label and L block barriers
 // per step.
 #include <cstdlib>
@@ -35,7 +35,7 @@ __host__ __device__ inline size_t wide_chain_bytes(int ns, int A, int k, int L, 
 }
 
 // ------------------------------------------------------------------------------------------------
-// Inference, rank-1 context that saturates inside a window (truncated linear / quadratic, Potts),
+// Rank-1 context that saturates inside a window (truncated linear / quadratic, Potts),
 // 32 < L <= 256, L % 4 == 0: one WARP per chain, LPT = ceil(L/32) consecutive labels per lane.
 //
 // With several labels per lane the whole label vector of a chain lives in one warp's registers:
@@ -46,7 +46,21 @@ __host__ __device__ inline size_t wide_chain_bytes(int ns, int A, int k, int L, 
 // RW = compile-time window half-width (candidates |c-f| < RW; RW >= R of the context: offsets
 // beyond R carry the saturated value, which is an exact candidate of the dense evaluation too).
 // ------------------------------------------------------------------------------------------------
-template <int LPT, int RW, int DT>
+// TRAIN: also saves the argmin index of every label and the normalisation index, with the
+// reference's rule (highest index among equal minima, MPLayers/TRWP/TRWP_forward.cu:126-152).  A
+// source label outside the window contributes the saturated candidate fma(e, cmax, h[f]); fma is
+// monotone in h[f], so the smallest of them is fma(e, cmax, min h) = gv, and fstar is the highest
+// label whose saturated candidate equals gv (rounding can make several h values tie).  Inside the
+// window fw is the highest offset attaining the minimum.  The index is fw, unless gv attains the
+// minimum too: then the higher of fw and fstar (if fstar lies inside the window its true candidate is
+// no larger than gv, so it is counted by fw already).
+__device__ __forceinline__ int warp_max_i32(int v) {
+  int m;
+  asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;" : "=r"(m) : "r"(v));
+  return m;
+}
+
+template <int LPT, int RW, int DT, bool TRAIN = false>
 __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __grid_constant__ FwdParams p,
                                                                        const __grid_constant__ TmaMaps maps) {
   extern __shared__ __align__(128) float smem_all[];
@@ -147,6 +161,8 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
 #pragma unroll
   for (int k = 0; k < RW; ++k) cw[k] = k < L ? __ldg(p.ctx + k) : cmax;
   float* Mw = p.msg_write + (long long)ch.dir * p.slice + ibase * L;
+  uint8_t* MI = TRAIN ? p.min_idx + (long long)ch.dir * p.slice + ibase * L : nullptr;
+  uint8_t* NI = TRAIN ? p.norm_idx + (long long)ch.dir * p.pslice + ibase : nullptr;
   const float* E = p.ew ? p.ew + (long long)ch.dir * p.pslice + ibase : nullptr;
   const int c0 = lane * LPT;                    // first label of this lane
   const int nl = L - c0 < 0 ? 0 : (L - c0 < LPT ? L - c0 : LPT);  // labels of this lane that exist
@@ -219,8 +235,8 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
         const float e = et[k];
         float* hw = hwin + ((s * K + k) & 1) * (LP + 2 * G);
         float hl = kInf;
+        float hv[LPT];
         if (nl == LPT) {
-          float hv[LPT];
 #pragma unroll
           for (int i = 0; i < LPT; ++i) {
             hv[i] = fmaf(rho, r[i], uu[i]);
@@ -232,14 +248,22 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
         } else {
 #pragma unroll
           for (int i = 0; i < LPT; ++i) {
-            const float h = fmaf(rho, r[i], uu[i]);
+            hv[i] = fmaf(rho, r[i], uu[i]);
             if (i < nl) {
-              hw[G + c0 + i] = h;
-              hl = fminf(hl, h);
+              hw[G + c0 + i] = hv[i];
+              hl = fminf(hl, hv[i]);
             }
           }
         }
-        const float gv = fmaf(e, cmax, warp_min(hl));  // candidate through the saturated value
+        const float hmin = warp_min(hl);
+        const float gv = fmaf(e, cmax, hmin);  // candidate through the saturated value
+        int fstar = 0;                         // TRAIN: highest label whose saturated candidate equals gv
+        if (TRAIN) {
+          int lf = -1;
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) lf = (i < nl && fmaf(e, cmax, hv[i]) == gv) ? c0 + i : lf;
+          fstar = warp_max_i32(lf);
+        }
         __syncwarp();
         // window of this lane: labels c0 - G .. c0 + LPT + G - 1 (guards read +inf)
         float win[NWV * 2];
@@ -257,6 +281,7 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
           }
         }
         float best[LPT];
+        int bidx[TRAIN ? LPT : 1];
         float bl = kInf;
 #pragma unroll
         for (int i = 0; i < LPT; ++i) {
@@ -267,9 +292,35 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
             cand[kk + RW] = fmaf(e, cw[kk < 0 ? -kk : kk], win[G + i + kk]);
           best[i] = min_tree<2 * RW>(cand);
           if (i < nl) bl = fminf(bl, best[i]);
+          if constexpr (TRAIN) {
+            // highest window offset attaining the minimum (candidates outside 0..L-1 read +inf)
+            int fw = -1;
+#pragma unroll
+            for (int kk = -(RW - 1); kk <= RW - 1; ++kk) fw = (cand[kk + RW] == best[i]) ? c0 + i + kk : fw;
+            bidx[i] = (gv == best[i]) ? (fstar > fw ? fstar : fw) : fw;
+          }
         }
         const float m = warp_min(bl);
-        float* out = Mw + (long long)(pix0 + (s * K + k) * ch.pstep) * L + c0;
+        const int pxo = pix0 + (s * K + k) * ch.pstep;
+        if constexpr (TRAIN) {
+          int ln = -1;
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) ln = (i < nl && best[i] == m) ? c0 + i : ln;
+          const int nrm = warp_max_i32(ln);
+          if (lane == 0) NI[pxo] = (uint8_t)nrm;
+          uint8_t* mi = MI + (long long)pxo * L + c0;
+          if (nl == LPT) {
+#pragma unroll
+            for (int q = 0; q < LPT / 2; ++q)
+              reinterpret_cast<unsigned short*>(mi)[q] =
+                  (unsigned short)((bidx[2 * q] & 0xff) | ((bidx[2 * q + 1] & 0xff) << 8));
+          } else {
+#pragma unroll
+            for (int i = 0; i < LPT; ++i)
+              if (i < nl) mi[i] = (uint8_t)bidx[i];
+          }
+        }
+        float* out = Mw + (long long)pxo * L + c0;
 #pragma unroll
         for (int i = 0; i < LPT; ++i) r[i] = best[i] - m;
         if (nl == LPT) {
@@ -292,7 +343,7 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
 }
 
 
-template <int LPT, int RW, int DT>
+template <int LPT, int RW, int DT, bool TRAIN>
 cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
   const int total = p.chain_off[p.ndirs];
   const int A = (p.agg ? 2 : p.D) + 1;
@@ -332,47 +383,53 @@ cudaError_t launch_wide_d(FwdParams p, cudaStream_t st) {
       p.tma_box = 1;
   }
   const size_t smem = bytes(K, NS) * C;
-  cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW, DT>, smem);
+  cudaError_t e = ensure_smem(fwd_wide_kernel<LPT, RW, DT, TRAIN>, smem);
   if (e != cudaSuccess) return e;
   // the residency computed above assumes the largest shared-memory carve-out
-  e = cudaFuncSetAttribute(fwd_wide_kernel<LPT, RW, DT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  e = cudaFuncSetAttribute(fwd_wide_kernel<LPT, RW, DT, TRAIN>, cudaFuncAttributePreferredSharedMemoryCarveout,
                            (int)cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return e;
   ProfScope prof(kProfFwdSweep, st);
-  fwd_wide_kernel<LPT, RW, DT><<<ctas, C == 1 ? 96 : C * 64, smem, st>>>(p, maps);
+  fwd_wide_kernel<LPT, RW, DT, TRAIN><<<ctas, C == 1 ? 96 : C * 64, smem, st>>>(p, maps);
   count_launch();
   return cudaGetLastError();
 }
 
-template <int LPT, int RW>
+template <int LPT, int RW, bool TRAIN>
 cudaError_t launch_wide(const FwdParams& p, cudaStream_t st) {
-  if (p.agg) return launch_wide_d<LPT, RW, 2>(p, st);
+  if (p.agg) return launch_wide_d<LPT, RW, 2, TRAIN>(p, st);
   if (p.D == 2) return cudaErrorNotSupported;  // DT == 2 is reserved for the aggregate mode
-  if (p.D == 4) return launch_wide_d<LPT, RW, 4>(p, st);
-  if (p.D == 8) return launch_wide_d<LPT, RW, 8>(p, st);
-  return launch_wide_d<LPT, RW, 0>(p, st);
+  if (p.D == 4) return launch_wide_d<LPT, RW, 4, TRAIN>(p, st);
+  if (p.D == 8) return launch_wide_d<LPT, RW, 8, TRAIN>(p, st);
+  return launch_wide_d<LPT, RW, 0, TRAIN>(p, st);
 }
 
-template <int LPT>
+template <int LPT, bool TRAIN>
 cudaError_t launch_wide_r(const FwdParams& p, int R, cudaStream_t st) {
-  if (R <= 2) return launch_wide<LPT, 2>(p, st);
-  if (R <= 4) return launch_wide<LPT, 4>(p, st);
-  if (R <= 8) return launch_wide<LPT, 8>(p, st);
-  return launch_wide<LPT, 16>(p, st);
+  if (R <= 2) return launch_wide<LPT, 2, TRAIN>(p, st);
+  if (R <= 4) return launch_wide<LPT, 4, TRAIN>(p, st);
+  if (R <= 8) return launch_wide<LPT, 8, TRAIN>(p, st);
+  return launch_wide<LPT, 16, TRAIN>(p, st);
+}
+
+template <bool TRAIN>
+cudaError_t launch_wide_l(const FwdParams& p, cudaStream_t st) {
+  const int lpt = 2 * ((p.L + 63) / 64);
+  switch (lpt) {
+    case 2: return launch_wide_r<2, TRAIN>(p, p.host_R, st);
+    case 4: return launch_wide_r<4, TRAIN>(p, p.host_R, st);
+    case 6: return launch_wide_r<6, TRAIN>(p, p.host_R, st);
+    default: return launch_wide_r<8, TRAIN>(p, p.host_R, st);
+  }
 }
 
 }  // namespace
 
 // Dispatch on labels per lane and window width; the caller has checked that the windowed
 // evaluation is exact (FwdParams::host_windowed) and that the staging alignment rules hold.
-cudaError_t launch_forward_wide(const FwdParams& p, cudaStream_t st) {
-  const int lpt = 2 * ((p.L + 63) / 64);
-  switch (lpt) {
-    case 2: return launch_wide_r<2>(p, p.host_R, st);
-    case 4: return launch_wide_r<4>(p, p.host_R, st);
-    case 6: return launch_wide_r<6>(p, p.host_R, st);
-    default: return launch_wide_r<8>(p, p.host_R, st);
-  }
+// `train`: the sweep also saves the argmin and normalisation indices (FwdParams::min_idx / norm_idx).
+cudaError_t launch_forward_wide(const FwdParams& p, bool train, cudaStream_t st) {
+  return train ? launch_wide_l<true>(p, st) : launch_wide_l<false>(p, st);
 }
 
 }  // namespace mpl

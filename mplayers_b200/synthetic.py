@@ -63,7 +63,7 @@ def config1(mode="TRWP", seed=0):
                 edge_weights=0.5 + 0.5 * torch.rand(1, D, H, W, generator=g))
 
 
-def config2_stereo(seed=0, H=375, W=1242, L=192, n_iter=3):
+def config2_stereo(seed=0, H=375, W=1242, L=192, n_iter=3, training=False):
     """Stereo TRWP forward: piecewise-planar disparity from 20 planes over a Voronoi partition,
     unary min(|d-d_gt|/8, 1) + U[0,0.3], 10% outlier pixels U[0,1]; truncated linear pairwise."""
     g = _gen(seed)
@@ -82,7 +82,7 @@ def config2_stereo(seed=0, H=375, W=1242, L=192, n_iter=3):
     noise = torch.rand(L, H, W, generator=g)
     unary = torch.where(outl[None], noise, unary)
     ctx = torch.arange(L, dtype=torch.float32).clamp(max=2.0)
-    return dict(mode="TRWP", n_dir=4, n_iter=n_iter, training=False,
+    return dict(mode="TRWP", n_dir=4, n_iter=n_iter, training=training,
                 unary=unary.view(1, 1, L, H, W).contiguous(), label_context=ctx, edge_weights=None)
 
 

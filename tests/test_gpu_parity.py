@@ -230,6 +230,45 @@ def test_wide_inference_kernel(mode, D, H, W, L, kind, ewk):
     assert np.array_equal(got["label_all"], want["label_all"])
 
 
+@pytest.mark.parametrize("mode,D,H,W,L,kind,ewk,quant", [
+    ("TRWP", 4, 11, 23, 192, "tl1d", "none", False),   # 6 labels per lane, window 2
+    ("ISGMR", 4, 9, 10, 256, "tq1d", "none", False),   # 8 labels per lane, window 16, aggregate mode
+    ("TRWP", 16, 9, 8, 100, "tq1d", "pos", False),     # L not a multiple of the lane block, diagonals
+    ("ISGMR", 8, 10, 9, 128, "tl1d", "pos", False),
+    ("ISGMR", 4, 8, 9, 128, "potts1d", "none", False),
+    ("TRWP", 4, 9, 21, 192, "tl1d", "none", True),     # quantised costs: exact ties everywhere
+    ("ISGMR", 8, 8, 9, 96, "tq1d", "pos", True),
+    ("TRWP", 4, 8, 9, 128, "potts1d", "none", True),
+])
+def test_wide_training_kernel(mode, D, H, W, L, kind, ewk, quant):
+    """Training with a windowed rank-1 context and more than 64 labels runs the warp-per-chain kernel
+    too.  Its saved indices follow the reference's rule among equal candidates
+    (MPLayers/TRWP/TRWP_forward.cu:126-152: the highest index wins), so they must EQUAL the dense
+    evaluation's, also where costs quantised to quarters make most minima tie; the backward pass
+    replays them."""
+    g = _gpu()
+    rng = np.random.default_rng(1300 + L + D + (7 if quant else 0))
+    unary = rng.standard_normal((2, 1, H, W, L)).astype(np.float32)
+    if quant:
+        unary = np.round(unary * 2) / 2
+    if kind == "potts1d":
+        ctx = np.ones(L, np.float32)
+        ctx[0] = 0
+    else:
+        ctx = cases.make_context(kind, L, rng)
+        if quant:
+            ctx = np.round(ctx * 4) / 4
+    ew = None if ewk == "none" else rng.uniform(0.2, 1.0, size=(D, 2, 1, H, W)).astype(np.float32)
+    if quant and ew is not None:
+        ew = np.round(ew * 4 + 1) / 4
+    dcost = rng.uniform(0, 1, size=unary.shape).astype(np.float32)
+    got = g.forward(mode, unary, ctx, ew, D, 2, save_labels=True)
+    want = oracle.forward(mode, unary, ctx, ew, D, 2, save_labels=True)
+    for k in ("cost", "msg", "norm_idx", "min_idx", "label_all"):
+        assert np.array_equal(got[k], want[k]), k
+    _check_backward(mode, ctx, ew, dcost, want)
+
+
 @pytest.mark.parametrize("mode,D,L,I", [
     ("ISGMR", 8, 64, 2), ("ISGMR", 8, 64, 3),   # aggregate path (many labels / directions), even and odd iteration counts
     ("ISGMR", 4, 21, 2), ("ISGMR", 4, 21, 3),   # every slice staged
