@@ -38,7 +38,7 @@ def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weig
 
 
 def backward(enable_sgm, rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,
-             dunary, dcontext, dedge_weights, dmsg, dunary_update, dmsg_update, keep_diag=False):
+             dunary, dcontext, dedge_weights, dmsg, dunary_update, dmsg_update, keep_diag=False, context_window=0):
     dev = dcost_final.device
     for t, n in ((context, "context"), (edge_weights, "edge_weights"), (dcost_final, "dcost_final"),
                  (dunary, "dunary"), (dcontext, "dcontext"), (dedge_weights, "dedge_weights"),
@@ -49,7 +49,7 @@ def backward(enable_sgm, rho, context, edge_weights, dcost_final, msg_min_index,
     if msg_min_index.dim() != 7:
         raise RuntimeError("msg_min_index must be [I,D,B,cv,H,W,L]")
     prob = _problem(msg_min_index.size(0), tuple(msg_min_index.shape[1:]), context, rho,
-                    enable_sgm=enable_sgm, keep_diag_=keep_diag)
+                    enable_sgm=enable_sgm, keep_diag_=keep_diag, context_window=max(int(context_window), 0))
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_backward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)

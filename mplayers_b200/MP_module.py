@@ -83,6 +83,7 @@ class TRWPFunction(torch.autograd.Function):
                       cost_final, message_index, cost_index, _empty_f32(unary.device), label_all,
                       context_window=int(getattr(args, "context_window", 0) or 0))
         ctx.intermediate_results = rho, message_index, cost_index, label_context, ew, enable_edge_weights
+        ctx.context_window = int(getattr(args, "context_window", 0) or 0)
         ctx.norm_index_override = _norm_index_override(args, cost_index, n_disp)
         ctx.mark_non_differentiable(label_all)
         return cost_final, label_all
@@ -104,7 +105,7 @@ class TRWPFunction(torch.autograd.Function):
         dedge_weights = torch.zeros_like(ew) if enable_edge_weights else _empty_f32(dcost_final.device)
         _TRWP.backward(rho, label_context, ew, dcost_final, message_index, cost_index, dunary,
                        dlabel_context, dedge_weights, dmessage, _empty_f32(dcost_final.device),
-                       keep_diag=ctx._forward_cls.keep_diag)
+                       keep_diag=ctx._forward_cls.keep_diag, context_window=ctx.context_window)
         return dunary, dlabel_context, (dedge_weights if enable_edge_weights else None), None
 
 
@@ -130,6 +131,7 @@ class ISGMRFunction(torch.autograd.Function):
                        context_window=int(getattr(args, "context_window", 0) or 0))
         ctx.intermediate_results = args.enable_sgm, rho, message_index, cost_index, label_context, ew, \
             enable_edge_weights
+        ctx.context_window = int(getattr(args, "context_window", 0) or 0)
         ctx.mark_non_differentiable(label_all)
         return cost_final, label_all
 
@@ -150,7 +152,7 @@ class ISGMRFunction(torch.autograd.Function):
         dedge_weights = torch.zeros_like(ew) if enable_edge_weights else _empty_f32(dcost_final.device)
         _ISGMR.backward(int(enable_sgm), rho, label_context, ew, dcost_final, message_index, cost_index,
                         dunary, dlabel_context, dedge_weights, dmessage,
-                        _empty_f32(dcost_final.device), dmessage_tmp)
+                        _empty_f32(dcost_final.device), dmessage_tmp, context_window=ctx.context_window)
         return dunary, dlabel_context, (dedge_weights if enable_edge_weights else None), None
 
 

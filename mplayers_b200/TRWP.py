@@ -50,7 +50,10 @@ def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, co
 
 
 def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index, dunary,
-             dcontext, dedge_weights, dmsg, dunary_update, keep_diag=None):
+             dcontext, dedge_weights, dmsg, dunary_update, keep_diag=None, context_window=0):
+    """`context_window` (keyword, not in the reference's signature): in the backward pass only a hint
+    for how the scatter of a rank-1 context with more than 64 labels is split; any value gives the
+    same sums."""
     dev = dcost_final.device
     for t, n in ((context, "context"), (edge_weights, "edge_weights"), (dcost_final, "dcost_final"),
                  (dunary, "dunary"), (dcontext, "dcontext"), (dedge_weights, "dedge_weights"),
@@ -62,7 +65,7 @@ def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_in
         raise RuntimeError("msg_min_index must be [I,D,B,cv,H,W,L]")
     kd = globals()["keep_diag"] if keep_diag is None else keep_diag
     prob = _problem(msg_min_index.size(0), tuple(msg_min_index.shape[1:]), context, rho,
-                    keep_diag_=kd)
+                    keep_diag_=kd, context_window=max(int(context_window), 0))
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_backward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)

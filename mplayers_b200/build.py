@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmplayers_b200.so")
-SOURCES = ["mp_api.cu", "mp_forward.cu", "mp_backward.cu", "mp_wide.cu", "mp_soft_cta.cu", "mp_terms.cu", "mp_swbp.cu"]
+SOURCES = ["mp_api.cu", "mp_forward.cu", "mp_backward.cu", "mp_wide.cu", "mp_wide_bwd.cu", "mp_soft_cta.cu", "mp_terms.cu", "mp_swbp.cu"]
 HEADERS = [os.path.join(CSRC, "mp_common.cuh"), os.path.join(CSRC, "mp_minplus.cuh"),
            os.path.join(os.path.dirname(HERE), "include", "mplayers_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

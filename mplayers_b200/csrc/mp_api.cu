@@ -342,6 +342,7 @@ void fill_backward(mpl::BwdParams& bp, const mpl_problem* p, const Dims& d, cons
   bp.ctx_rank = p->context_rank;
   bp.keep_diag = p->keep_diag;
   bp.cp_scheme = cp;
+  bp.window = p->context_window > 0 ? p->context_window : 0;
   bp.status = status;
 }
 
@@ -374,7 +375,9 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   // which knows the C + P scheme as well.)
   const bool pair_cp = L <= 64 && (L & 3) == 0 && ((((uintptr_t)dunary | (uintptr_t)dmsg) & 15) == 0) &&
                        !mpl::pair_kernels_disabled();
-  const int cp = isgmr ? 2 : ((L <= 32 || pair_cp) ? 1 : 0);
+  // (a rank-1 context with 64 < L <= 256 runs the several-labels-per-lane kernel, C + P too)
+  const bool wide_cp = mpl::bwd_wide_eligible(L, p->context_rank, 1, dunary, dmsg, dmsg);
+  const int cp = isgmr ? 2 : ((L <= 32 || pair_cp || wide_cp) ? 1 : 0);
   float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced
   float* Y = isgmr ? dmsg : dmsg;         // gradients of the messages the sweeps read
   MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp == 1, st));

@@ -1463,6 +1463,9 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
       e = p.cp_scheme == 1 ? go(bwd_pair_kernel<1, false>) : go(bwd_pair_kernel<2, false>);
     }
     if (e != cudaSuccess) return e;
+  } else if (bwd_wide_eligible(L, p.ctx_rank, p.cp_scheme, p.dunary, p.dm_read, p.dm_acc)) {
+    cudaError_t e = launch_backward_wide(p, total, st);
+    if (e != cudaSuccess) return e;
   } else {
     const int NT = ((L + 31) / 32) * 32;
     p.table_in_smem = (p.ctx_rank == 2 && L <= kSmemTableMaxL) ? 1 : 0;

@@ -154,6 +154,8 @@ struct BwdParams {
   // dM_k = rho*Q - rho*q_k - q_inv(k), dU += rho*Q with Q = sum_d q_d.
   int cp_scheme;
   int tma_stages;
+  int tma_k;              // wide kernel: chain steps per stage
+  int window;             // wide kernel: the caller's statement about a rank-1 context (mpl_problem::context_window), or 0
   int* status;            // device word: 0 = ok, else the code of a wait that gave up
 };
 
@@ -303,6 +305,10 @@ cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, 
 cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, long long n, int D,
                                  float factor, int cp_scheme, cudaStream_t st);
 cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
+// mp_wide_bwd.cu: rank-1 context, 64 < L <= 256, L % 4 == 0, schemes 1 and 2
+bool bwd_wide_eligible(int L, int ctx_rank, int cp_scheme, const void* dunary, const void* dm_read,
+                       const void* dm_acc);
+cudaError_t launch_backward_wide(const BwdParams& p, int total, cudaStream_t st);
 cudaError_t launch_isgmr_combine_total(const float* q_total, const float* q, float* dm, float* dunary, long long n,
                                        int dir0, int ndirs, float rho, cudaStream_t st);
 cudaError_t launch_forward_soft_sweep(const FwdParams& p, bool train, cudaStream_t st);

@@ -40,7 +40,7 @@ def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=Tr
 
 
 def backward(mode, ctx, edge_weights, dcost, min_idx, norm_idx, rho=None, enable_sgm=False,
-             keep_diag=False):
+             keep_diag=False, context_window=0):
     if rho is None:
         rho = 0.5 if mode == "TRWP" else 1.0
     g = _dev(dcost)
@@ -56,11 +56,12 @@ def backward(mode, ctx, edge_weights, dcost, min_idx, norm_idx, rho=None, enable
     # scratch is deliberately filled with garbage: the library must not rely on its contents
     dmsg = torch.full((n_dir,) + tuple(g.shape), float("nan"), device="cuda")
     if mode == "TRWP":
-        TRWP.backward(rho, c, ew, g, mi, ni, dunary, dctx, dew, dmsg, e0, keep_diag=keep_diag)
+        TRWP.backward(rho, c, ew, g, mi, ni, dunary, dctx, dew, dmsg, e0, keep_diag=keep_diag,
+                      context_window=context_window)
     else:
         dmu = torch.full_like(dmsg, float("nan"))
         ISGMR.backward(int(enable_sgm), rho, c, ew, g, mi, ni, dunary, dctx, dew, dmsg, e0, dmu,
-                       keep_diag=keep_diag)
+                       keep_diag=keep_diag, context_window=context_window)
     torch.cuda.synchronize()
     return dict(dunary=dunary.cpu().numpy(), dctx=dctx.cpu().numpy(),
                 dew=dew.cpu().numpy() if edge_weights is not None else None)

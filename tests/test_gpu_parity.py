@@ -269,6 +269,44 @@ def test_wide_training_kernel(mode, D, H, W, L, kind, ewk, quant):
     _check_backward(mode, ctx, ew, dcost, want)
 
 
+@pytest.mark.parametrize("mode,D,H,W,L,kind,ewk", [
+    ("TRWP", 4, 19, 37, 192, "tl1d", "pos"),       # 6 labels per lane; chains longer than two stages
+    ("ISGMR", 4, 9, 21, 256, "tq1d", "none"),      # 8 labels per lane, scatter-field scheme
+    ("TRWP", 16, 9, 8, 100, "tq1d", "pos"),        # 4 labels per lane, a partly filled lane, diagonals
+    ("ISGMR", 8, 11, 9, 136, "tl1d", "pos"),       # 6 labels per lane with a partly filled lane
+    ("TRWP", 4, 8, 19, 128, "nonmono1d", "pos"),   # context that does not saturate: many far targets per step
+    ("ISGMR", 4, 8, 9, 68, "nonmono1d", "none"),
+    ("TRWP", 4, 9, 13, 96, "potts1d", "none"),
+])
+def test_wide_backward_kernel(mode, D, H, W, L, kind, ewk):
+    """Backward pass for a rank-1 context with 64 < L <= 256, L % 4 == 0: warp-per-chain kernel with
+    several labels per lane.  The split of the scatter into near and far indices is a tuning
+    parameter (the window hint): every width, and no hint, must give the oracle's gradients."""
+    g = _gpu()
+    rng = np.random.default_rng(1700 + L + D)
+    unary = rng.standard_normal((2, 1, H, W, L)).astype(np.float32)
+    if kind == "potts1d":
+        ctx = np.ones(L, np.float32)
+        ctx[0] = 0
+    elif kind == "nonmono1d":
+        ctx = rng.uniform(0, 2, size=(L,)).astype(np.float32)
+        ctx[0] = 0
+    else:
+        ctx = cases.make_context(kind, L, rng)
+    ew = None if ewk == "none" else rng.uniform(0.2, 1.0, size=(D, 2, 1, H, W)).astype(np.float32)
+    dcost = rng.uniform(0, 1, size=unary.shape).astype(np.float32)
+    fwd = oracle.forward(mode, unary, ctx, ew, D, 2)
+    for keep_diag in (False, True):
+        want = oracle.backward(mode, ctx, ew, dcost, fwd["min_idx"], fwd["norm_idx"], keep_diag=keep_diag)
+        for window in (0, 1, 3, 6, 16):
+            got = g.backward(mode, ctx, ew, dcost, fwd["min_idx"], fwd["norm_idx"], keep_diag=keep_diag,
+                             context_window=window)
+            assert_grad_close(got["dunary"], want["dunary"], "dunary w%d" % window)
+            assert_grad_close(got["dctx"], want["dctx"], "dctx w%d" % window)
+            if ew is not None:
+                assert_grad_close(got["dew"], want["dew"], "dew w%d" % window)
+
+
 @pytest.mark.parametrize("mode,D,L,I", [
     ("ISGMR", 8, 64, 2), ("ISGMR", 8, 64, 3),   # aggregate path (many labels / directions), even and odd iteration counts
     ("ISGMR", 4, 21, 2), ("ISGMR", 4, 21, 3),   # every slice staged
