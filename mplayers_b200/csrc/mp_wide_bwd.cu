@@ -17,9 +17,16 @@ constexpr int kWNS = 2;  // stages in flight per warp
 
 // Floats of shared memory per warp: staged gradients [kWNS][NA][K][L], argmin indices
 // [kWNS][K][L] bytes, product tile [16][33], t and index-as-float windows [2][2][LP + 2G], the
-// chain's label-context gradient table [L], the far scatter buffer [LP], kWNS mbarriers.
+// chain's label-context gradient table by SIGNED offset c - f [2L], the far scatter buffer [LP],
+// kWNS mbarriers.
 __host__ __device__ inline int bwd_wide_floats(int L, int lp, int g, int K, int na) {
-  return kWNS * na * K * L + kWNS * K * L / 4 + 16 * 33 + 4 * (lp + 2 * g) + ((L + 3) & ~3) + lp + 2 * kWNS + 2;
+  return kWNS * na * K * L + kWNS * K * L / 4 + 16 * 33 + 4 * (lp + 2 * g) + ((2 * L + 3) & ~3) + lp + 2 * kWNS + 2;
+}
+
+// Two adjacent floats added to global memory with one reduction (8-byte aligned address).
+__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(__cvta_generic_to_global(addr)), "f"(a), "f"(b)
+               : "memory");
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -29,14 +36,19 @@ __host__ __device__ inline int bwd_wide_floats(int L, int lp, int g, int K, int 
 //   dE[cur] += sum_c ctx[|c - f[c]|] * t[c];   dctx[|c - f[c]|] += E * t[c]
 // The scatter q' is split by the distance |c - f[c]|:
 //  * near (< RW): lane-local gather over the 2 RW - 1 neighbours of each of its labels from a
-//    window of t and f in shared memory -- one compare-to-flag and one packed fma per candidate,
-//    the second half of the packed fma accumulating the per-offset sums of the label-context
-//    gradient in registers;
+//    window of t and f in shared memory -- per candidate one compare-to-flag, one multiply and two
+//    adds, the second add accumulating the per-offset sums of the label-context gradient in
+//    registers;
 //  * far: with a context that saturates, every label whose minimum came through the saturated value
 //    points at the SAME label (the one with the smallest h), so the far labels that share the
 //    target of the first of them are summed with one warp reduction and handed to the target's
 //    lane; whatever is left after that round (other targets: possible only among exactly tied
 //    candidates, or with a context that does not saturate) goes through shared-memory atomics.
+//    The label-context gradient of the far labels is kept by SIGNED offset c - f: the labels that
+//    share a target then own distinct cells, so the round adds to them without atomics (float
+//    atomics on shared memory are compare-and-swap loops); the two signs are folded at the end.
+// With RW == 2 the only neighbours outside a lane are one label on each side: they come by
+// shuffle, the gather compares integer indices in registers, and nothing goes through shared memory.
 // RW is a tuning parameter only: any split gives the same sums.
 // ------------------------------------------------------------------------------------------------
 template <int LPT, int RW, int SCH>
@@ -56,8 +68,8 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
   float* dtile = ring + kWNS * stage_floats + kWNS * K * L / 4;             // [16][33]
   float* tbuf = dtile + 16 * 33;                             // [2][WB]
   float* ibuf = tbuf + 2 * WB;                               // [2][WB] argmin as float
-  float* acc = ibuf + 2 * WB;                                // [L] label-context gradient of the chain
-  float* qfar = acc + ((L + 3) & ~3);                        // [LP]
+  float* acc = ibuf + 2 * WB;                                // [2L] label-context gradient of the chain, cell L + c - f
+  float* qfar = acc + ((2 * L + 3) & ~3);                    // [LP]
   unsigned long long* full = reinterpret_cast<unsigned long long*>(qfar + LP);
   float* ctab = reinterpret_cast<float*>(full + kWNS + 1);   // [L] the context
   if (lane == 0) {
@@ -66,6 +78,7 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
   }
   for (int i = lane; i < L; i += 32) {
     acc[i] = 0.f;
+    acc[L + i] = 0.f;
     ctab[i] = __ldg(p.ctx + i);
   }
   for (int i = lane; i < 2 * WB; i += 32) tbuf[i] = 0.f, ibuf[i] = -1.f;
@@ -230,20 +243,40 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
           if (i < nl) de = fmaf(ctab[kd[i]], t[i], de);
         }
         dtile[sl * 33 + lane] = de;
-        if (whole) {
-#pragma unroll
-          for (int v = 0; v < LPT / 2; ++v) {
-            reinterpret_cast<float2*>(tb + c0)[v] = make_float2(t[2 * v], t[2 * v + 1]);
-            reinterpret_cast<float2*>(ib + c0)[v] = make_float2((float)f[2 * v], (float)f[2 * v + 1]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < LPT; ++i)
-            if (i < nl) tb[c0 + i] = t[i], ib[c0 + i] = (float)f[i];
-        }
-        __syncwarp();
         // ---- near: gather over the window of each label of this lane ----
-        {
+        if constexpr (RW == 2) {
+          const float tl = __shfl_up_sync(0xffffffffu, t[LPT - 1], 1), tr = __shfl_down_sync(0xffffffffu, t[0], 1);
+          int fl = __shfl_up_sync(0xffffffffu, f[LPT - 1], 1), fr = __shfl_down_sync(0xffffffffu, f[0], 1);
+          fl = lane == 0 ? -1 : fl;
+          fr = lane == 31 ? -1 : fr;
+          float sk0 = 0.f, sk1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) {
+            const int me = c0 + i;
+            const float tlv = i == 0 ? tl : t[i == 0 ? 0 : i - 1];
+            const int flv = i == 0 ? fl : f[i == 0 ? 0 : i - 1];
+            const float trv = i == LPT - 1 ? tr : t[i == LPT - 1 ? i : i + 1];
+            const int frv = i == LPT - 1 ? fr : f[i == LPT - 1 ? i : i + 1];
+            if (flv == me) qn[i] += tlv, sk1 += tlv;
+            if (f[i] == me) qn[i] += t[i], sk0 += t[i];
+            if (frv == me) qn[i] += trv, sk1 += trv;
+          }
+          ack[0] = fmaf(e, sk0, ack[0]);
+          ack[1] = fmaf(e, sk1, ack[1]);
+          __syncwarp();  // orders the table updates of successive steps
+        } else {
+          if (whole) {
+#pragma unroll
+            for (int v = 0; v < LPT / 2; ++v) {
+              reinterpret_cast<float2*>(tb + c0)[v] = make_float2(t[2 * v], t[2 * v + 1]);
+              reinterpret_cast<float2*>(ib + c0)[v] = make_float2((float)f[2 * v], (float)f[2 * v + 1]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < LPT; ++i)
+              if (i < nl) tb[c0 + i] = t[i], ib[c0 + i] = (float)f[i];
+          }
+          __syncwarp();
           float wt[NWV * 2], wi[NWV * 2];
 #pragma unroll
           for (int v = 0; v < NWV; ++v) {
@@ -260,9 +293,9 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
             const float me = (float)(c0 + i);
 #pragma unroll
             for (int o = -(RW - 1); o <= RW - 1; ++o) {
-              const float fl = eq_flag(wi[G + i + o], me);
-              const float tv = wt[G + i + o];
-              ffma2(qn[i], sk[o < 0 ? -o : o], fl, fl, tv, tv, qn[i], sk[o < 0 ? -o : o]);
+              const float pr = eq_flag(wi[G + i + o], me) * wt[G + i + o];
+              qn[i] += pr;
+              sk[o < 0 ? -o : o] += pr;
             }
           }
 #pragma unroll
@@ -284,12 +317,13 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
           const int tg = __shfl_sync(0xffffffffu, ft, __ffs(anyb) - 1);
           float part = 0.f;
           bool left = false;
+          float* cell = acc + (L + c0 - tg);  // signed offset: distinct labels, distinct cells
 #pragma unroll
           for (int i = 0; i < LPT; ++i) {
             const bool hit = pend[i] && f[i] == tg;
             if (hit) {
               part += t[i];
-              atomicAdd(acc + kd[i], e * t[i]);
+              cell[i] = fmaf(e, t[i], cell[i]);
             }
             pend[i] = pend[i] && !hit;
             left |= pend[i];
@@ -298,11 +332,12 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
 #pragma unroll
           for (int i = 0; i < LPT; ++i) qn[i] += (c0 + i == tg) ? tot : 0.f;
           if (__ballot_sync(0xffffffffu, left)) {
+            __syncwarp();
 #pragma unroll
             for (int i = 0; i < LPT; ++i) {
               if (pend[i]) {
                 atomicAdd(qfar + f[i], t[i]);
-                atomicAdd(acc + kd[i], e * t[i]);
+                atomicAdd(acc + (L + c0 + i - f[i]), e * t[i]);
               }
             }
             __syncwarp();
@@ -339,7 +374,7 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
               reinterpret_cast<float2*>(DMr + of)[v] = make_float2(-cn[2 * v], -cn[2 * v + 1]);
             }
 #pragma unroll
-            for (int i = 0; i < LPT; ++i) atomicAdd(pi + i, -q[i]);
+            for (int v = 0; v < LPT / 2; ++v) red_add_v2(pi + 2 * v, -q[2 * v], -q[2 * v + 1]);
           } else {
 #pragma unroll
             for (int i = 0; i < LPT; ++i) {
@@ -380,12 +415,12 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
 #pragma unroll
   for (int k = 0; k < RW; ++k) {
     const float v = warp_sum(ack[k]);
-    if (lane == 0 && k < L && (k > 0 || p.keep_diag)) acc[k] += v;
+    if (lane == 0 && k < L && (k > 0 || p.keep_diag)) acc[L + k] += v;
   }
   __syncwarp();
   float* part = p.dctx_part + (long long)(blockIdx.x % p.n_slots) * L;
   for (int i = lane; i < L; i += 32) {
-    const float v = acc[i];
+    const float v = i > 0 ? acc[L + i] + acc[L - i] : acc[L];  // fold the two signs of the offset
     if (v != 0.f) atomicAdd(part + i, v);
   }
 }
@@ -393,7 +428,9 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
 template <int LPT, int RW, int SCH>
 cudaError_t launch_bw(BwdParams p, int total, cudaStream_t st) {
   constexpr int LP = 32 * LPT, G = RW & ~1, NA = SCH == 1 ? 2 : 1;
-  auto bytes = [&](int k) { return ((size_t)bwd_wide_floats(p.L, LP, G, k, NA) + ((p.L + 3) & ~3) + 4) * sizeof(float); };
+  auto bytes = [&](int k) {
+    return ((size_t)bwd_wide_floats(p.L, LP, G, k, NA) + ((p.L + 3) & ~3) + 4) * sizeof(float);
+  };
   // every chain of the launch resident at once where possible: the stage depth shrinks first
   const int per_sm = (total + 147) / 148;
   const size_t budget = (size_t)225 * 1024 / (per_sm > 0 ? per_sm : 1);
