@@ -5,6 +5,7 @@
 // a block barrier per candidate and D + 1 global reductions per label and step
 // (MPLayers/TRWP/TRWP_backward.cu:26-275).
 #include <cstdlib>
+#include <type_traits>
 
 #include "mp_common.cuh"
 #include "mp_minplus.cuh"
@@ -169,237 +170,266 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
   for (int i = 0; i < LPT; ++i) q[i] = 0.f;  // scatter sums carried from the successor pixel
 #pragma unroll
   for (int k = 0; k < RW; ++k) ack[k] = 0.f;  // near offsets of the label-context gradient (this lane's share)
-  int of = pixl * L + c0;
+  // output pointers of the current pixel (label c0), moved by one pixel per step
+  float* pA = (CP ? DU : DMa + (long long)dir * p.slice) + (long long)pixl * L + c0;  // C, or the scatter field
+  float* pB = DMr + (long long)pixl * L + c0;                                         // P_dir
+  float* pI = DMa + (long long)inv * p.slice + (long long)pixl * L + c0;              // P_inv
+  const bool flip = contiguous && pstep == 1;
+
+  // One step.  FULL (warp-uniform): all 32 * LPT labels exist, no per-label bounds tests.
+  auto step = [&](auto full_c, const float* row, const uint8_t* irow, float* drow, int sl, bool staged,
+                  bool has_front) {
+    constexpr bool FULL = decltype(full_c)::value;
+    float rq[LPT], x0[LPT], x1[LPT], qn[LPT];
+#pragma unroll
+    for (int i = 0; i < LPT; ++i) rq[i] = rho * q[i], x0[i] = 0.f, x1[i] = 0.f, qn[i] = 0.f;
+    if (staged) {
+      if (FULL || whole) {
+#pragma unroll
+        for (int v = 0; v < LPT / 2; ++v) {
+          const float2 a = reinterpret_cast<const float2*>(row)[v];
+          x0[2 * v] = a.x, x0[2 * v + 1] = a.y;
+          if (CP) {
+            const float2 c = reinterpret_cast<const float2*>(row + K * L)[v];
+            x1[2 * v] = c.x, x1[2 * v + 1] = c.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          if (i < nl) {
+            x0[i] = row[i];
+            if (CP) x1[i] = row[K * L + i];
+          }
+        }
+      }
+    }
+    if (has_front) {
+      const float e = __shfl_sync(0xffffffffu, e_cur, sl);
+      const int n = __shfl_sync(0xffffffffu, n_cur, sl);
+      float xs[LPT];
+#pragma unroll
+      for (int i = 0; i < LPT; ++i) xs[i] = CP ? x0[i] + x1[i] : x0[i];
+      // normalisation sum over the stored gradient of this pixel
+      float ps = 0.f;
+#pragma unroll
+      for (int i = 0; i < LPT; ++i) ps += xs[i];
+      const float S = warp_sum(ps);
+      int f[LPT], kd[LPT];
+      float t[LPT];
+      if (FULL || whole) {
+#pragma unroll
+        for (int v = 0; v < LPT / 2; ++v) {
+          const uchar2 fi = *reinterpret_cast<const uchar2*>(irow + 2 * v);
+          f[2 * v] = fi.x, f[2 * v + 1] = fi.y;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) f[i] = i < nl ? (int)irow[i] : c0 + i;
+      }
+      float de = 0.f;
+      const int jn = n - c0;  // position of the normalisation label inside this lane, if it is here
+#pragma unroll
+      for (int i = 0; i < LPT; ++i) {
+        const float ti = xs[i] + rq[i];
+        t[i] = (i == jn) ? ti - S : ti;  // MPLayers/commonCUDA.cuh:131-145
+        const int d = c0 + i - f[i];
+        kd[i] = d < 0 ? -d : d;
+        if (FULL || i < nl) de = fmaf(ctab[kd[i]], t[i], de);
+      }
+      *drow = de;
+      // ---- near: gather over the window of each label of this lane ----
+      if constexpr (RW == 2) {
+        const float tl = __shfl_up_sync(0xffffffffu, t[LPT - 1], 1), tr = __shfl_down_sync(0xffffffffu, t[0], 1);
+        int fl = __shfl_up_sync(0xffffffffu, f[LPT - 1], 1), fr = __shfl_down_sync(0xffffffffu, f[0], 1);
+        fl = lane == 0 ? -1 : fl;
+        fr = lane == 31 ? -1 : fr;
+        float sk0 = 0.f, sk1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          const int me = c0 + i;
+          const float tlv = i == 0 ? tl : t[i == 0 ? 0 : i - 1];
+          const int flv = i == 0 ? fl : f[i == 0 ? 0 : i - 1];
+          const float trv = i == LPT - 1 ? tr : t[i == LPT - 1 ? i : i + 1];
+          const int frv = i == LPT - 1 ? fr : f[i == LPT - 1 ? i : i + 1];
+          const float a = flv == me ? tlv : 0.f, b = f[i] == me ? t[i] : 0.f, c = frv == me ? trv : 0.f;
+          const float ac = a + c;
+          qn[i] = ac + b;
+          sk0 += b;
+          sk1 += ac;
+        }
+        ack[0] = fmaf(e, sk0, ack[0]);
+        ack[1] = fmaf(e, sk1, ack[1]);
+        __syncwarp();  // orders the table updates of successive steps
+      } else {
+        float* tb = tbuf + (sl & 1) * WB + G;
+        float* ib = ibuf + (sl & 1) * WB + G;
+        if (FULL || whole) {
+#pragma unroll
+          for (int v = 0; v < LPT / 2; ++v) {
+            reinterpret_cast<float2*>(tb + c0)[v] = make_float2(t[2 * v], t[2 * v + 1]);
+            reinterpret_cast<float2*>(ib + c0)[v] = make_float2((float)f[2 * v], (float)f[2 * v + 1]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < LPT; ++i)
+            if (i < nl) tb[c0 + i] = t[i], ib[c0 + i] = (float)f[i];
+        }
+        __syncwarp();
+        float wt[NWV * 2], wi[NWV * 2];
+#pragma unroll
+        for (int v = 0; v < NWV; ++v) {
+          const float2 a = reinterpret_cast<const float2*>(tb + c0 - G)[v];
+          const float2 c = reinterpret_cast<const float2*>(ib + c0 - G)[v];
+          wt[2 * v] = a.x, wt[2 * v + 1] = a.y;
+          wi[2 * v] = c.x, wi[2 * v + 1] = c.y;
+        }
+        float sk[RW];
+#pragma unroll
+        for (int k = 0; k < RW; ++k) sk[k] = 0.f;
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          const float me = (float)(c0 + i);
+#pragma unroll
+          for (int o = -(RW - 1); o <= RW - 1; ++o) {
+            const float pr = eq_flag(wi[G + i + o], me) * wt[G + i + o];
+            qn[i] += pr;
+            sk[o < 0 ? -o : o] += pr;
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < RW; ++k) ack[k] = fmaf(e, sk[k], ack[k]);
+      }
+      // ---- far ----
+      bool pend[LPT];
+      bool any = false;
+#pragma unroll
+      for (int i = 0; i < LPT; ++i) {
+        pend[i] = (FULL || i < nl) && kd[i] >= RW;
+        any |= pend[i];
+      }
+      const unsigned anyb = __ballot_sync(0xffffffffu, any);
+      if (anyb) {
+        int ft = 0;
+#pragma unroll
+        for (int i = LPT - 1; i >= 0; --i) ft = pend[i] ? f[i] : ft;
+        const int tg = __shfl_sync(0xffffffffu, ft, __ffs(anyb) - 1);
+        float part = 0.f;
+        bool left = false;
+        // signed offset: distinct labels, distinct cells (lanes without a far label keep away: the
+        // cells of labels that do not exist may lie outside the table)
+        float* cell = acc + (any ? L + c0 - tg : L);
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) {
+          const bool hit = pend[i] && f[i] == tg;
+          const float ht = hit ? t[i] : 0.f;
+          part += ht;
+          const float cv = fmaf(e, ht, cell[i]);
+          if (hit) cell[i] = cv;
+          pend[i] = pend[i] && !hit;
+          left |= pend[i];
+        }
+        const float tot = warp_sum(part);
+        const int jt = tg - c0;
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) qn[i] += (i == jt) ? tot : 0.f;
+        if (__ballot_sync(0xffffffffu, left)) {
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) {
+            if (pend[i]) {
+              atomicAdd(qfar + f[i], t[i]);
+              atomicAdd(acc + (L + c0 + i - f[i]), e * t[i]);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) qn[i] += qfar[c0 + i];
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) qfar[c0 + i] = 0.f;
+        }
+      }
+    }
+    if (FULL || nl > 0) {
+      if (!CP) {
+        // scatter field of this direction at this pixel
+        if (FULL || whole) {
+#pragma unroll
+          for (int v = 0; v < LPT / 2; ++v) reinterpret_cast<float2*>(pA)[v] = make_float2(q[2 * v], q[2 * v + 1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < LPT; ++i)
+            if (i < nl) pA[i] = q[i];
+        }
+      } else {
+        // dU and every dM_k (k != dir, inv) receive rho*q; dM_dir = C + P_dir = 0 after its sweep
+        float cn[LPT];
+#pragma unroll
+        for (int i = 0; i < LPT; ++i) cn[i] = x0[i] + rq[i];
+        if (FULL || whole) {
+#pragma unroll
+          for (int v = 0; v < LPT / 2; ++v) {
+            reinterpret_cast<float2*>(pA)[v] = make_float2(cn[2 * v], cn[2 * v + 1]);
+            reinterpret_cast<float2*>(pB)[v] = make_float2(-cn[2 * v], -cn[2 * v + 1]);
+          }
+#pragma unroll
+          for (int v = 0; v < LPT / 2; ++v) red_add_v2(pI + 2 * v, -q[2 * v], -q[2 * v + 1]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < LPT; ++i) {
+            if (i < nl) {
+              pA[i] = cn[i];
+              pB[i] = -cn[i];
+              atomicAdd(pI + i, -q[i]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < LPT; ++i) q[i] = qn[i];
+    pA -= ostep;
+    pB -= ostep;
+    pI -= ostep;
+  };
+
+  const bool all_whole = L == LP;  // warp-uniform
   for (int b = 0; b < nblocks; ++b) {
     load_blk(b + 1, e_nxt, n_nxt);
     const int rows = stage_rows(b);
     const int slot = b % kWNS;
-    const float* T = ring + slot * stage_floats;
-    const uint8_t* IT = itile + (slot * K) * L + c0;
     cp_async_wait<kWNS - 1>();
     if (rows > 0 && !mbar_wait(&full[slot], (b / kWNS) & 1)) {
       if (lane == 0) atomicExch(p.status, 161);
       return;
     }
     __syncwarp();
-    const bool flip = contiguous && pstep == 1;
     const int send = len - K * b < K ? len - K * b : K;
+    const float* row = ring + slot * stage_floats + (flip ? rows - 1 : 0) * L + c0;
+    const int rstep = flip ? -L : L;
+    const uint8_t* irow = itile + (slot * K) * L + c0;
+    float* drow = dtile + lane;
     for (int sl = 0; sl < send; ++sl) {
       const int s = K * b + sl;
-      float rq[LPT], x0[LPT], x1[LPT], qn[LPT];
-#pragma unroll
-      for (int i = 0; i < LPT; ++i) rq[i] = rho * q[i], x0[i] = 0.f, x1[i] = 0.f, qn[i] = 0.f;
-      if (sl < rows) {
-        const float* row = T + (flip ? rows - 1 - sl : sl) * L + c0;
-        if (whole) {
-#pragma unroll
-          for (int v = 0; v < LPT / 2; ++v) {
-            const float2 a = reinterpret_cast<const float2*>(row)[v];
-            x0[2 * v] = a.x, x0[2 * v + 1] = a.y;
-            if (CP) {
-              const float2 c = reinterpret_cast<const float2*>(row + K * L)[v];
-              x1[2 * v] = c.x, x1[2 * v + 1] = c.y;
-            }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) {
-            if (i < nl) {
-              x0[i] = row[i];
-              if (CP) x1[i] = row[K * L + i];
-            }
-          }
-        }
+      if (all_whole) {
+        step(std::true_type{}, row, irow, drow, sl, sl < rows, s < nsteps);
+      } else {
+        step(std::false_type{}, row, irow, drow, sl, sl < rows, s < nsteps);
       }
-      if (s < nsteps) {
-        const float e = __shfl_sync(0xffffffffu, e_cur, sl);
-        const int n = __shfl_sync(0xffffffffu, n_cur, sl);
-        // normalisation sum over the stored gradient of this pixel
-        float ps = 0.f;
-#pragma unroll
-        for (int i = 0; i < LPT; ++i) ps += CP ? x0[i] + x1[i] : x0[i];
-        const float S = warp_sum(ps);
-        int f[LPT], kd[LPT];
-        float t[LPT];
-        if (whole) {
-#pragma unroll
-          for (int v = 0; v < LPT / 2; ++v) {
-            const uchar2 fi = *reinterpret_cast<const uchar2*>(IT + sl * L + 2 * v);
-            f[2 * v] = fi.x, f[2 * v + 1] = fi.y;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) f[i] = i < nl ? (int)IT[sl * L + i] : c0 + i;
-        }
-        float de = 0.f;
-        float* tb = tbuf + (s & 1) * WB + G;
-        float* ib = ibuf + (s & 1) * WB + G;
-#pragma unroll
-        for (int i = 0; i < LPT; ++i) {
-          const float ti = (CP ? x0[i] + x1[i] : x0[i]) + rq[i];
-          t[i] = (c0 + i == n) ? ti - S : ti;  // MPLayers/commonCUDA.cuh:131-145
-          const int d = c0 + i - f[i];
-          kd[i] = d < 0 ? -d : d;
-          if (i < nl) de = fmaf(ctab[kd[i]], t[i], de);
-        }
-        dtile[sl * 33 + lane] = de;
-        // ---- near: gather over the window of each label of this lane ----
-        if constexpr (RW == 2) {
-          const float tl = __shfl_up_sync(0xffffffffu, t[LPT - 1], 1), tr = __shfl_down_sync(0xffffffffu, t[0], 1);
-          int fl = __shfl_up_sync(0xffffffffu, f[LPT - 1], 1), fr = __shfl_down_sync(0xffffffffu, f[0], 1);
-          fl = lane == 0 ? -1 : fl;
-          fr = lane == 31 ? -1 : fr;
-          float sk0 = 0.f, sk1 = 0.f;
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) {
-            const int me = c0 + i;
-            const float tlv = i == 0 ? tl : t[i == 0 ? 0 : i - 1];
-            const int flv = i == 0 ? fl : f[i == 0 ? 0 : i - 1];
-            const float trv = i == LPT - 1 ? tr : t[i == LPT - 1 ? i : i + 1];
-            const int frv = i == LPT - 1 ? fr : f[i == LPT - 1 ? i : i + 1];
-            if (flv == me) qn[i] += tlv, sk1 += tlv;
-            if (f[i] == me) qn[i] += t[i], sk0 += t[i];
-            if (frv == me) qn[i] += trv, sk1 += trv;
-          }
-          ack[0] = fmaf(e, sk0, ack[0]);
-          ack[1] = fmaf(e, sk1, ack[1]);
-          __syncwarp();  // orders the table updates of successive steps
-        } else {
-          if (whole) {
-#pragma unroll
-            for (int v = 0; v < LPT / 2; ++v) {
-              reinterpret_cast<float2*>(tb + c0)[v] = make_float2(t[2 * v], t[2 * v + 1]);
-              reinterpret_cast<float2*>(ib + c0)[v] = make_float2((float)f[2 * v], (float)f[2 * v + 1]);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < LPT; ++i)
-              if (i < nl) tb[c0 + i] = t[i], ib[c0 + i] = (float)f[i];
-          }
-          __syncwarp();
-          float wt[NWV * 2], wi[NWV * 2];
-#pragma unroll
-          for (int v = 0; v < NWV; ++v) {
-            const float2 a = reinterpret_cast<const float2*>(tb + c0 - G)[v];
-            const float2 c = reinterpret_cast<const float2*>(ib + c0 - G)[v];
-            wt[2 * v] = a.x, wt[2 * v + 1] = a.y;
-            wi[2 * v] = c.x, wi[2 * v + 1] = c.y;
-          }
-          float sk[RW];
-#pragma unroll
-          for (int k = 0; k < RW; ++k) sk[k] = 0.f;
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) {
-            const float me = (float)(c0 + i);
-#pragma unroll
-            for (int o = -(RW - 1); o <= RW - 1; ++o) {
-              const float pr = eq_flag(wi[G + i + o], me) * wt[G + i + o];
-              qn[i] += pr;
-              sk[o < 0 ? -o : o] += pr;
-            }
-          }
-#pragma unroll
-          for (int k = 0; k < RW; ++k) ack[k] = fmaf(e, sk[k], ack[k]);
-        }
-        // ---- far ----
-        bool pend[LPT];
-        bool any = false;
-#pragma unroll
-        for (int i = 0; i < LPT; ++i) {
-          pend[i] = i < nl && kd[i] >= RW;
-          any |= pend[i];
-        }
-        const unsigned anyb = __ballot_sync(0xffffffffu, any);
-        if (anyb) {
-          int ft = 0;
-#pragma unroll
-          for (int i = LPT - 1; i >= 0; --i) ft = pend[i] ? f[i] : ft;
-          const int tg = __shfl_sync(0xffffffffu, ft, __ffs(anyb) - 1);
-          float part = 0.f;
-          bool left = false;
-          float* cell = acc + (L + c0 - tg);  // signed offset: distinct labels, distinct cells
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) {
-            const bool hit = pend[i] && f[i] == tg;
-            if (hit) {
-              part += t[i];
-              cell[i] = fmaf(e, t[i], cell[i]);
-            }
-            pend[i] = pend[i] && !hit;
-            left |= pend[i];
-          }
-          const float tot = warp_sum(part);
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) qn[i] += (c0 + i == tg) ? tot : 0.f;
-          if (__ballot_sync(0xffffffffu, left)) {
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < LPT; ++i) {
-              if (pend[i]) {
-                atomicAdd(qfar + f[i], t[i]);
-                atomicAdd(acc + (L + c0 + i - f[i]), e * t[i]);
-              }
-            }
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < LPT; ++i) qn[i] += qfar[c0 + i];
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < LPT; ++i) qfar[c0 + i] = 0.f;
-          }
-        }
-      }
-      if (nl > 0) {
-        if (!CP) {
-          // scatter field of this direction at this pixel
-          float* out = DMa + (long long)dir * p.slice + of;
-          if (whole) {
-#pragma unroll
-            for (int v = 0; v < LPT / 2; ++v) reinterpret_cast<float2*>(out)[v] = make_float2(q[2 * v], q[2 * v + 1]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < LPT; ++i)
-              if (i < nl) out[i] = q[i];
-          }
-        } else {
-          // dU and every dM_k (k != dir, inv) receive rho*q; dM_dir = C + P_dir = 0 after its sweep
-          float cn[LPT];
-#pragma unroll
-          for (int i = 0; i < LPT; ++i) cn[i] = x0[i] + rq[i];
-          float* pi = DMa + (long long)inv * p.slice + of;
-          if (whole) {
-#pragma unroll
-            for (int v = 0; v < LPT / 2; ++v) {
-              reinterpret_cast<float2*>(DU + of)[v] = make_float2(cn[2 * v], cn[2 * v + 1]);
-              reinterpret_cast<float2*>(DMr + of)[v] = make_float2(-cn[2 * v], -cn[2 * v + 1]);
-            }
-#pragma unroll
-            for (int v = 0; v < LPT / 2; ++v) red_add_v2(pi + 2 * v, -q[2 * v], -q[2 * v + 1]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < LPT; ++i) {
-              if (i < nl) {
-                DU[of + i] = cn[i];
-                DMr[of + i] = -cn[i];
-                atomicAdd(pi + i, -q[i]);
-              }
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < LPT; ++i) q[i] = qn[i];
-      of -= ostep;
+      row += rstep;
+      irow += L;
+      drow += 33;
     }
     // edge-weight gradients of this block: lane j sums row j of the product tile
     __syncwarp();
     if (DE && lane < K) {
       const int s = K * b + lane;
       if (s < nsteps) {
-        const float* row = dtile + lane * 33;
+        const float* dr = dtile + lane * 33;
         float da = 0.f, db = 0.f;
 #pragma unroll 8
-        for (int c = 0; c < 32; c += 2) da += row[c], db += row[c + 1];
+        for (int c = 0; c < 32; c += 2) da += dr[c], db += dr[c + 1];
         atomicAdd(DE + (pixl - s * pstep), da + db);
       }
     }
