@@ -53,7 +53,7 @@ __device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
 // RW is a tuning parameter only: any split gives the same sums.
 // ------------------------------------------------------------------------------------------------
 template <int LPT, int RW, int SCH>
-__global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(32, 8) bwd_wide_kernel(const __grid_constant__ BwdParams p) {
   constexpr bool CP = SCH == 1;
   constexpr int NA = CP ? 2 : 1;  // staged arrays: (C, P_dir) or the gradient slice of the direction
   constexpr int LP = 32 * LPT;
@@ -176,10 +176,12 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
   float* pI = DMa + (long long)inv * p.slice + (long long)pixl * L + c0;              // P_inv
   const bool flip = contiguous && pstep == 1;
 
-  // One step.  FULL (warp-uniform): all 32 * LPT labels exist, no per-label bounds tests.
-  auto step = [&](auto full_c, const float* row, const uint8_t* irow, float* drow, int sl, bool staged,
-                  bool has_front) {
+  // One step.  FULL (warp-uniform): all 32 * LPT labels exist, no per-label bounds tests.  FRONT: the
+  // pixel has a predecessor on the chain (all but the chain's first pixel, which only stores).
+  auto step = [&](auto full_c, auto front_c, const float* row, const uint8_t* irow, float* drow, int sl) {
     constexpr bool FULL = decltype(full_c)::value;
+    constexpr bool has_front = decltype(front_c)::value;
+    constexpr bool staged = has_front || CP;  // the scatter-field scheme stages no row for the first pixel
     float rq[LPT], x0[LPT], x1[LPT], qn[LPT];
 #pragma unroll
     for (int i = 0; i < LPT; ++i) rq[i] = rho * q[i], x0[i] = 0.f, x1[i] = 0.f, qn[i] = 0.f;
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
         }
       }
     }
-    if (has_front) {
+    if constexpr (has_front) {
       const float e = __shfl_sync(0xffffffffu, e_cur, sl);
       const int n = __shfl_sync(0xffffffffu, n_cur, sl);
       float xs[LPT];
@@ -412,10 +414,14 @@ __global__ void __launch_bounds__(32) bwd_wide_kernel(const __grid_constant__ Bw
     float* drow = dtile + lane;
     for (int sl = 0; sl < send; ++sl) {
       const int s = K * b + sl;
-      if (all_whole) {
-        step(std::true_type{}, row, irow, drow, sl, sl < rows, s < nsteps);
+      if (s < nsteps) {
+        if (all_whole) {
+          step(std::true_type{}, std::true_type{}, row, irow, drow, sl);
+        } else {
+          step(std::false_type{}, std::true_type{}, row, irow, drow, sl);
+        }
       } else {
-        step(std::false_type{}, row, irow, drow, sl, sl < rows, s < nsteps);
+        step(std::false_type{}, std::false_type{}, row, irow, drow, sl);
       }
       row += rstep;
       irow += L;
