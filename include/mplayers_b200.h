@@ -75,6 +75,11 @@ typedef struct mpl_problem {
                                part holds both messages of every line it owns); chain_parts <= 1: all chains.
                                Lets more ranks than direction pairs share one image: pixels a call
                                does not visit are left untouched in every output. */
+  int32_t cost_labels_first; /* mpl_trwp_forward / mpl_isgmr_forward and their backward calls: 1 = cost_final and
+                               dcost_final are [B, cv, L, H, W] (the layout pytorch/MP_module.py:232 hands back
+                               after its permute) instead of [B, cv, H, W, L]; the final aggregation writes and
+                               the backward prologue reads that layout directly, so the caller needs no
+                               separate layout pass.  Every other tensor keeps the labels last. */
 } mpl_problem;
 
 /* Analyses a rank-1 context (and the edge weights, may be NULL) for mpl_problem::context_window:

@@ -14,7 +14,8 @@ from .TRWP import _problem
 
 
 def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, cost_final,
-            msg_min_index, msg_norm_index, unary_update, msg_update, label_all, context_window=0):
+            msg_min_index, msg_norm_index, unary_update, msg_update, label_all, context_window=0,
+            cost_labels_first=False):
     dev = unary.device
     for t, n in ((unary, "unary"), (context, "context"), (edge_weights, "edge_weights"), (msg, "msg"),
                  (cost_final, "cost_final"), (msg_update, "msg_update")):
@@ -25,7 +26,7 @@ def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weig
     if msg.dim() != 6 or tuple(unary.shape) != tuple(msg.shape[1:]) or msg.shape != msg_update.shape:
         raise RuntimeError("msg and msg_update must be [D,B,cv,H,W,L] matching unary [B,cv,H,W,L]")
     prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir, enable_sgm,
-                    context_window=context_window)
+                    context_window=context_window, cost_labels_first=cost_labels_first)
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_forward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)
@@ -38,7 +39,8 @@ def forward(enable_sgm, rho, n_iter, enable_min_a_dir, unary, context, edge_weig
 
 
 def backward(enable_sgm, rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index,
-             dunary, dcontext, dedge_weights, dmsg, dunary_update, dmsg_update, keep_diag=False, context_window=0):
+             dunary, dcontext, dedge_weights, dmsg, dunary_update, dmsg_update, keep_diag=False, context_window=0,
+             cost_labels_first=False):
     dev = dcost_final.device
     for t, n in ((context, "context"), (edge_weights, "edge_weights"), (dcost_final, "dcost_final"),
                  (dunary, "dunary"), (dcontext, "dcontext"), (dedge_weights, "dedge_weights"),
@@ -49,7 +51,8 @@ def backward(enable_sgm, rho, context, edge_weights, dcost_final, msg_min_index,
     if msg_min_index.dim() != 7:
         raise RuntimeError("msg_min_index must be [I,D,B,cv,H,W,L]")
     prob = _problem(msg_min_index.size(0), tuple(msg_min_index.shape[1:]), context, rho,
-                    enable_sgm=enable_sgm, keep_diag_=keep_diag, context_window=max(int(context_window), 0))
+                    enable_sgm=enable_sgm, keep_diag_=keep_diag, context_window=max(int(context_window), 0),
+                    cost_labels_first=cost_labels_first)
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_backward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)

@@ -74,14 +74,16 @@ class TRWPFunction(torch.autograd.Function):
         unary = unary.contiguous()
         label_context = label_context.contiguous()
         message = unary.new_zeros(n_dir, batch, cv, h, w, n_disp)
-        cost_final = torch.empty_like(unary)
+        lf = bool(getattr(args, "cost_labels_first", False))  # cost_final as [B,cv,L,H,W]
+        cost_final = unary.new_empty(batch, cv, n_disp, h, w) if lf else torch.empty_like(unary)
         message_index, cost_index, label_all = _alloc_indices(unary, n_iter, n_dir, is_training,
                                                               args.enable_saving_label)
         enable_edge_weights = edge_weights is not None
         ew = edge_weights.contiguous() if enable_edge_weights else _empty_f32(unary.device)
         _TRWP.forward(rho, int(n_iter), int(args.enable_min_a_dir), unary, label_context, ew, message,
                       cost_final, message_index, cost_index, _empty_f32(unary.device), label_all,
-                      context_window=int(getattr(args, "context_window", 0) or 0))
+                      context_window=int(getattr(args, "context_window", 0) or 0), cost_labels_first=lf)
+        ctx.cost_labels_first = lf
         ctx.intermediate_results = rho, message_index, cost_index, label_context, ew, enable_edge_weights
         ctx.context_window = int(getattr(args, "context_window", 0) or 0)
         ctx.norm_index_override = _norm_index_override(args, cost_index, n_disp)
@@ -99,13 +101,14 @@ class TRWPFunction(torch.autograd.Function):
             cost_index = ctx.norm_index_override
         dcost_final = dcost_final.contiguous()
         n_iter, n_dir, batch, cv, h, w, n_disp = message_index.size()
-        dunary = torch.empty_like(dcost_final)
+        dunary = dcost_final.new_empty(batch, cv, h, w, n_disp)
         dmessage = dcost_final.new_empty(n_dir, batch, cv, h, w, n_disp)
         dlabel_context = torch.zeros_like(label_context)
         dedge_weights = torch.zeros_like(ew) if enable_edge_weights else _empty_f32(dcost_final.device)
         _TRWP.backward(rho, label_context, ew, dcost_final, message_index, cost_index, dunary,
                        dlabel_context, dedge_weights, dmessage, _empty_f32(dcost_final.device),
-                       keep_diag=ctx._forward_cls.keep_diag, context_window=ctx.context_window)
+                       keep_diag=ctx._forward_cls.keep_diag, context_window=ctx.context_window,
+                       cost_labels_first=ctx.cost_labels_first)
         return dunary, dlabel_context, (dedge_weights if enable_edge_weights else None), None
 
 
@@ -120,7 +123,8 @@ class ISGMRFunction(torch.autograd.Function):
         label_context = label_context.contiguous()
         message = unary.new_zeros(n_dir, batch, cv, h, w, n_disp)
         message_tmp = unary.new_zeros(n_dir, batch, cv, h, w, n_disp)
-        cost_final = torch.empty_like(unary)
+        lf = bool(getattr(args, "cost_labels_first", False))  # cost_final as [B,cv,L,H,W]
+        cost_final = unary.new_empty(batch, cv, n_disp, h, w) if lf else torch.empty_like(unary)
         message_index, cost_index, label_all = _alloc_indices(unary, n_iter, n_dir, is_training,
                                                               args.enable_saving_label)
         enable_edge_weights = edge_weights is not None
@@ -128,7 +132,8 @@ class ISGMRFunction(torch.autograd.Function):
         _ISGMR.forward(int(args.enable_sgm), rho, int(n_iter), int(args.enable_min_a_dir), unary,
                        label_context, ew, message, cost_final, message_index, cost_index,
                        _empty_f32(unary.device), message_tmp, label_all,
-                       context_window=int(getattr(args, "context_window", 0) or 0))
+                       context_window=int(getattr(args, "context_window", 0) or 0), cost_labels_first=lf)
+        ctx.cost_labels_first = lf
         ctx.intermediate_results = args.enable_sgm, rho, message_index, cost_index, label_context, ew, \
             enable_edge_weights
         ctx.context_window = int(getattr(args, "context_window", 0) or 0)
@@ -145,14 +150,15 @@ class ISGMRFunction(torch.autograd.Function):
                                "(args.training was False)")
         dcost_final = dcost_final.contiguous()
         n_iter, n_dir, batch, cv, h, w, n_disp = message_index.size()
-        dunary = torch.empty_like(dcost_final)
+        dunary = dcost_final.new_empty(batch, cv, h, w, n_disp)
         dmessage = dcost_final.new_empty(n_dir, batch, cv, h, w, n_disp)
         dmessage_tmp = dcost_final.new_empty(n_dir, batch, cv, h, w, n_disp)
         dlabel_context = torch.zeros_like(label_context)
         dedge_weights = torch.zeros_like(ew) if enable_edge_weights else _empty_f32(dcost_final.device)
         _ISGMR.backward(int(enable_sgm), rho, label_context, ew, dcost_final, message_index, cost_index,
                         dunary, dlabel_context, dedge_weights, dmessage,
-                        _empty_f32(dcost_final.device), dmessage_tmp, context_window=ctx.context_window)
+                        _empty_f32(dcost_final.device), dmessage_tmp, context_window=ctx.context_window,
+                        cost_labels_first=ctx.cost_labels_first)
         return dunary, dlabel_context, (dedge_weights if enable_edge_weights else None), None
 
 
@@ -251,6 +257,7 @@ class MPModule(torch.nn.Module):
         label_context).  Used by glue.mp_on_scores."""
         label_context = self._transformed_label_context()
         self.args.training = self.training
+        self.args.cost_labels_first = False
         self.args.context_window = self._context_window(label_context, edge_weights)
         if self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'}:
             cost_final, _ = ISGMRFunction.apply(unary, label_context, edge_weights, self.args)
@@ -270,10 +277,15 @@ class MPModule(torch.nn.Module):
             assert unary.size()[-3:-1] == edge_weights.size()[-2:]
         self.args.training = self.training
         self.args.context_window = self._context_window(label_context, edge_weights)
+        # The layer writes cost_final (and reads its gradient) with the labels first, the layout the
+        # reference reaches with a permute here (pytorch/MP_module.py:232): no layout pass on the way
+        # out.  (The direction-sharded mode keeps its own path.)
+        self.args.cost_labels_first = self.direction_comm is None
         if self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'} and self.direction_comm is not None:
             from .direction_sharding import isgmr_direction_sharded
             cost_final = isgmr_direction_sharded(unary, label_context, edge_weights, self.args,
                                                  comm=self.direction_comm)
+            cost_final = _glue.labels_first(cost_final)
             cost_all = _empty_u8(unary.device)
         elif self.args.mpnet_mrf_mode in {'ISGMR', 'SGM'}:
             cost_final, cost_all = ISGMRFunction.apply(unary, label_context, edge_weights, self.args)
@@ -281,6 +293,6 @@ class MPModule(torch.nn.Module):
             cost_final, cost_all = TRWPFunction.apply(unary, label_context, edge_weights, self.args)
         else:
             assert False
-        cost_final = _glue.labels_first(cost_final)
+        self.args.cost_labels_first = False
         label_context = label_context.unsqueeze(0)
         return cost_final, label_context, cost_all, None, None

@@ -123,13 +123,17 @@ class MPModule(torch.nn.Module):
         if edge_weights is not None:
             assert unary.size()[-3:-1] == edge_weights.size()[-2:]
         self.args.training = self.training
+        self.args.cost_labels_first = False
         if getattr(self.args, 'mpnet_enable_soft', False):
             cost_final, cost_all, message_vector, message_index = \
                 TRWPSoftFunction.apply(unary, label_context, edge_weights, self.args)
             cost_final = _glue.labels_first(cost_final)
             return cost_final, label_context.unsqueeze(0), cost_all, message_vector, message_index
+        # the layer writes cost_final (and reads its gradient) with the labels first: no layout pass
+        # on the way out (pytorch/MP_module_hard_soft.py permutes here)
+        self.args.cost_labels_first = True
         cost_final, cost_all = TRWPFunction.apply(unary, label_context, edge_weights, self.args)
-        cost_final = _glue.labels_first(cost_final)
+        self.args.cost_labels_first = False
         label_context = label_context.unsqueeze(0)
         empty = torch.empty(0, dtype=torch.float32, device=unary.device)
         return cost_final, label_context, cost_all, empty, empty

@@ -17,18 +17,19 @@ keep_diag = False  # TRWP_hard_soft accumulates dcontext on the diagonal, the TR
 
 
 def _problem(n_iter, msg_shape, context, rho, enable_min_a_dir=0, enable_sgm=0, keep_diag_=0,
-             context_window=0):
+             context_window=0, cost_labels_first=False):
     n_dir, batch, n_cv, h, w, n_disp = msg_shape
     return _lib.Problem(int(n_iter), n_dir, batch, n_cv, h, w, n_disp,
                         _lib.context_rank(context, n_disp), int(enable_min_a_dir), int(enable_sgm),
-                        int(keep_diag_), float(rho), int(context_window))
+                        int(keep_diag_), float(rho), int(context_window), 0, 0, int(bool(cost_labels_first)))
 
 
 def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, cost_final,
-            msg_min_index, msg_norm_index, unary_update, label_all, context_window=0):
+            msg_min_index, msg_norm_index, unary_update, label_all, context_window=0, cost_labels_first=False):
     """`context_window` (keyword, not in the reference's signature): see mpl_problem::context_window;
     0 lets the library find out by itself, which makes an inference call with a rank-1 context and
-    more than 32 labels wait for the stream once."""
+    more than 32 labels wait for the stream once.  `cost_labels_first` (keyword): cost_final is
+    [B,cv,L,H,W] instead of [B,cv,H,W,L] (mpl_problem::cost_labels_first)."""
     dev = unary.device
     for t, n in ((unary, "unary"), (context, "context"), (edge_weights, "edge_weights"), (msg, "msg"),
                  (cost_final, "cost_final")):
@@ -38,7 +39,8 @@ def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, co
         _lib.require(t, n, torch.uint8, dev)
     if msg.dim() != 6 or tuple(unary.shape) != tuple(msg.shape[1:]):
         raise RuntimeError("msg must be [D,B,cv,H,W,L] matching unary [B,cv,H,W,L]")
-    prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir, context_window=context_window)
+    prob = _problem(n_iter, tuple(msg.shape), context, rho, enable_min_a_dir, context_window=context_window,
+                    cost_labels_first=cost_labels_first)
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_forward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)
@@ -50,7 +52,8 @@ def forward(rho, n_iter, enable_min_a_dir, unary, context, edge_weights, msg, co
 
 
 def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_index, dunary,
-             dcontext, dedge_weights, dmsg, dunary_update, keep_diag=None, context_window=0):
+             dcontext, dedge_weights, dmsg, dunary_update, keep_diag=None, context_window=0,
+             cost_labels_first=False):
     """`context_window` (keyword, not in the reference's signature): in the backward pass only a hint
     for how the scatter of a rank-1 context with more than 64 labels is split; any value gives the
     same sums."""
@@ -65,7 +68,8 @@ def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_in
         raise RuntimeError("msg_min_index must be [I,D,B,cv,H,W,L]")
     kd = globals()["keep_diag"] if keep_diag is None else keep_diag
     prob = _problem(msg_min_index.size(0), tuple(msg_min_index.shape[1:]), context, rho,
-                    keep_diag_=kd, context_window=max(int(context_window), 0))
+                    keep_diag_=kd, context_window=max(int(context_window), 0),
+                    cost_labels_first=cost_labels_first)
     with torch.cuda.device(dev):
         nbytes = _lib.lib().mpl_backward_workspace_bytes(ctypes.byref(prob))
         ws = _lib.workspace(nbytes, dev)

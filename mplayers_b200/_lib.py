@@ -23,7 +23,8 @@ class Problem(ctypes.Structure):
                  "enable_min_a_dir", "enable_sgm", "keep_diag")] + [("rho", ctypes.c_float),
                                                                    ("context_window", ctypes.c_int32),
                                                                    ("chain_part", ctypes.c_int32),
-                                                                   ("chain_parts", ctypes.c_int32)]
+                                                                   ("chain_parts", ctypes.c_int32),
+                                                                   ("cost_labels_first", ctypes.c_int32)]
 
 
 _lib = None

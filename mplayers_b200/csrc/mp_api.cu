@@ -313,8 +313,13 @@ int forward_common(bool isgmr, const mpl_problem* p, const float* unary, const f
   const float* fin = isgmr ? rd : msg;
   if (isgmr && p->n_iter > 0 && fin != msg)
     return fail(MPL_ERR_CUDA, "internal: ISGMR buffer parity");
-  MPL_CUDA(mpl::launch_aggregate(unary, msg, cost_final, nullptr, d.npix, L, D, d.slice, factor,
-                                 p->enable_min_a_dir, st));
+  if (p->cost_labels_first) {
+    MPL_CUDA(mpl::launch_aggregate_lhw(unary, msg, cost_final, (int)d.nimg, L, (long long)p->height * p->width, D,
+                                       d.slice, factor, p->enable_min_a_dir, st));
+  } else {
+    MPL_CUDA(mpl::launch_aggregate(unary, msg, cost_final, nullptr, d.npix, L, D, d.slice, factor,
+                                   p->enable_min_a_dir, st));
+  }
   return MPL_OK;
 }
 
@@ -380,7 +385,12 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   const int cp = isgmr ? 2 : ((L <= 32 || pair_cp || wide_cp) ? 1 : 0);
   float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced
   float* Y = isgmr ? dmsg : dmsg;         // gradients of the messages the sweeps read
-  MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp == 1, st));
+  if (p->cost_labels_first) {
+    MPL_CUDA(mpl::launch_backward_init_lhw(dcost_final, dunary, X, (int)d.nimg, L, (long long)p->height * p->width,
+                                           D, factor, cp == 1, st));
+  } else {
+    MPL_CUDA(mpl::launch_backward_init(dcost_final, dunary, X, d.slice, D, factor, cp == 1, st));
+  }
   int* status = ws_status(workspace);
   MPL_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
 

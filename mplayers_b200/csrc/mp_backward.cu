@@ -1189,6 +1189,27 @@ __global__ void backward_init_kernel(const float* __restrict__ g, float* __restr
   }
 }
 
+// The same prologue reading g with the labels first ([nimg, L, H*W] planes): one block per 32 pixels
+// of an image, through a shared-memory tile.
+__global__ void __launch_bounds__(256)
+backward_init_lhw_kernel(const float* __restrict__ g, float* __restrict__ dunary, float* __restrict__ dm, int L,
+                         long long HW, long long n, int D, float factor, int cp) {
+  extern __shared__ float tile[];  // [L][33]
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long b = blockIdx.y, p0 = blockIdx.x * 32ll;
+  const int np = HW - p0 < 32 ? (int)(HW - p0) : 32;
+  const float* src = g + b * L * HW + p0;
+  for (int l = ty; l < L; l += 8) tile[l * 33 + tx] = tx < np ? src[(long long)l * HW + tx] : 0.f;
+  __syncthreads();
+  const long long base = (b * HW + p0) * L;
+  for (int i = threadIdx.x; i < np * L; i += 256) {
+    const int px = i / L, l = i - px * L;
+    const float v = tile[l * 33 + px];
+    dunary[base + i] = cp ? v : factor * v;
+    for (int k = 0; k < D; ++k) dm[k * n + base + i] = cp ? 0.f : v;
+  }
+}
+
 // ISGMR, cp_scheme 2: after the D independent sweeps of an iteration have stored their scatter
 // fields q_d, the gradients of the messages that iteration read are
 //   dM_k = rho * Q - rho * q_k - q_inv(k),   Q = sum_d q_d,   and   dU += rho * Q
@@ -1382,6 +1403,17 @@ cudaError_t launch_backward_init(const float* dcost, float* dunary, float* dm, l
   if (blocks > 148 * 32) blocks = 148 * 32;
   ProfScope prof(kProfElementwise, st);
   backward_init_kernel<<<(int)blocks, 256, 0, st>>>(dcost, dunary, dm, n, D, factor, cp_scheme);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_backward_init_lhw(const float* dcost, float* dunary, float* dm, int nimg, int L, long long HW,
+                                     int D, float factor, int cp_scheme, cudaStream_t st) {
+  const dim3 grid((unsigned)((HW + 31) / 32), (unsigned)nimg);
+  const size_t smem = (size_t)L * 33 * sizeof(float);
+  ProfScope prof(kProfElementwise, st);
+  backward_init_lhw_kernel<<<grid, 256, smem, st>>>(dcost, dunary, dm, L, HW, (long long)nimg * HW * L, D, factor,
+                                                    cp_scheme);
   count_launch();
   return cudaGetLastError();
 }

@@ -1031,6 +1031,38 @@ aggregate_vec4_kernel(const float4* __restrict__ unary, const float4* __restrict
   }
 }
 
+// The same sums written with the labels FIRST ([nimg, L, H*W] planes, the layout the reference's
+// module hands back after its permute, pytorch/MP_module.py:232): one block per 32 pixels of an
+// image, through a shared-memory tile so that both sides are coalesced.
+__global__ void __launch_bounds__(256)
+aggregate_lhw_kernel(const float* __restrict__ unary, const float* __restrict__ msg, float* __restrict__ cost,
+                     int L, long long HW, int D, long long slice, float factor, int min_a_dir) {
+  extern __shared__ float tile[];  // [L][33]
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long b = blockIdx.y, p0 = blockIdx.x * 32ll;
+  const int np = HW - p0 < 32 ? (int)(HW - p0) : 32;
+  const long long base = (b * HW + p0) * L;
+  for (int i = threadIdx.x; i < np * L; i += 256) {
+    float v = unary[base + i] * factor;
+    if (min_a_dir) {
+      float mm = msg[base + i];
+      for (int k = 1; k < D; ++k) {
+        const float x = msg[k * slice + base + i];
+        if (x < mm) mm = x;
+      }
+      v += mm;
+    } else {
+      for (int k = 0; k < D; ++k) v += msg[k * slice + base + i];
+    }
+    const int px = i / L, l = i - px * L;
+    tile[l * 33 + px] = v;
+  }
+  __syncthreads();
+  float* dst = cost + b * L * HW + p0;
+  for (int l = ty; l < L; l += 8)
+    if (tx < np) dst[(long long)l * HW + tx] = tile[l * 33 + tx];
+}
+
 __global__ void label_kernel(const float* __restrict__ cost, uint8_t* __restrict__ label,
                              long long npix, int L) {
   const long long px = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -1640,6 +1672,17 @@ cudaError_t launch_aggregate(const float* unary, const float* msg, float* cost, 
     label_kernel<<<(int)((npix + 127) / 128), 128, 0, st>>>(cost, label, npix, L);
     count_launch();
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_aggregate_lhw(const float* unary, const float* msg, float* cost, int nimg, int L,
+                                 long long HW, int D, long long slice, float factor, int min_a_dir,
+                                 cudaStream_t st) {
+  const dim3 grid((unsigned)((HW + 31) / 32), (unsigned)nimg);
+  const size_t smem = (size_t)L * 33 * sizeof(float);
+  ProfScope prof(kProfElementwise, st);
+  aggregate_lhw_kernel<<<grid, 256, smem, st>>>(unary, msg, cost, L, HW, D, slice, factor, min_a_dir);
+  count_launch();
   return cudaGetLastError();
 }
 

@@ -11,7 +11,8 @@ def _dev(a, dtype=torch.float32):
 
 
 def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=True,
-            save_labels=False, enable_sgm=False, enable_min_a_dir=False, msg_init=None, context_window=0):
+            save_labels=False, enable_sgm=False, enable_min_a_dir=False, msg_init=None, context_window=0,
+            cost_labels_first=False):
     if rho is None:
         rho = 0.5 if mode == "TRWP" else 1.0
     u = _dev(unary)
@@ -21,17 +22,17 @@ def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=Tr
     e8 = torch.empty(0, dtype=torch.uint8, device="cuda")
     ew = _dev(edge_weights) if edge_weights is not None else e0
     msg = torch.zeros(n_dir, b, cv, h, w, l, device="cuda") if msg_init is None else _dev(msg_init)
-    cost = torch.full((b, cv, h, w, l), float("nan"), device="cuda")
+    cost = torch.full((b, cv, l, h, w) if cost_labels_first else (b, cv, h, w, l), float("nan"), device="cuda")
     mi = torch.zeros(n_iter, n_dir, b, cv, h, w, l, dtype=torch.uint8, device="cuda") if training else e8
     ni = torch.zeros(n_iter, n_dir, b, cv, h, w, dtype=torch.uint8, device="cuda") if training else e8
     lab = torch.zeros(n_iter, b, cv, h, w, dtype=torch.uint8, device="cuda") if save_labels else e8
     if mode == "TRWP":
         TRWP.forward(rho, n_iter, int(enable_min_a_dir), u, c, ew, msg, cost, mi, ni, e0, lab,
-                     context_window=context_window)
+                     context_window=context_window, cost_labels_first=cost_labels_first)
     else:
         mu = torch.zeros_like(msg)
         ISGMR.forward(int(enable_sgm), rho, n_iter, int(enable_min_a_dir), u, c, ew, msg, cost, mi, ni,
-                      e0, mu, lab, context_window=context_window)
+                      e0, mu, lab, context_window=context_window, cost_labels_first=cost_labels_first)
     torch.cuda.synchronize()
     return dict(cost=cost.cpu().numpy(), msg=msg.cpu().numpy(),
                 min_idx=mi.cpu().numpy() if training else None,
@@ -40,7 +41,8 @@ def forward(mode, unary, ctx, edge_weights, n_dir, n_iter, rho=None, training=Tr
 
 
 def backward(mode, ctx, edge_weights, dcost, min_idx, norm_idx, rho=None, enable_sgm=False,
-             keep_diag=False, context_window=0):
+             keep_diag=False, context_window=0, cost_labels_first=False):
+    """`dcost` is [B,cv,L,H,W] with cost_labels_first, else [B,cv,H,W,L]; dunary always [B,cv,H,W,L]."""
     if rho is None:
         rho = 0.5 if mode == "TRWP" else 1.0
     g = _dev(dcost)
@@ -50,18 +52,19 @@ def backward(mode, ctx, edge_weights, dcost, min_idx, norm_idx, rho=None, enable
     n_iter, n_dir = mi.shape[:2]
     e0 = torch.empty(0, device="cuda")
     ew = _dev(edge_weights) if edge_weights is not None else e0
-    dunary = torch.full_like(g, float("nan"))
+    shape = tuple(mi.shape[2:])
+    dunary = torch.full(shape, float("nan"), device="cuda")
     dctx = torch.zeros_like(c)
     dew = torch.zeros_like(ew)
     # scratch is deliberately filled with garbage: the library must not rely on its contents
-    dmsg = torch.full((n_dir,) + tuple(g.shape), float("nan"), device="cuda")
+    dmsg = torch.full((n_dir,) + shape, float("nan"), device="cuda")
     if mode == "TRWP":
         TRWP.backward(rho, c, ew, g, mi, ni, dunary, dctx, dew, dmsg, e0, keep_diag=keep_diag,
-                      context_window=context_window)
+                      context_window=context_window, cost_labels_first=cost_labels_first)
     else:
         dmu = torch.full_like(dmsg, float("nan"))
         ISGMR.backward(int(enable_sgm), rho, c, ew, g, mi, ni, dunary, dctx, dew, dmsg, e0, dmu,
-                       keep_diag=keep_diag, context_window=context_window)
+                       keep_diag=keep_diag, context_window=context_window, cost_labels_first=cost_labels_first)
     torch.cuda.synchronize()
     return dict(dunary=dunary.cpu().numpy(), dctx=dctx.cpu().numpy(),
                 dew=dew.cpu().numpy() if edge_weights is not None else None)

@@ -30,7 +30,8 @@ def test_exports_every_declared_symbol():
 
 def _prob(**kw):
     d = dict(n_iter=2, n_dir=4, batch=1, n_cv=1, height=8, width=9, n_disp=21, context_rank=2,
-             enable_min_a_dir=0, enable_sgm=0, keep_diag=0, rho=0.5, context_window=0, chain_part=0, chain_parts=0)
+             enable_min_a_dir=0, enable_sgm=0, keep_diag=0, rho=0.5, context_window=0, chain_part=0, chain_parts=0,
+             cost_labels_first=0)
     d.update(kw)
     return _lib.Problem(*[d[n] for n, _ in _lib.Problem._fields_])
 

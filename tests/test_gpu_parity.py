@@ -328,6 +328,30 @@ def test_warm_start_from_given_messages(mode, D, L, I):
     assert np.array_equal(got["msg"], whole["msg"])
 
 
+@pytest.mark.parametrize("mode,D,H,W,L,I", [
+    ("TRWP", 4, 13, 37, 21, 2),      # 37 pixels per row: a ragged last tile of 32
+    ("ISGMR", 8, 9, 10, 64, 2),
+    ("TRWP", 4, 5, 7, 100, 1),
+])
+def test_cost_with_labels_first(mode, D, H, W, L, I):
+    """mpl_problem::cost_labels_first: the forward writes cost_final, and the backward reads its
+    gradient, as [B,cv,L,H,W] (what pytorch/MP_module.py:232 produces with a permute); values are
+    those of the labels-last call, bit for bit."""
+    g = _gpu()
+    unary, ctx, ew, dcost = _rand_case(500 + L, mode, D, 2, 2, H, W, L, I, "sym2d")
+    plain = g.forward(mode, unary, ctx, ew, D, I)
+    first = g.forward(mode, unary, ctx, ew, D, I, cost_labels_first=True)
+    assert first["cost"].shape == (2, 2, L, H, W)
+    assert np.array_equal(first["cost"], plain["cost"].transpose(0, 1, 4, 2, 3))
+    for k in ("msg", "min_idx", "norm_idx"):
+        assert np.array_equal(first[k], plain[k]), k
+    b0 = g.backward(mode, ctx, ew, dcost, plain["min_idx"], plain["norm_idx"])
+    b1 = g.backward(mode, ctx, ew, np.ascontiguousarray(dcost.transpose(0, 1, 4, 2, 3)), plain["min_idx"],
+                    plain["norm_idx"], cost_labels_first=True)
+    for k in ("dunary", "dctx", "dew"):
+        assert np.array_equal(b0[k], b1[k]), k
+
+
 def test_context_window_statement_and_analysis():
     """Inference with a rank-1 context and more than 32 labels: the caller's statement about the
     context (mpl_problem::context_window) selects the same kernels as the library's own analysis, and
