@@ -37,6 +37,8 @@ WORKLOADS = {
     # the same inputs as a training step (learning the truncated-linear function): indices saved, fwd+bwd
     "stereo_trwp_train": ("config2_stereo", {"training": True}, True),
     "denoise_isgmr_infer": ("config3_denoise", {}, False),
+    # the same inputs as a training step (learning the truncated-quadratic function), 10 iterations
+    "denoise_isgmr_train": ("config3_denoise", {"training": True, "n_iter": 10}, True),
     "large_isgmr_train": ("config5_large", {}, True),
     "config1_trwp_train": ("config1", {"mode": "TRWP"}, True),
     "config1_isgmr_train": ("config1", {"mode": "ISGMR"}, True),

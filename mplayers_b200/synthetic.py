@@ -86,7 +86,7 @@ def config2_stereo(seed=0, H=375, W=1242, L=192, n_iter=3, training=False):
                 unary=unary.view(1, 1, L, H, W).contiguous(), label_context=ctx, edge_weights=None)
 
 
-def config3_denoise(seed=0, H=256, W=256, L=256, n_iter=50):
+def config3_denoise(seed=0, H=256, W=256, L=256, n_iter=50, training=False):
     """Denoise ISGMR forward: 12 constant rectangles/discs + N(0,20^2), unary (l-obs)^2/256,
     truncated quadratic pairwise 25*min(k^2, 200)."""
     g = _gen(seed)
@@ -106,7 +106,7 @@ def config3_denoise(seed=0, H=256, W=256, L=256, n_iter=50):
     unary = (lab - obs[None]) ** 2 / 256.0
     k = torch.arange(L, dtype=torch.float32)
     ctx = 25.0 * (k * k).clamp(max=200.0)
-    return dict(mode="ISGMR", n_dir=4, n_iter=n_iter, training=False,
+    return dict(mode="ISGMR", n_dir=4, n_iter=n_iter, training=training,
                 unary=unary.view(1, 1, L, H, W).contiguous(), label_context=ctx, edge_weights=None)
 
 
