@@ -165,6 +165,33 @@ __device__ __forceinline__ int highest_equal(const float (&val)[LMAX], float bes
   return bi;
 }
 
+// The same for a value that need not be among val: -1 if no val[f] equals it.
+template <int LMAX>
+__device__ __forceinline__ int highest_equal_or_none(const float (&val)[LMAX], float best) {
+  constexpr int NA = (LMAX + 23) / 24;
+  float acc[NA][4];
+#pragma unroll
+  for (int a = 0; a < NA; ++a) acc[a][0] = acc[a][1] = acc[a][2] = acc[a][3] = 0.f;
+#pragma unroll
+  for (int f = 0; f + 1 < LMAX; f += 2) {
+    const int a = f / 24, j = f & 2;
+    ffma2(acc[a][j], acc[a][j + 1], eq_flag(val[f], best), eq_flag(val[f + 1], best), pow2f(f % 24),
+          pow2f((f + 1) % 24), acc[a][j], acc[a][j + 1]);
+  }
+  if (LMAX & 1) {
+    constexpr int f = LMAX - 1;
+    acc[f / 24][0] = fmaf(eq_flag(val[f], best), pow2f(f % 24), acc[f / 24][0]);
+  }
+  int bi = -1;
+#pragma unroll
+  for (int a = 0; a < NA; ++a) {
+    const float sum = (acc[a][0] + acc[a][1]) + (acc[a][2] + acc[a][3]);
+    const int ex = ((__float_as_int(sum) >> 23) & 0xff) - 127 + 24 * a;
+    bi = sum != 0.f ? ex : bi;
+  }
+  return bi;
+}
+
 template <int LMAX, bool TRAIN, int CN = LMAX, int OFF = 0>
 __device__ __forceinline__ void minplus_regrow(const float* hb, const float (&cr)[CN], float e,
                                                float& best, int& bi) {

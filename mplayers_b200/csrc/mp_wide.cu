@@ -295,8 +295,18 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
           if constexpr (TRAIN) {
             // highest window offset attaining the minimum (candidates outside 0..L-1 read +inf)
             int fw = -1;
+            if constexpr (RW >= 8) {
+              // many candidates: flags summed with weights 2^k on the full-rate pipe, the index is the
+              // exponent of the sum (a compare and a select per candidate run at half rate)
+              float wv[2 * RW - 1];
 #pragma unroll
-            for (int kk = -(RW - 1); kk <= RW - 1; ++kk) fw = (cand[kk + RW] == best[i]) ? c0 + i + kk : fw;
+              for (int j = 0; j < 2 * RW - 1; ++j) wv[j] = cand[j + 1];
+              const int hw = highest_equal_or_none<2 * RW - 1>(wv, best[i]);
+              fw = hw >= 0 ? c0 + i + hw - (RW - 1) : -1;
+            } else {
+#pragma unroll
+              for (int kk = -(RW - 1); kk <= RW - 1; ++kk) fw = (cand[kk + RW] == best[i]) ? c0 + i + kk : fw;
+            }
             bidx[i] = (gv == best[i]) ? (fstar > fw ? fstar : fw) : fw;
           }
         }
