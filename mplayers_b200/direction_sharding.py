@@ -134,15 +134,16 @@ class CudaBackend:
                 _owned_ptr(norm_idx, d0), _lib.ptr(ws), n, _lib.stream_ptr(dev)))
             _lib.check_status(ws, "ISGMR forward (direction-sharded)")
 
-    def sum_directions(self, prob, d0, dc, fields, out, first=0, count=None):
-        """out[first : first + count] (flat) = sum over the owned slices of `fields`; zeros when
-        none is owned."""
+    def sum_directions(self, prob, d0, dc, fields, out, first=0, count=None, base=None):
+        """out[first : first + count] (flat) = base + sum over the owned slices of `fields`
+        (base None: plain sum; zeros when nothing is owned)."""
         dev = out.device
         count = out.numel() - first if count is None else count
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().mpl_sum_directions_range(
-                ctypes.byref(prob), d0 if dc else 0, dc, None, 0.0, _owned_ptr(fields, d0) if dc else None,
-                _lib.ptr(out), int(first), int(count), _lib.stream_ptr(dev)))
+                ctypes.byref(prob), d0 if dc else 0, dc, _lib.ptr(base) if base is not None else None, 1.0,
+                _owned_ptr(fields, d0) if dc else None, _lib.ptr(out), int(first), int(count),
+                _lib.stream_ptr(dev)))
         return out
 
     def backward_workspace(self, prob, dev):
@@ -176,20 +177,21 @@ class CudaBackend:
                 ctypes.byref(prob), _lib.ptr(ws), ws.numel(), _lib.ptr(dcontext), _lib.stream_ptr(dev)))
 
 
-def _sum_and_reduce(backend, comm, prob, d0, dc, fields, out, chunks):
+def _sum_and_reduce(backend, comm, prob, d0, dc, fields, out, chunks, base=None):
     """out = all-reduce over the ranks of (sum over this rank's slices of `fields`), formed chunk by
-    chunk: the collective of chunk k runs while chunk k + 1 is being summed."""
+    chunk: the collective of chunk k runs while chunk k + 1 is being summed.  `base` (given on ONE
+    rank only) is added to that rank's partial sum, so that it ends up in the total once."""
     n = out.numel()
     flat = out.view(-1)
     start = getattr(comm, "all_reduce_async", None)
     if start is None or chunks <= 1 or comm.world_size == 1:
-        backend.sum_directions(prob, d0, dc, fields, out)
+        backend.sum_directions(prob, d0, dc, fields, out, base=base)
         comm.all_reduce(out)
         return out
     handles = []
     for k in range(chunks):
         lo, hi = n * k // chunks, n * (k + 1) // chunks
-        backend.sum_directions(prob, d0, dc, fields, out, lo, hi - lo)
+        backend.sum_directions(prob, d0, dc, fields, out, lo, hi - lo, base=base)
         handles.append(start(flat[lo:hi]))
     for h in handles:
         comm.wait(h)
@@ -235,17 +237,22 @@ class DirectionShardedISGMRFunction(torch.autograd.Function):
             norm_idx = torch.zeros(n_iter, dc, b, cv, h, w, dtype=torch.uint8, device=unary.device)
         else:
             min_idx = norm_idx = None
+        # The aggregate A = U + (sum over ALL directions of the newest messages) comes straight out of the
+        # all-reduce: rank 0 adds the unaries to its partial sum.  The sweeps of the next iteration read
+        # it, and the sum after them overwrites it (same stream, after the sweeps).
         aggregate = unary
-        total = torch.zeros_like(unary)   # sum over ALL directions of the newest messages
-        buf = torch.empty_like(unary)
+        total = torch.empty_like(unary)
         for it in range(n_iter):
             backend.forward_directions(prob, d0, dc, aggregate, label_context, ew, rd, wr,
                                        min_idx[it] if training else None, norm_idx[it] if training else None)
-            _sum_and_reduce(backend, comm, prob, d0, dc, wr, total, chunks)
-            torch.add(unary, total, out=buf)
-            aggregate = buf
+            _sum_and_reduce(backend, comm, prob, d0, dc, wr, total, chunks,
+                            base=unary if comm.rank == 0 else None)
+            aggregate = total
             rd, wr = wr, rd
-        cost_final = unary * factor + total if factor != 1.0 else (unary + total)
+        if n_iter == 0:
+            cost_final = unary * factor
+        else:
+            cost_final = total if factor == 1.0 else total.add_(unary, alpha=factor - 1.0)
         ctx.intermediate_results = (sgm, rho, min_idx, norm_idx, label_context, ew, comm, backend, d0, dc, n_dir,
                                     part, parts)
         return cost_final

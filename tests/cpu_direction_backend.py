@@ -82,10 +82,10 @@ class CpuBackend:
                     r = best - best.min()
                     Wr[o, b, v, y, x] = r.astype(np.float32)
 
-    def sum_directions(self, p, d0, dc, fields, out, first=0, count=None):
+    def sum_directions(self, p, d0, dc, fields, out, first=0, count=None, base=None):
         flat = out.view(-1)
         count = flat.numel() - first if count is None else count
-        acc = torch.zeros(count)
+        acc = torch.zeros(count) if base is None else base.reshape(-1)[first:first + count].clone()
         for o in range(dc):
             acc += fields[o].reshape(-1)[first:first + count]
         flat[first:first + count] = acc
