@@ -56,7 +56,7 @@ typedef struct mpl_problem {
   int32_t context_window;   /* rank-1 context with more than 32 labels (inference) or more than 64 (training,
                                i.e. with index outputs) only; else ignored.
                                0: unknown -- the forward call analyses context and edge weights on the
-                                  device and reads the verdict back, i.e. it waits for `stream` once;
+                                  device and reads the result back, i.e. it waits for `stream` once;
                                   while `stream` is being captured it does not wait and evaluates all
                                   L candidates per label instead;
                                R > 0: the caller states that context[k] is non-decreasing for k < R,

@@ -193,7 +193,7 @@ void set_dirs(mpl::FwdParams& fp, int dir0, int ndirs) {
   }
 }
 
-// Verdict of the device-side analysis (launch_analyze, in `workspace`): *window = R > 0 if the
+// Result of the device-side analysis (launch_analyze, in `workspace`): *window = R > 0 if the
 // windowed evaluation is exact, else -1.  Waits for the stream.
 int read_window(const void* workspace, bool has_weights, int* window, cudaStream_t st) {
   mpl::CtxInfo hi;
@@ -205,7 +205,7 @@ int read_window(const void* workspace, bool has_weights, int* window, cudaStream
 }
 
 // Fills the sweep parameters, clears the status word and runs the context / edge-weight analysis
-// (and, where a rank-1 context may take the windowed kernel, reads its verdict back: one small
+// (and, where a rank-1 context may take the windowed kernel, reads its result back: one small
 // synchronising copy).
 int prepare_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, const float* unary,
                     const float* context, const float* edge_weights, void* workspace, bool train,
@@ -219,7 +219,7 @@ int prepare_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, con
     // Rank-1 context (inference above 32 labels, training above 64): the wide windowed kernel is
     // chosen on the host.  With a
     // statement from the caller (mpl_problem::context_window) nothing is read back; without one the
-    // verdict of the device-side analysis is copied to the host, which waits for the stream --
+    // result of the device-side analysis is copied to the host, which waits for the stream --
     // unless the stream is being captured, where waiting is not allowed: then all candidates are
     // evaluated.
     if (p->context_window > 0) {

@@ -239,6 +239,8 @@ def test_wide_inference_kernel(mode, D, H, W, L, kind, ewk):
     ("TRWP", 4, 9, 21, 192, "tl1d", "none", True),     # quantised costs: exact ties everywhere
     ("ISGMR", 8, 8, 9, 96, "tq1d", "pos", True),
     ("TRWP", 4, 8, 9, 128, "potts1d", "none", True),
+    ("TRWP", 4, 10, 840, 192, "tl1d", "pos", False),   # many short chains: shallow staging
+    ("ISGMR", 4, 64, 70, 192, "tl1d", "pos", True),    # chains longer than several stages, ties
 ])
 def test_wide_training_kernel(mode, D, H, W, L, kind, ewk, quant):
     """Training with a windowed rank-1 context and more than 64 labels runs the warp-per-chain kernel
@@ -277,6 +279,8 @@ def test_wide_training_kernel(mode, D, H, W, L, kind, ewk, quant):
     ("TRWP", 4, 8, 19, 128, "nonmono1d", "pos"),   # context that does not saturate: many far targets per step
     ("ISGMR", 4, 8, 9, 68, "nonmono1d", "none"),
     ("TRWP", 4, 9, 13, 96, "potts1d", "none"),
+    ("TRWP", 4, 10, 840, 192, "tl1d", "pos"),      # 1680 vertical chains in a launch: shallow stages (4 steps)
+    ("ISGMR", 4, 6, 700, 128, "tq1d", "none"),     # 2800 chains in the one launch of an ISGMR iteration
 ])
 def test_wide_backward_kernel(mode, D, H, W, L, kind, ewk):
     """Backward pass for a rank-1 context with 64 < L <= 256, L % 4 == 0: warp-per-chain kernel with
