@@ -222,6 +222,7 @@ NCU_TRAFFIC = {
     ("seg_trwp_train", "bwd"): 149.3e6 + 80.9e6,
     ("seg_trwp_train", "fwd"): 222.4e6 + 33.9e6,
     ("stereo_trwp_infer", "fwd"): 1788.5e6 + 338.6e6,
+    ("stereo_trwp_train", "bwd"): 1163.8e6 + 1017.2e6,
     ("denoise_isgmr_infer", "fwd"): 728.4e6 + 245.6e6,
     # captured on the 384 x 384 copy of the workload (a full-size launch is too large to replay under
     # the profiler); traffic is proportional to the pixel count, so the full-size figures are those
