@@ -53,8 +53,7 @@ typedef struct mpl_problem {
                                MPLayers/TRWP_hard_soft does), 0 = skip it (TRWP / ISGMR libs,
                                MPLayers/TRWP/TRWP_backward.cu:111-112) */
   float rho;                /* 0.5 for TRWP, 1 for ISGMR (pytorch/MP_module.py:172) */
-  int32_t context_window;   /* rank-1 context with more than 32 labels (inference) or more than 64 (training,
-                               i.e. with index outputs) only; else ignored.
+  int32_t context_window;   /* rank-1 context with more than 32 labels only; else ignored.
                                0: unknown -- the forward call analyses context and edge weights on the
                                   device and reads the result back, i.e. it waits for `stream` once;
                                   while `stream` is being captured it does not wait and evaluates all

@@ -232,15 +232,15 @@ class MPModule(torch.nn.Module):
         return label_context
 
     def _context_window(self, label_context, edge_weights):
-        """A rank-1 context with more than 32 labels (inference) or more than 64 (training): the
-        kernels' windowed evaluation needs to know where the context saturates.  The library can find out per call, but then the
+        """A rank-1 context with more than 32 labels: the kernels' windowed evaluation needs to know
+        where the context saturates.  The library can find out per call, but then the
         call waits for the stream; here the answer is computed once per state of the context
         parameter (its version counter tells when an optimiser step or an assignment changed it) and
         handed down as a statement (mpl_problem::context_window).  Only without edge weights: those
         are new tensors every call, and the statement covers them too."""
         if label_context.dim() != 1 or edge_weights is not None:
             return 0
-        if label_context.numel() <= (64 if self.training else 32):
+        if label_context.numel() <= 32:
             return 0
         src = self.label_context
         key = (id(src), src._version, src.data_ptr(), getattr(self.args, 'mpnet_smoothness_train', None),

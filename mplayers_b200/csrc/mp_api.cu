@@ -215,9 +215,8 @@ int prepare_forward(mpl::FwdParams& fp, const mpl_problem* p, const Dims& d, con
   MPL_CUDA(cudaMemsetAsync(fp.status, 0, sizeof(int), st));
   MPL_CUDA(mpl::launch_analyze(context, L, p->context_rank, edge_weights, d.npix * D,
                                static_cast<mpl::CtxInfo*>(workspace), st));
-  if (p->context_rank == 1 && (train ? L > 64 : L > 32)) {
-    // Rank-1 context (inference above 32 labels, training above 64): the wide windowed kernel is
-    // chosen on the host.  With a
+  if (p->context_rank == 1 && L > 32) {
+    // Rank-1 context with more than 32 labels: the wide windowed kernel is chosen on the host.  With a
     // statement from the caller (mpl_problem::context_window) nothing is read back; without one the
     // result of the device-side analysis is copied to the host, which waits for the stream --
     // unless the stream is being captured, where waiting is not allowed: then all candidates are

@@ -1476,12 +1476,13 @@ cudaError_t launch_forward_sweep(const FwdParams& p, bool train, cudaStream_t st
     if (p.L == 21) return train ? launch_warp<21, true>(rest, st) : launch_warp<21, false>(rest, st);
     return train ? launch_warp<32, true>(rest, st) : launch_warp<32, false>(rest, st);
   }
-  // windowed rank-1 context: warp-per-chain kernel (training keeps the pair kernel up to 64 labels)
+  // windowed rank-1 context: warp-per-chain kernel, inference and training (at most 31 candidates per
+  // label against the pair kernel's 64: 2.0 against 7.2 ms for a 512 x 512 x 64 training forward)
   static const bool no_wide_train = [] {  // MPL_NO_WIDE_TRAIN=1: tuning / comparison knob
     const char* e = getenv("MPL_NO_WIDE_TRAIN");
     return e && e[0] == '1';
   }();
-  if (p.ctx_rank == 1 && (!train || (p.L > 64 && !no_wide_train)) && p.host_windowed && p.host_R <= 16 &&
+  if (p.ctx_rank == 1 && (!train || !no_wide_train) && p.host_windowed && p.host_R <= 16 &&
       p.L <= 256 && cta_tma_eligible(p) && (p.agg || p.D != 2)) {
     return launch_forward_wide(p, train, st);
   }

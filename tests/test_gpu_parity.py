@@ -240,11 +240,13 @@ def test_wide_inference_kernel(mode, D, H, W, L, kind, ewk):
     ("ISGMR", 8, 8, 9, 96, "tq1d", "pos", True),
     ("TRWP", 4, 8, 9, 128, "potts1d", "none", True),
     ("TRWP", 4, 10, 840, 192, "tl1d", "pos", False),   # many short chains: shallow staging
+    ("ISGMR", 8, 10, 9, 64, "tl1d", "pos", True),      # 2 labels per lane (33..64 labels, narrow window)
+    ("TRWP", 4, 7, 19, 36, "tq1d", "pos", False),      # window 6 on 36 labels
     ("ISGMR", 4, 64, 70, 192, "tl1d", "pos", True),    # chains longer than several stages, ties
 ])
 def test_wide_training_kernel(mode, D, H, W, L, kind, ewk, quant):
-    """Training with a windowed rank-1 context and more than 64 labels runs the warp-per-chain kernel
-    too.  Its saved indices follow the reference's rule among equal candidates
+    """Training with a windowed rank-1 context runs the warp-per-chain kernel too (above 64 labels, and
+    from 33 labels for windows up to 8).  Its saved indices follow the reference's rule among equal candidates
     (MPLayers/TRWP/TRWP_forward.cu:126-152: the highest index wins), so they must EQUAL the dense
     evaluation's, also where costs quantised to quarters make most minima tie; the backward pass
     replays them."""
