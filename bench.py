@@ -203,10 +203,9 @@ def dominant_kernel(cfg, kind):
     if kind == "bwd":
         if L <= 32:
             return "bwd_tma_kernel"
-        if pair:
-            return "bwd_pair_kernel"
-        wide = cfg["label_context"].dim() == 1 and 64 < L <= 256 and L % 4 == 0
-        return "bwd_wide_kernel" if wide else "bwd_cta_kernel"
+        if cfg["label_context"].dim() == 1 and 32 < L <= 256 and L % 4 == 0:
+            return "bwd_wide_kernel"
+        return "bwd_pair_kernel" if pair else "bwd_cta_kernel"
     if L <= 32:
         return "fwd_tma_kernel"
     if (not cfg["training"] or L > 64) and cfg["label_context"].dim() == 1 and L % 4 == 0:

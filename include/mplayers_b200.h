@@ -64,7 +64,7 @@ typedef struct mpl_problem {
                                   asynchronous; a wrong statement gives wrong results;
                                -1: evaluate all L candidates per label.
                                Backward calls never read anything back; there a value R > 0 is only a
-                               hint for how the scatter of a rank-1 context with more than 64 labels
+                               hint for how the scatter of a rank-1 context with more than 32 labels
                                is split (any value gives the same sums). */
   int32_t chain_part;       /* iteration-level ISGMR entry points only (mpl_isgmr_forward_directions, */
   int32_t chain_parts;      /* mpl_isgmr_backward_directions): the call runs part chain_part of

@@ -55,7 +55,7 @@ def backward(rho, context, edge_weights, dcost_final, msg_min_index, msg_norm_in
              dcontext, dedge_weights, dmsg, dunary_update, keep_diag=None, context_window=0,
              cost_labels_first=False):
     """`context_window` (keyword, not in the reference's signature): in the backward pass only a hint
-    for how the scatter of a rank-1 context with more than 64 labels is split; any value gives the
+    for how the scatter of a rank-1 context with more than 32 labels is split; any value gives the
     same sums."""
     dev = dcost_final.device
     for t, n in ((context, "context"), (edge_weights, "edge_weights"), (dcost_final, "dcost_final"),

@@ -379,7 +379,7 @@ int backward_common(bool isgmr, const mpl_problem* p, const float* context, cons
   // which knows the C + P scheme as well.)
   const bool pair_cp = L <= 64 && (L & 3) == 0 && ((((uintptr_t)dunary | (uintptr_t)dmsg) & 15) == 0) &&
                        !mpl::pair_kernels_disabled();
-  // (a rank-1 context with 64 < L <= 256 runs the several-labels-per-lane kernel, C + P too)
+  // (a rank-1 context with 32 < L <= 256 runs the several-labels-per-lane kernel, C + P too)
   const bool wide_cp = mpl::bwd_wide_eligible(L, p->context_rank, 1, dunary, dmsg, dmsg);
   const int cp = isgmr ? 2 : ((L <= 32 || pair_cp || wide_cp) ? 1 : 0);
   float* X = isgmr ? dmsg_update : dmsg;  // gradients of the messages the sweeps produced

@@ -1476,6 +1476,10 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
       e = p.D == 4 ? go(bwd_warp_kernel<4, 0>) : p.D == 8 ? go(bwd_warp_kernel<8, 0>) : go(bwd_warp_kernel<0, 0>);
     }
     if (e != cudaSuccess) return e;
+  } else if (bwd_wide_eligible(L, p.ctx_rank, p.cp_scheme, p.dunary, p.dm_read, p.dm_acc)) {
+    // rank-1 context, 32 < L <= 256: several labels per lane, scatter split into near and far indices
+    cudaError_t e = launch_backward_wide(p, total, st);
+    if (e != cudaSuccess) return e;
   } else if (bwd_pair_eligible(p)) {
     const size_t per_warp = (size_t)((bwd_pair_floats(L, p.ctx_rank, p.cp_scheme) + 3) & ~3) * sizeof(float);
     const size_t table = (size_t)((L * LS + 3) & ~3) * sizeof(float);
@@ -1494,9 +1498,6 @@ cudaError_t launch_backward_sweep(const BwdParams& p0, cudaStream_t st) {
     } else {
       e = p.cp_scheme == 1 ? go(bwd_pair_kernel<1, false>) : go(bwd_pair_kernel<2, false>);
     }
-    if (e != cudaSuccess) return e;
-  } else if (bwd_wide_eligible(L, p.ctx_rank, p.cp_scheme, p.dunary, p.dm_read, p.dm_acc)) {
-    cudaError_t e = launch_backward_wide(p, total, st);
     if (e != cudaSuccess) return e;
   } else {
     const int NT = ((L + 31) / 32) * 32;

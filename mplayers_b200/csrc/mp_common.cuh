@@ -311,7 +311,7 @@ cudaError_t launch_aggregate_lhw(const float* unary, const float* msg, float* co
 cudaError_t launch_backward_init_lhw(const float* dcost, float* dunary, float* dm, int nimg, int L, long long HW,
                                      int D, float factor, int cp_scheme, cudaStream_t st);
 cudaError_t launch_backward_sweep(const BwdParams& p, cudaStream_t st);
-// mp_wide_bwd.cu: rank-1 context, 64 < L <= 256, L % 4 == 0, schemes 1 and 2
+// mp_wide_bwd.cu: rank-1 context, 32 < L <= 256, L % 4 == 0, schemes 1 and 2
 bool bwd_wide_eligible(int L, int ctx_rank, int cp_scheme, const void* dunary, const void* dm_read,
                        const void* dm_acc);
 cudaError_t launch_backward_wide(const BwdParams& p, int total, cudaStream_t st);

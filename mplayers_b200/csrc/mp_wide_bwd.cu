@@ -1,4 +1,4 @@
-// Backward sweep for a rank-1 context with 64 < L <= 256 labels, L % 4 == 0 (learning a truncated
+// Backward sweep for a rank-1 context with 32 < L <= 256 labels, L % 4 == 0 (learning a truncated
 // linear / quadratic function on stereo- or denoising-sized label sets): one WARP per chain, LPT
 // consecutive labels per lane, schemes 1 (C + P bookkeeping, TRWP) and 2 (scatter field, ISGMR).
 // Replaces, for those problems, the reference's backward chain kernels with one thread per label,
@@ -498,6 +498,7 @@ cudaError_t launch_bw_r(const BwdParams& p, int total, cudaStream_t st) {
 template <int SCH>
 cudaError_t launch_bw_l(const BwdParams& p, int total, cudaStream_t st) {
   switch (2 * ((p.L + 63) / 64)) {
+    case 2: return launch_bw_r<2, SCH>(p, total, st);
     case 4: return launch_bw_r<4, SCH>(p, total, st);
     case 6: return launch_bw_r<6, SCH>(p, total, st);
     default: return launch_bw_r<8, SCH>(p, total, st);
@@ -508,7 +509,11 @@ cudaError_t launch_bw_l(const BwdParams& p, int total, cudaStream_t st) {
 
 bool bwd_wide_eligible(int L, int ctx_rank, int cp_scheme, const void* dunary, const void* dm_read,
                        const void* dm_acc) {
-  if (ctx_rank != 1 || L <= 64 || L > 256 || (L & 3) || cp_scheme == 0) return false;
+  static const int min_l = [] {  // MPL_WIDE_BWD_MIN_L: tuning / comparison knob (first label count taken)
+    const char* e = getenv("MPL_WIDE_BWD_MIN_L");
+    return e ? atoi(e) : 33;
+  }();
+  if (ctx_rank != 1 || L < min_l || L > 256 || (L & 3) || cp_scheme == 0) return false;
   if (((uintptr_t)dunary | (uintptr_t)dm_read | (uintptr_t)dm_acc) & 15) return false;
   return !pair_kernels_disabled();
 }

@@ -282,10 +282,12 @@ def test_wide_training_kernel(mode, D, H, W, L, kind, ewk, quant):
     ("ISGMR", 4, 8, 9, 68, "nonmono1d", "none"),
     ("TRWP", 4, 9, 13, 96, "potts1d", "none"),
     ("TRWP", 4, 10, 840, 192, "tl1d", "pos"),      # 1680 vertical chains in a launch: shallow stages (4 steps)
+    ("ISGMR", 8, 10, 9, 64, "tl1d", "pos"),        # 2 labels per lane
+    ("TRWP", 4, 7, 19, 36, "tq1d", "pos"),         # 2 labels per lane, half of the lanes without labels
     ("ISGMR", 4, 6, 700, 128, "tq1d", "none"),     # 2800 chains in the one launch of an ISGMR iteration
 ])
 def test_wide_backward_kernel(mode, D, H, W, L, kind, ewk):
-    """Backward pass for a rank-1 context with 64 < L <= 256, L % 4 == 0: warp-per-chain kernel with
+    """Backward pass for a rank-1 context with 32 < L <= 256, L % 4 == 0: warp-per-chain kernel with
     several labels per lane.  The split of the scatter into near and far indices is a tuning
     parameter (the window hint): every width, and no hint, must give the oracle's gradients."""
     g = _gpu()
