@@ -49,6 +49,16 @@ def test_shard_plan_splits_chains_when_ranks_outnumber_pairs():
             assert sorted(p for p, _ in lst) == list(range(parts)) and all(q == parts for _, q in lst)
 
 
+def test_chunk_count_follows_the_world_size():
+    f = ds.DirectionShardedISGMRFunction
+    assert [f._chunks(w) for w in (1, 2, 4, 5, 8)] == [4, 4, 4, 1, 1]
+    f.chunks = 2                                     # an explicit setting wins
+    try:
+        assert f._chunks(8) == 2
+    finally:
+        f.chunks = None
+
+
 def _inputs():
     rng = np.random.default_rng(11)
     B, H, W, L, D, I = 1, 5, 6, 4, 8, 2

@@ -145,6 +145,8 @@ def _check(results, want, exact=False):
     (8, (1, 20, 17, 21, 8, 2, True)),     # two ranks per pair: each walks half of the pair's lines
     (6, (2, 18, 22, 64, 4, 2, True)),     # three ranks per pair, two images, two-labels-per-lane kernels
     (5, (1, 14, 15, 40, 8, 2, False)),    # more ranks than pairs but not twice as many: one rank owns nothing
+    (8, (1, 14, 15, 96, 8, 2, False)),    # 1-D context, 96 labels: the several-labels-per-lane kernels on half of a pair's lines
+    (6, (1, 12, 18, 40, 4, 2, False)),    # 1-D context, three ranks per pair
 ])
 def test_thread_ranks_match_the_monolithic_layer(world, shape):
     B, H, W, L, D, I, rank2 = shape
