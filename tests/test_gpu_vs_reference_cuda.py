@@ -152,6 +152,10 @@ def test_isgmr_rank1_training():
     ("segmentation", "config4_segmentation", {}, True),
     ("stereo", "config2_stereo", {}, False),
     ("denoise", "config3_denoise", {"n_iter": 10}, False),
+    # the same inputs as training steps: the several-labels-per-lane kernels save every index the
+    # reference's kernels save, at full size, and their gradients agree
+    ("stereo training", "config2_stereo", {"training": True}, True),
+    ("denoise training", "config3_denoise", {"n_iter": 3, "training": True}, True),
 ])
 def test_benchmark_configurations_full_size(name, gen, kw, train):
     """The seeded synthetic inputs of the benchmark workloads at full size (the denoising one with
