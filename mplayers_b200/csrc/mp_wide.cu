@@ -177,6 +177,15 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
   float uu[LPT], r[LPT];
 #pragma unroll
   for (int i = 0; i < LPT; ++i) uu[i] = 0.f, r[i] = 0.f;
+  // Everything that moves with the chain pixel is kept as a running pointer or offset (the stage
+  // depth K is a launch parameter, so nothing of it folds into immediates).
+  const int KL = K * L;
+  const int ostep = ch.pstep * L;
+  float* out = Mw + (long long)pix0 * L + c0;                       // message row of the current pixel
+  uint8_t* idxp = TRAIN ? MI + (long long)pix0 * L + c0 : nullptr;  // its argmin indices
+  uint8_t* nrmp = TRAIN ? NI + pix0 : nullptr;                      // its normalisation index
+  int hpar = 0;                                                     // which window buffer the pixel writes
+  bool first = true;                                                // chain pixel 0 only provides inputs
 
   for (int s = 0; s < nstages; ++s) {
     const int slot = s % NS;
@@ -191,8 +200,9 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
     const int kbase = (contiguous && ch.pstep == -1) ? np - 1 : (up ? K - 1 : 0);
     const int kstep = ((contiguous && ch.pstep == -1) || up) ? -1 : 1;
     __syncwarp();
-    for (int k = 0; k < np; ++k) {
-      const float* t = T + (kbase + k * kstep) * L + c0;
+    const float* t = T + kbase * L + c0;
+    const int tstep = kstep * L;
+    for (int k = 0; k < np; ++k, t += tstep, out += ostep, hpar ^= 1) {
       // inputs of this pixel -> UU (reference order of the additions), LPT labels per lane
       float un[LPT];
       if (nl == LPT) {
@@ -211,7 +221,7 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
           if (a <= D && !AGG) {
 #pragma unroll
             for (int q = 0; q < LPT / 2; ++q) {
-              const float2 x = reinterpret_cast<const float2*>(t + a * K * L)[q];
+              const float2 x = reinterpret_cast<const float2*>(t + a * KL)[q];
               v[2 * q] += x.x, v[2 * q + 1] += x.y;
             }
           }
@@ -225,15 +235,15 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
           if (i < nl) {
             float sum = t[i];
             if (!AGG)
-              for (int a = 1; a <= D; ++a) sum += t[a * K * L + i];
+              for (int a = 1; a <= D; ++a) sum += t[a * KL + i];
             sum -= t[dir_off + i];
             un[i] = fmaf(sum, rho, -t[inv_off + i]);
           }
         }
       }
-      if (s + k > 0) {
+      if (!first) {
         const float e = et[k];
-        float* hw = hwin + ((s * K + k) & 1) * (LP + 2 * G);
+        float* hw = hwin + hpar * (LP + 2 * G);
         float hl = kInf;
         float hv[LPT];
         if (nl == LPT) {
@@ -311,26 +321,23 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
           }
         }
         const float m = warp_min(bl);
-        const int pxo = pix0 + (s * K + k) * ch.pstep;
         if constexpr (TRAIN) {
           int ln = -1;
 #pragma unroll
           for (int i = 0; i < LPT; ++i) ln = (i < nl && best[i] == m) ? c0 + i : ln;
           const int nrm = warp_max_i32(ln);
-          if (lane == 0) NI[pxo] = (uint8_t)nrm;
-          uint8_t* mi = MI + (long long)pxo * L + c0;
+          if (lane == 0) *nrmp = (uint8_t)nrm;
           if (nl == LPT) {
 #pragma unroll
             for (int q = 0; q < LPT / 2; ++q)
-              reinterpret_cast<unsigned short*>(mi)[q] =
+              reinterpret_cast<unsigned short*>(idxp)[q] =
                   (unsigned short)((bidx[2 * q] & 0xff) | ((bidx[2 * q + 1] & 0xff) << 8));
           } else {
 #pragma unroll
             for (int i = 0; i < LPT; ++i)
-              if (i < nl) mi[i] = (uint8_t)bidx[i];
+              if (i < nl) idxp[i] = (uint8_t)bidx[i];
           }
         }
-        float* out = Mw + (long long)pxo * L + c0;
 #pragma unroll
         for (int i = 0; i < LPT; ++i) r[i] = best[i] - m;
         if (nl == LPT) {
@@ -344,6 +351,11 @@ __global__ void __launch_bounds__(kWideChains * 64, 1) fwd_wide_kernel(const __g
       }
 #pragma unroll
       for (int i = 0; i < LPT; ++i) uu[i] = un[i];
+      first = false;
+      if constexpr (TRAIN) {
+        idxp += ostep;
+        nrmp += ch.pstep;
+      }
     }
     if (lane < K) etile[((s + 1) & 1) * K + lane] = e_next;
     e_next = load_e(s + 2);
