@@ -232,7 +232,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, u
                : "memory");
 }
 // Waits for the phase with the given parity; gives up after `limit` clocks (default: about a second)
-// and returns false.
+// and returns false.  Each try may leave the thread suspended for up to kMbarSuspendNs (it resumes
+// as soon as the phase completes), so a warp that is far ahead of its partner (a producer with a
+// full ring) does not spend issue slots of its scheduler on polling.
+constexpr unsigned kMbarSuspendNs = 20000;
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
                                           long long limit = 2000000000ll) {
   const unsigned a = smem_u32(bar);
@@ -241,10 +244,10 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     unsigned ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(a), "r"(parity)
+        : "r"(a), "r"(parity), "r"(kMbarSuspendNs)
         : "memory");
     if (ok) return true;
     if (clock64() - t0 > limit) return false;
