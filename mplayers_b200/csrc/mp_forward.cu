@@ -386,8 +386,14 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
     sum -= t[dir_off];
     return fmaf(sum, rho, -t[inv_off]);
   };
-  // message of chain pixel `px` from its predecessor's UU (in `uu`) and running message `r`
-  auto step = [&](const float* t, float e, int par, int px) {
+  // Output rows of the current chain pixel, moved by one pixel per step (running pointers: one
+  // 64-bit add each instead of an index multiplication and a widening add per store).
+  const long long ostep = (long long)pstep * L;
+  float* mw = Mwl + (long long)px0 * L;
+  uint8_t* mip = TRAIN ? MIl + (long long)px0 * L : nullptr;
+  uint8_t* nip = TRAIN ? NI + px0 : nullptr;
+  // message of the current chain pixel from its predecessor's UU (in `uu`) and running message `r`
+  auto step = [&](const float* t, float e, int par) {
     const float uu_next = uu_at(t);
     float* hb = hbuf + par * 32;
     if (LT == 0 || LMAX != LT) {
@@ -403,14 +409,20 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
     r = best - m;
     // Unpredicated stores: idle lanes hold the same values as lane L-1 and write the same
     // address, and the normalisation index is warp-uniform.
-    const int of = px * L;
-    Mwl[of] = r;
+    *mw = r;
     if (TRAIN) {
       const unsigned bal = __ballot_sync(0xffffffffu, best == m) & lmask;
-      MIl[of] = (uint8_t)bi;
-      NI[px] = (uint8_t)(31 - __clz(bal));
+      *mip = (uint8_t)bi;
+      *nip = (uint8_t)(31 - __clz(bal));
     }
     uu = uu_next;
+  };
+  auto advance = [&]() {
+    mw += ostep;
+    if (TRAIN) {
+      mip += ostep;
+      nip += pstep;
+    }
   };
 
   for (int s = 0; s < nstages; ++s) {
@@ -431,18 +443,21 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
       t0 = T + wc * A * kTK * L + (FWD ? 0 : (npix - 1) * L);
       e0 = ET + wc * kTK + (FWD ? 0 : npix - 1);
     }
-    const int pxs = px0 + s * kTK * pstep;
     if (s > 0 && npix == kTK) {
       // full stage: fully unrolled, every tile offset is an immediate
 #pragma unroll
-      for (int k = 0; k < kTK; ++k) step(t0 + k * sk, e0[k * ek], k & 1, pxs + k * pstep);
+      for (int k = 0; k < kTK; ++k) {
+        step(t0 + k * sk, e0[k * ek], k & 1);
+        advance();
+      }
     } else {
       for (int k = 0; k < npix; ++k) {
         if (s + k == 0) {
           uu = uu_at(t0);  // chain pixel 0 only provides the inputs of pixel 1
         } else {
-          step(t0 + k * sk, e0[k * ek], k & 1, pxs + k * pstep);
+          step(t0 + k * sk, e0[k * ek], k & 1);
         }
+        advance();
       }
     }
     __syncwarp();
