@@ -675,7 +675,10 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
   load_blk(0, e_cur, n_cur);
 
   float q0 = 0.f, q1 = 0.f;  // scatter sums carried from the successor pixel (labels c0, c0 + 1)
-  int of = pixl * L + c0;
+  // output rows of the current pixel (labels c0, c0 + 1), moved by one pixel per step
+  float* pA = (CP ? DU : DMa + (long long)dir * p.slice) + (long long)pixl * L + c0;  // C, or the scatter field
+  float* pB = DMr + (long long)pixl * L + c0;                                         // P_dir
+  float* pI = DMa + (long long)inv * p.slice + (long long)pixl * L + c0;              // P_inv
   for (int b = 0; b < nblocks; ++b) {
     load_blk(b + 1, e_nxt, n_nxt);
     const int rows = stage_rows(b);
@@ -710,13 +713,16 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
       s_cur += __shfl_xor_sync(0xffffffffu, s_cur, 16);
     }
     const int send = len - kPB * b < kPB ? len - kPB * b : kPB;
-    for (int sl = 0; sl < send; ++sl) {
+    const float* row = T + (flip ? rows - 1 : 0) * L + c0;
+    const int rstep = flip ? -L : L;
+    const uint8_t* irow = IT;
+    float* drow = dtile + lane;
+    for (int sl = 0; sl < send; ++sl, row += rstep, irow += L, drow += 33, pA -= ostep, pB -= ostep, pI -= ostep) {
       const int s = kPB * b + sl;
       const float rq0 = rho * q0, rq1 = rho * q1;
       float qn0 = 0.f, qn1 = 0.f;
       float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
       if (act && sl < rows) {
-        const float* row = T + (flip ? rows - 1 - sl : sl) * L + c0;
         x0 = *reinterpret_cast<const float2*>(row);
         if (CP) x1 = *reinterpret_cast<const float2*>(row + kPB * L);
       }
@@ -726,7 +732,7 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
         const float S = __shfl_sync(0xffffffffu, s_cur, sl);
         float t0 = 0.f, t1 = 0.f, cv0 = 0.f, cv1 = 0.f;
         if (act) {
-          const uchar2 fi = *reinterpret_cast<const uchar2*>(IT + sl * L);
+          const uchar2 fi = *reinterpret_cast<const uchar2*>(irow);
           const int f0 = fi.x, f1 = fi.y;
           t0 = x0.x + x1.x + rq0;
           t1 = x0.y + x1.y + rq1;
@@ -746,25 +752,24 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
           *reinterpret_cast<float2*>(tb + c0) = make_float2(t0, t1);
           *reinterpret_cast<float2*>(ib + c0) = make_float2((float)f0, (float)f1);
         }
-        dtile[sl * 33 + lane] = fmaf(cv0, t0, cv1 * t1);
+        *drow = fmaf(cv0, t0, cv1 * t1);
         __syncwarp();
         gather_q2<FULL>(ts + (s & 1) * 64, is + (s & 1) * 64, L, (float)c0, qn0, qn1);
       }
       if (act) {
         if (!CP) {
           // scatter field of this direction at this pixel
-          *reinterpret_cast<float2*>(DMa + (long long)dir * p.slice + of) = make_float2(q0, q1);
+          *reinterpret_cast<float2*>(pA) = make_float2(q0, q1);
         } else {
           const float2 cn = make_float2(x0.x + rq0, x0.y + rq1);  // dU and every dM_k (k != dir, inv) receive rho*q
-          *reinterpret_cast<float2*>(DU + of) = cn;
-          *reinterpret_cast<float2*>(DMr + of) = make_float2(-cn.x, -cn.y);  // dM_dir = C + P_dir = 0 after its sweep
-          atomicAdd(DMa + inv * p.slice + of, -q0);
-          atomicAdd(DMa + inv * p.slice + of + 1, -q1);
+          *reinterpret_cast<float2*>(pA) = cn;
+          *reinterpret_cast<float2*>(pB) = make_float2(-cn.x, -cn.y);  // dM_dir = C + P_dir = 0 after its sweep
+          atomicAdd(pI, -q0);
+          atomicAdd(pI + 1, -q1);
         }
       }
       q0 = qn0;
       q1 = qn1;
-      of -= ostep;
     }
     // edge-weight gradients of this block: lane j sums row j of the product tile
     __syncwarp();
