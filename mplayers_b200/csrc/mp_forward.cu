@@ -1339,9 +1339,15 @@ __global__ void __launch_bounds__(kPairSWarps * 32, 3) fwd_pair_smem_kernel(cons
   if (lane < K) etile[lane] = load_e(0);
   float e_next = load_e(1);
   float uu0 = 0.f, uu1 = 0.f, r0 = 0.f, r1 = 0.f;
-  int po = pix0 * L;
-  const int postep = ch.pstep * L;
-  int px = pix0;
+  // rows of the current chain pixel, moved by one pixel per step (the stage depth is a launch
+  // parameter: nothing of it folds into immediates)
+  const int postep = ch.pstep * L, KL = K * L;
+  float* mwa = Mw + (long long)pix0 * L + la;
+  uint8_t* mia = TRAIN ? MI + (long long)pix0 * L + la : nullptr;
+  uint8_t* nip = TRAIN ? NI + pix0 : nullptr;
+  int hpar = 0;
+  bool first = true;
+  const bool flip = contiguous && ch.pstep == -1;
   for (int s = 0; s < nstages; ++s) {
     const int slot = s % NS;
     if (!mbar_wait(&full[slot], (s / NS) & 1)) {
@@ -1351,18 +1357,18 @@ __global__ void __launch_bounds__(kPairSWarps * 32, 3) fwd_pair_smem_kernel(cons
     const int np = len - s * K < K ? len - s * K : K;
     const float* T = tiles + slot * tile_floats;
     const float* et = etile + (s & 1) * K;
-    const bool flip = contiguous && ch.pstep == -1;
     __syncwarp();
-    for (int k = 0; k < np; ++k) {
-      const float* t = T + (flip ? np - 1 - k : k) * L;
+    const float* t = T + (flip ? np - 1 : 0) * L;
+    const int tstep = flip ? -L : L;
+    for (int k = 0; k < np; ++k, t += tstep, mwa += postep, hpar ^= 64) {
       float va = t[la], vb = t[lbc];
       if (!p.agg)
-        for (int a = 1; a <= D; ++a) va += t[a * K * L + la], vb += t[a * K * L + lbc];
+        for (int a = 1; a <= D; ++a) va += t[a * KL + la], vb += t[a * KL + lbc];
       const float un0 = fmaf(va - t[dir_off + la], rho, -t[inv_off + la]);
       const float un1 = fmaf(vb - t[dir_off + lbc], rho, -t[inv_off + lbc]);
-      if (s + k > 0) {
+      if (!first) {
         const float e = et[k];
-        float* hb = hbuf + ((s * K + k) & 1) * 64;
+        float* hb = hbuf + hpar;
         hb[la] = fmaf(rho, r0, uu0);
         if (actb) hb[lb] = fmaf(rho, r1, uu1);
         __syncwarp();
@@ -1374,20 +1380,23 @@ __global__ void __launch_bounds__(kPairSWarps * 32, 3) fwd_pair_smem_kernel(cons
         const float m = warp_min(fminf(b0, x1));
         r0 = b0 - m;
         r1 = b1 - m;
-        Mw[po + la] = r0;
-        if (actb) Mw[po + lb] = r1;
+        mwa[0] = r0;
+        if (actb) mwa[32] = r1;
         if (TRAIN) {
           const unsigned bal0 = __ballot_sync(0xffffffffu, b0 == m);
           const unsigned bal1 = __ballot_sync(0xffffffffu, x1 == m);
-          MI[po + la] = (uint8_t)i0;
-          if (actb) MI[po + lb] = (uint8_t)i1;
-          if (lane == 0) NI[px] = (uint8_t)(bal1 ? 63 - __clz(bal1) : 31 - __clz(bal0));
+          mia[0] = (uint8_t)i0;
+          if (actb) mia[32] = (uint8_t)i1;
+          if (lane == 0) *nip = (uint8_t)(bal1 ? 63 - __clz(bal1) : 31 - __clz(bal0));
         }
       }
       uu0 = un0;
       uu1 = un1;
-      po += postep;
-      px += ch.pstep;
+      first = false;
+      if (TRAIN) {
+        mia += postep;
+        nip += ch.pstep;
+      }
     }
     if (lane < K) etile[((s + 1) & 1) * K + lane] = e_next;
     e_next = load_e(s + 2);
