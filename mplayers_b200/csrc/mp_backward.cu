@@ -414,8 +414,14 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
   load_scalars(0, e_st, n_st);
   load_idx(0, fa);
 
+  // output rows of the current pixel, moved by one pixel per step
+  const long long ostep = (long long)pstep * L;
+  float* pC = QM ? nullptr : Cl + (long long)px0 * L;
+  float* pPd = Pdl + (long long)px0 * L;
+  float* pPi = Pil + (long long)px0 * L;
+  float* pQ = Ql + (long long)px0 * L;
   // one step: t = tile pointer of this pixel (C at t[0], P_dir at t[sa]), k = step inside the stage
-  auto step = [&](const float* t, int k, int f, float S_st, int px, bool has_front) {
+  auto step = [&](const float* t, int k, int f, float S_st, bool has_front) {
     const float cval = QM ? 0.f : t[0];
     const float rq = rho * q;
     float qn = 0.f;
@@ -436,14 +442,17 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
       __syncwarp();
       qn = gather_q<LT>(tb, ib, L, mef);
     }
-    const int of = px * L;
     if constexpr (QM) {
-      Ql[of] = q;
+      *pQ = q;
+      pQ += ostep;
     } else {
       const float cnew = cval + rq;  // dU and every dM_k (k != dir, inv) receive rho*q
-      Cl[of] = cnew;
-      Pdl[of] = -cnew;               // dM_dir = C + P_dir = 0 after its sweep
-      if (act) atomicAdd(Pil + of, -q);
+      *pC = cnew;
+      *pPd = -cnew;                  // dM_dir = C + P_dir = 0 after its sweep
+      if (act) atomicAdd(pPi, -q);
+      pC += ostep;
+      pPd += ostep;
+      pPi += ostep;
     }
     q = qn;
   };
@@ -479,11 +488,11 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
     const int pxs = px0 + s * kBK * pstep;
     if (npix == kBK && s != nstages - 1) {
 #pragma unroll
-      for (int k = 0; k < kBK; ++k) step(tl + k * sk, k, fa[k], S_st, pxs + k * pstep, true);
+      for (int k = 0; k < kBK; ++k) step(tl + k * sk, k, fa[k], S_st, true);
     } else {
 #pragma unroll
       for (int k = 0; k < kBK; ++k)
-        if (k < npix) step(tl + k * sk, k, fa[k], S_st, pxs + k * pstep, s * kBK + k < nsteps);
+        if (k < npix) step(tl + k * sk, k, fa[k], S_st, s * kBK + k < nsteps);
     }
     // edge-weight gradients of this stage: lane j sums row j of the product tile
     __syncwarp();
