@@ -53,7 +53,8 @@ WORKLOADS = {
     "large_isgmr_train_384": ("config5_large", {"H": 384, "W": 384, "n_iter": 4}, True),
 }
 # the configurations carried in the `workloads` block next to the headline one
-EXTRA_WORKLOADS = ["stereo_trwp_infer", "denoise_isgmr_infer", "large_isgmr_train"]
+# (the stereo inputs also as a training step: the 192-label forward + backward)
+EXTRA_WORKLOADS = ["stereo_trwp_infer", "stereo_trwp_train", "denoise_isgmr_infer", "large_isgmr_train"]
 METRIC_UNIT = "pixel*label*iter/s"
 
 
