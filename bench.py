@@ -36,6 +36,8 @@ WORKLOADS = {
     "stereo_trwp_infer": ("config2_stereo", {}, False),
     # the same inputs as a training step (learning the truncated-linear function): indices saved, fwd+bwd
     "stereo_trwp_train": ("config2_stereo", {"training": True}, True),
+    # reduced copy of it (same labels, directions and context) that is small enough to profile
+    "stereo_trwp_train_188": ("config2_stereo", {"training": True, "H": 188, "W": 620}, True),
     "denoise_isgmr_infer": ("config3_denoise", {}, False),
     # the same inputs as a training step (learning the truncated-quadratic function), 10 iterations
     "denoise_isgmr_train": ("config3_denoise", {"training": True, "n_iter": 10}, True),
