@@ -433,8 +433,9 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
       const float tt = (lc == n) ? t0 - S : t0;  // MPLayers/commonCUDA.cuh:131-145
       const float cv = ctab[lc * LS + f];
       dtile[k * kDS + lane] = cv * tt;
-      const float et = (lc != f || diag_ok) ? e * tt : 0.f;
-      acc[lc * LS + f] += et;  // idle lanes repeat lane L-1's read-modify-write in lockstep
+      // the diagonal (c == f) is accumulated like every other cell and dropped at the flush unless
+      // it is wanted; idle lanes repeat lane L-1's read-modify-write in lockstep
+      acc[lc * LS + f] = fmaf(e, tt, acc[lc * LS + f]);
       float* tb = ts + (k & 1) * 32;
       float* ib = is + (k & 1) * 32;
       tb[lane] = tt;
@@ -514,9 +515,9 @@ __global__ void __launch_bounds__(160, 1) bwd_tma_kernel(const __grid_constant__
     for (int i = lane; i < L * L; i += 32) {
       const int c = i / L, f = i - c * L;
       const float v = acc[c * LS + f];
-      if (v != 0.f) atomicAdd(part + i, v);
+      if (v != 0.f && (c != f || diag_ok)) atomicAdd(part + i, v);
     }
-  } else if (act) {  // rank 1: lane k folds every (c, f) with |c - f| == k, in a fixed order
+  } else if (act && (lane > 0 || diag_ok)) {  // rank 1: lane k folds every (c, f) with |c - f| == k, in a fixed order
     float v = 0.f;
     for (int c = 0; c < L; ++c) {
       if (c - lane >= 0) v += acc[c * LS + c - lane];
