@@ -751,8 +751,9 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
           cv0 = ctab[c0 * LS + f0];
           cv1 = ctab[(c0 + 1) * LS + f1];
           if (p.ctx_rank == 2) {
-            if (c0 != f0 || p.keep_diag) acc[c0 * LS + f0] += e * t0;
-            if (c0 + 1 != f1 || p.keep_diag) acc[(c0 + 1) * LS + f1] += e * t1;
+            // the diagonal is accumulated like every other cell and dropped at the flush unless wanted
+            acc[c0 * LS + f0] = fmaf(e, t0, acc[c0 * LS + f0]);
+            acc[(c0 + 1) * LS + f1] = fmaf(e, t1, acc[(c0 + 1) * LS + f1]);
           } else {
             if (c0 != f0 || p.keep_diag) atomicAdd(acc + (c0 > f0 ? c0 - f0 : f0 - c0), e * t0);
             if (c0 + 1 != f1 || p.keep_diag) atomicAdd(acc + (c0 + 1 > f1 ? c0 + 1 - f1 : f1 - c0 - 1), e * t1);
@@ -805,8 +806,9 @@ __global__ void __launch_bounds__(256, 1) bwd_pair_kernel(const __grid_constant_
   float* part = p.dctx_part + (long long)(g % p.n_slots) * (p.ctx_rank == 2 ? L * L : L);
   if (p.ctx_rank == 2) {
     for (int i = lane; i < L * L; i += 32) {
-      const float v = acc[(i / L) * LS + (i % L)];
-      if (v != 0.f) atomicAdd(part + i, v);
+      const int c = i / L, f = i - c * L;
+      const float v = acc[c * LS + f];
+      if (v != 0.f && (c != f || p.keep_diag)) atomicAdd(part + i, v);
     }
   } else {
     for (int i = lane; i < L; i += 32) {
