@@ -402,10 +402,14 @@ __global__ void __launch_bounds__(160, 1) fwd_tma_kernel(const __grid_constant__
       hb[lane] = fmaf(rho, r, uu);  // entries >= L are written but never read
     }
     __syncwarp();
-    float best;
-    int bi;
-    minplus_regrow<LMAX, TRAIN>(hb, cr, e, best, bi);
+    // The warp-wide minimum is issued as soon as the lane's own minimum is known: its latency
+    // runs behind the argmin flags, which need only the lane's candidates.
+    float val[LMAX];
+    minplus_vals<LMAX>(hb, cr, e, val);
+    const float best = min_tree<LMAX>(val);
     const float m = warp_min(best);
+    int bi = 0;
+    if (TRAIN) bi = highest_equal<LMAX>(val, best);
     r = best - m;
     // Unpredicated stores: idle lanes hold the same values as lane L-1 and write the same
     // address, and the normalisation index is warp-uniform.
