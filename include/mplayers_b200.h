@@ -296,8 +296,8 @@ int mpl_trwp_backward_static(const mpl_problem* p, const float* context, const f
  * call that used the workspace: 0 = every kernel ran to completion, otherwise the code of the wait
  * that gave up -- forward staging 101 / 102 (labels <= 32), 111 / 112 and 121 / 122 (one CTA per
  * chain, many labels per lane), 131 / 132 (two labels per lane); backward staging 201 / 202
- * (labels <= 32), 141 (two labels per lane), 151 (soft TRWP); 901 the self-test below -- and the
- * call's outputs must be discarded.  mpl_static_scratch_status
+ * (labels <= 32), 141 (two labels per lane), 161 (several labels per lane), 151 (soft TRWP); 901 the
+ * self-test below -- and the call's outputs must be discarded.  mpl_static_scratch_status
  * does the same for the built-in scratch of mpl_trwp_backward_static on the current device.
  * mpl_forward_status is the older name of mpl_workspace_status.  No counterpart in the reference,
  * whose kernels never wait on anything.
